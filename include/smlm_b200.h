@@ -1,0 +1,122 @@
+/* smlm_b200 - C ABI of the B200 (sm_100a) Segmented Multi-LoRA Multiplication path.
+ *
+ * Every entry point takes raw device pointers, sizes and a CUDA stream handle
+ * (a cudaStream_t passed as void*), enqueues work on that stream and returns an
+ * int status (SMLM_OK == 0) without synchronising and without allocating: all
+ * scratch is caller-owned (see smlm_b200_plan_bytes).  `dtype` selects the 16-bit
+ * storage type of activations and adapter weights; accumulation is always fp32.
+ *
+ * Weight layout follows the reference operator's `is_row_major` flag
+ * (kernel_src/csrc/loquetier_ops.cc:294-303): 0 = column-major, i.e. the PEFT
+ * layout A[r, h_in], B[h_out, r] that the reference's add_lora passes
+ * (src/loquetier_src/kernel_utils.py:118-119); 1 = row-major, the math layout
+ * A[h_in, r], B[r, h_out].
+ *
+ * Adapter weights are given as a device array of device addresses, exactly like the
+ * reference's int64 pointer tensors (src/loquetier_src/models/mixed_lora.py:151-161).
+ * Either the array has one entry per segment (`seg_ids == NULL`, what the reference
+ * builds with `wa_ptrs[lora_ids]`, mixed_lora.py:182), or it is the per-adapter
+ * table itself and `seg_ids[nseg]` holds each segment's adapter index, which saves
+ * the gather.  `n_table` is the length of the array in both cases.
+ */
+#ifndef SMLM_B200_H_
+#define SMLM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SMLM_OK = 0,
+  SMLM_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size */
+  SMLM_ERR_DTYPE = 2,            /* dtype is neither SMLM_F16 nor SMLM_BF16 */
+  SMLM_ERR_NO_KERNEL = 3,        /* shape outside the path: the small dimension must be a
+                                    multiple of 8 and <= 128, the large one a multiple of 8
+                                    (the reference's "No suitable kernel.", loquetier_ops.cc:318) */
+  SMLM_ERR_MISALIGNED = 4,       /* a base pointer is not 16-byte aligned */
+  SMLM_ERR_WORKSPACE = 5,        /* plan buffer too small */
+  SMLM_ERR_CUDA = 6,             /* the CUDA runtime rejected a launch */
+  SMLM_ERR_BAD_INDPTR = 7,       /* reported by smlm_b200_plan_status */
+  SMLM_ERR_BAD_POINTER = 8,      /* reported by smlm_b200_plan_status */
+  SMLM_ERR_BAD_INDEX = 9         /* reported by smlm_b200_plan_status */
+};
+
+enum { SMLM_F16 = 0, SMLM_BF16 = 1 };
+
+int smlm_b200_version(void);
+const char* smlm_b200_status_string(int status);
+
+/* Scratch bytes the reference asks its caller for, 60 per segment
+ * (smlm_forward_tmp_size, kernel_src/csrc/smlm_forward/smlm_forward_cutlass.cuh:48-52;
+ * bound as smlm_forward_cutlass_tmp_size, loquetier_ops.cc:372).  Kept so that the
+ * reference's own size check (loquetier_ops.cc:304) holds; this library never
+ * writes into that buffer. */
+size_t smlm_b200_tmp_size(int num_problems);
+
+/* Bytes of the plan buffer for a batch of T token rows in nseg segments. */
+size_t smlm_b200_plan_bytes(int T, int nseg);
+
+/* Build the work list of a batch from its device-resident segment index pointer
+ * seg_indptr[nseg + 1] (int32, the reference's `s`).  Replaces
+ * precompute_smlm_forward_args (smlm_forward_cutlass.cuh:31-46, launched :76).
+ * One plan serves every call on the same index pointer (shrink, expand, every
+ * projection of a model step).  `plan` must be 16-byte aligned. */
+int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int nseg, int T, void* stream);
+
+/* Synchronises the stream and reports what the device recorded in a plan: number
+ * of pieces and SMLM_OK or one of the SMLM_ERR_BAD_* codes.  For tests and
+ * debugging; the compute entry points never synchronise. */
+int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream);
+
+/* One segmented GEMM  Y[s_i:s_{i+1}] = scale_i * X[s_i:s_{i+1}] . W_i  (+ Y).
+ * Stand-in for one call of the reference operator smlm_forward_cutlass(y, x, w_ptr,
+ * s, tmp, is_row_major) (dispatch_smlm_forward_cutlass, loquetier_ops.cc:277-319;
+ * smlm_forward, smlm_forward_cutlass.cuh:61-175): d_in >= d_out runs the shrink
+ * kernel, d_in < d_out the expand kernel.  With seg_scale == NULL and
+ * accumulate == 0 the result is the reference's (alpha 1, beta 0: rows inside
+ * segments overwritten, other rows untouched). */
+int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int32_t* seg_ids,
+                   const float* seg_scale, void* plan, int n_table, int T, int nseg, int d_in, int d_out,
+                   int dtype, int is_row_major, int accumulate, void* stream);
+
+/* Fused LoRA forward  v = x . A^T ;  y (+)= scale * v . B^T  for every segment:
+ * the two operator calls of add_lora.forward (kernel_utils.py:114-120) and, with
+ * seg_scale / accumulate, the scale and add of MixedLoraLinear.forward
+ * (mixed_lora.py:214-217).  `v` [T, rank] is written in the storage type like the
+ * reference's intermediate (kernel_utils.py:117) and is what the backward needs. */
+int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
+                  const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
+                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, void* stream);
+
+/* Per-partition weight gradient  G_p = scale_p * P[rows_p]^T . Q[rows_p]  with P
+ * [T, rank] and Q [T, h]; G_p is [rank, h] (transposed == 0) or [h, rank]
+ * (transposed == 1), of the storage type or fp32 (grad_fp32), overwritten or
+ * accumulated into.  The dA / dB products of add_lora.backward
+ * (kernel_utils.py:144-145).  `plan` is any plan buffer of the batch; only its
+ * error word is used. */
+int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
+                    const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
+                    int transposed, int accumulate, int grad_fp32, void* stream);
+
+/* Fine-tuning backward of the fused forward over the train partitions
+ * part_indptr[npart + 1] (add_lora.backward, kernel_utils.py:129-147):
+ *   dV = scale * gO . B     (written to dv [T, rank], storage type)
+ *   dB_p = scale * gO^T . V   dA_p = dV^T . X   dX = dV . A
+ * `plan` is a plan built on part_indptr.  wa_table / wb_table / part_ids follow
+ * the forward's convention with partitions in the role of segments.  dX rows
+ * outside the partitions are not written (the reference returns zeros there,
+ * kernel_utils.py:136; the host wrapper clears them).  dA_table / dB_table are
+ * device arrays of npart output addresses in the layout of A and B. */
+int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
+                  const void* x, const void* v, const void* const* wa_table, const void* const* wb_table,
+                  const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
+                  int n_table, int T, int npart, int h_in, int h_out, int rank, int dtype, int is_row_major,
+                  int accumulate_grads, int grad_fp32, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SMLM_B200_H_ */

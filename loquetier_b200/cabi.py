@@ -1,0 +1,70 @@
+"""ctypes binding of ``libsmlm_b200.so`` (declared in ``include/smlm_b200.h``).
+
+The library is the product: there is no fallback.  If it has not been built the
+import fails with the command that builds it."""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_int, c_size_t, c_void_p
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsmlm_b200.so")
+
+SMLM_OK = 0
+SMLM_F16 = 0
+SMLM_BF16 = 1
+
+STATUS_NAMES = {
+    0: "SMLM_OK", 1: "SMLM_ERR_INVALID_ARGUMENT", 2: "SMLM_ERR_DTYPE", 3: "SMLM_ERR_NO_KERNEL",
+    4: "SMLM_ERR_MISALIGNED", 5: "SMLM_ERR_WORKSPACE", 6: "SMLM_ERR_CUDA", 7: "SMLM_ERR_BAD_INDPTR",
+    8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX",
+}
+
+# name -> (restype, argtypes); mirrors include/smlm_b200.h one to one
+SIGNATURES = {
+    "smlm_b200_version": (c_int, []),
+    "smlm_b200_status_string": (c_char_p, [c_int]),
+    "smlm_b200_tmp_size": (c_size_t, [c_int]),
+    "smlm_b200_plan_bytes": (c_size_t, [c_int, c_int]),
+    "smlm_b200_plan": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p]),
+    "smlm_b200_plan_status": (c_int, [c_void_p, ctypes.POINTER(c_int), c_void_p]),
+    "smlm_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_wgrad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_bwd": (c_int, [c_void_p] * 13 + [c_int] * 10 + [c_void_p]),
+}
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: the CUDA library of the SMLM path has not been built. "
+            "Build it with `python -m loquetier_b200.build` (needs nvcc); there is no CPU fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    return lib
+
+
+lib = _load()
+
+
+class SmlmError(RuntimeError):
+    """Raised for a non-zero status; the reference surfaces its failures as
+    RuntimeError through TORCH_CHECK (kernel_src/csrc/loquetier_ops.cc:318)."""
+
+    def __init__(self, status: int, where: str):
+        self.status = status
+        msg = lib.smlm_b200_status_string(status).decode()
+        super().__init__(f"{where}: {msg} [{STATUS_NAMES.get(status, status)}]")
+
+
+def check(status: int, where: str) -> None:
+    if status != SMLM_OK:
+        raise SmlmError(status, where)

@@ -1,0 +1,313 @@
+// C ABI of the SMLM path: argument checks, kernel selection and launches.
+// Declarations and the reference interfaces they stand in for: include/smlm_b200.h.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+
+#include "../../include/smlm_b200.h"
+#include "smlm_expand.cuh"
+#include "smlm_plan.cuh"
+#include "smlm_shrink.cuh"
+#include "smlm_wgrad.cuh"
+
+namespace {
+
+using namespace smlm;
+
+constexpr int kTargetCtas = 148 * 4;  // aim for four resident CTAs on each of the 148 SMs
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+inline int max_pieces_of(int T, int nseg) { return T / kBM + nseg; }
+
+inline int pow2_at_least(int v) {
+  int p = 1;
+  while (p < v) p <<= 1;
+  return p;
+}
+
+// How many ways to cut the long dimension so that the grid fills the machine while
+// every CTA still streams at least four pipeline stages.
+inline int pick_split(int work_items, int stages_total) {
+  int ks = pow2_at_least((kTargetCtas + std::max(work_items, 1) - 1) / std::max(work_items, 1));
+  ks = std::min(ks, 8);
+  while (ks > 1 && stages_total / ks < 4) ks >>= 1;
+  return std::max(ks, 1);
+}
+
+template <typename Kern, typename Args>
+int launch(Kern kern, dim3 grid, int cluster_x, int smem_bytes, cudaStream_t stream, const Args& args) {
+  if (grid.x == 0 || grid.y == 0) return SMLM_OK;
+  if (smem_bytes > 48 * 1024) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+      cudaGetLastError();
+      return SMLM_ERR_CUDA;
+    }
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = smem_bytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster_x;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (cudaLaunchKernelEx(&cfg, kern, args) != cudaSuccess) {
+    cudaGetLastError();
+    return SMLM_ERR_CUDA;
+  }
+  return SMLM_OK;
+}
+
+// ---- shrink -----------------------------------------------------------------
+
+template <typename T, int NT, bool RM>
+int launch_shrink(const ShrinkArgs& a, int max_pieces, cudaStream_t stream) {
+  return launch(shrink_kernel<T, NT, RM>, dim3(max_pieces * a.ksplit, 1, 1), a.ksplit,
+                ShrinkSmem<NT, RM>::kTotal, stream, a);
+}
+
+template <typename T, bool RM>
+int dispatch_shrink_nt(const ShrinkArgs& a, int max_pieces, cudaStream_t stream) {
+  const int nt = (a.N + 7) / 8;
+  if (nt <= 1) return launch_shrink<T, 1, RM>(a, max_pieces, stream);
+  if (nt <= 2) return launch_shrink<T, 2, RM>(a, max_pieces, stream);
+  if (nt <= 4) return launch_shrink<T, 4, RM>(a, max_pieces, stream);
+  if (nt <= 8) return launch_shrink<T, 8, RM>(a, max_pieces, stream);
+  return launch_shrink<T, 16, RM>(a, max_pieces, stream);
+}
+
+int run_shrink(void* d, const void* x, const void* const* w_table, const int32_t* ids, const float* scale,
+               void* plan, int n_table, int T, int nseg, int K, int N, int dtype, int row_major,
+               cudaStream_t stream) {
+  ShrinkArgs a;
+  a.d = d; a.x = x; a.w_table = w_table; a.ids = ids; a.scale = scale;
+  a.plan = static_cast<int*>(plan);
+  a.n_table = n_table; a.N = N; a.K = K;
+  const int mp = max_pieces_of(T, nseg);
+  a.ksplit = pick_split(mp, (K + kKC - 1) / kKC);
+  if (dtype == SMLM_F16)
+    return row_major ? dispatch_shrink_nt<__half, true>(a, mp, stream)
+                     : dispatch_shrink_nt<__half, false>(a, mp, stream);
+  return row_major ? dispatch_shrink_nt<__nv_bfloat16, true>(a, mp, stream)
+                   : dispatch_shrink_nt<__nv_bfloat16, false>(a, mp, stream);
+}
+
+// ---- expand -----------------------------------------------------------------
+
+template <typename T, int KT, bool RM>
+int launch_expand(const ExpandArgs& a, int max_pieces, cudaStream_t stream) {
+  return launch(expand_kernel<T, KT, RM>, dim3(max_pieces, (a.N + kNCH - 1) / kNCH, 1), 1,
+                ExpandSmem<KT>::kTotal, stream, a);
+}
+
+template <typename T, bool RM>
+int dispatch_expand_kt(const ExpandArgs& a, int max_pieces, cudaStream_t stream) {
+  const int kt = (a.K + 15) / 16;
+  if (kt <= 1) return launch_expand<T, 1, RM>(a, max_pieces, stream);
+  if (kt <= 2) return launch_expand<T, 2, RM>(a, max_pieces, stream);
+  if (kt <= 4) return launch_expand<T, 4, RM>(a, max_pieces, stream);
+  return launch_expand<T, 8, RM>(a, max_pieces, stream);
+}
+
+int run_expand(void* d, const void* x, const void* const* w_table, const int32_t* ids, const float* scale,
+               void* plan, int n_table, int T, int nseg, int K, int N, int dtype, int row_major, int accumulate,
+               cudaStream_t stream) {
+  ExpandArgs a;
+  a.d = d; a.x = x; a.w_table = w_table; a.ids = ids; a.scale = scale;
+  a.plan = static_cast<int*>(plan);
+  a.n_table = n_table; a.N = N; a.K = K; a.accumulate = accumulate;
+  const int mp = max_pieces_of(T, nseg);
+  if (dtype == SMLM_F16)
+    return row_major ? dispatch_expand_kt<__half, true>(a, mp, stream)
+                     : dispatch_expand_kt<__half, false>(a, mp, stream);
+  return row_major ? dispatch_expand_kt<__nv_bfloat16, true>(a, mp, stream)
+                   : dispatch_expand_kt<__nv_bfloat16, false>(a, mp, stream);
+}
+
+// ---- wgrad ------------------------------------------------------------------
+
+template <typename T, int RT>
+int launch_wgrad(const WgradArgs& a, cudaStream_t stream) {
+  return launch(wgrad_kernel<T, RT>, dim3(a.npart * a.ksplit, (a.H + kWgCols - 1) / kWgCols, 1), a.ksplit,
+                WgradSmem<RT>::kTotal, stream, a);
+}
+
+template <typename T>
+int dispatch_wgrad_rt(const WgradArgs& a, cudaStream_t stream) {
+  const int rt = (a.R + 15) / 16;
+  if (rt <= 1) return launch_wgrad<T, 1>(a, stream);
+  if (rt <= 2) return launch_wgrad<T, 2>(a, stream);
+  if (rt <= 4) return launch_wgrad<T, 4>(a, stream);
+  return launch_wgrad<T, 8>(a, stream);
+}
+
+int run_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
+              const float* scale, const int32_t* ids, int n_table, int* err, int npart, int T, int R, int H,
+              int dtype, int transposed, int accumulate, int grad_fp32, cudaStream_t stream) {
+  WgradArgs a;
+  a.g_table = g_table; a.p = p; a.q = q; a.part_indptr = part_indptr; a.scale = scale; a.ids = ids;
+  a.n_table = n_table; a.err = err; a.npart = npart; a.T = T; a.R = R; a.H = H;
+  a.transposed = transposed; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
+  const int slabs = (H + kWgCols - 1) / kWgCols;
+  // token chunks of an average partition bound the useful split
+  const int avg_chunks = std::max(1, (T / std::max(npart, 1) + kWgTok - 1) / kWgTok);
+  a.ksplit = pick_split(npart * slabs, avg_chunks);
+  return dtype == SMLM_F16 ? dispatch_wgrad_rt<__half>(a, stream) : dispatch_wgrad_rt<__nv_bfloat16>(a, stream);
+}
+
+inline bool small_dim_ok(int v) { return v >= 8 && v <= 128 && (v % 8) == 0; }
+inline bool large_dim_ok(int v) { return v >= 8 && (v % 8) == 0; }
+
+}  // namespace
+
+extern "C" {
+
+int smlm_b200_version(void) { return 1; }
+
+const char* smlm_b200_status_string(int status) {
+  switch (status) {
+    case SMLM_OK: return "ok";
+    case SMLM_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case SMLM_ERR_DTYPE: return "unsupported dtype (fp16 and bf16 only)";
+    case SMLM_ERR_NO_KERNEL: return "No suitable kernel.";
+    case SMLM_ERR_MISALIGNED: return "pointer not 16-byte aligned";
+    case SMLM_ERR_WORKSPACE: return "plan buffer too small";
+    case SMLM_ERR_CUDA: return "CUDA launch failed";
+    case SMLM_ERR_BAD_INDPTR: return "segment index pointer is not monotone within [0, T]";
+    case SMLM_ERR_BAD_POINTER: return "adapter pointer is null or not 16-byte aligned";
+    case SMLM_ERR_BAD_INDEX: return "adapter index outside the table";
+    default: return "unknown status";
+  }
+}
+
+size_t smlm_b200_tmp_size(int num_problems) {
+  // three pointer arrays, three int64 leading dimensions and one 3-int problem size per segment
+  return num_problems > 0 ? static_cast<size_t>(3 * 8 + 3 * 8 + 12) * static_cast<size_t>(num_problems) : 0;
+}
+
+size_t smlm_b200_plan_bytes(int T, int nseg) {
+  if (T < 0 || nseg < 0) return 0;
+  return sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_pieces_of(T, nseg) + 1);
+}
+
+int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int nseg, int T, void* stream) {
+  if (plan == nullptr || seg_indptr == nullptr || nseg < 0 || T < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
+  plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg));
+  if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
+  return SMLM_OK;
+}
+
+int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream) {
+  if (plan == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  int hdr[kPlanHeaderInts] = {0, 0, 0, 0};
+  if (cudaMemcpyAsync(hdr, plan, sizeof(hdr), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)) !=
+          cudaSuccess ||
+      cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) {
+    cudaGetLastError();
+    return SMLM_ERR_CUDA;
+  }
+  if (n_pieces != nullptr) *n_pieces = hdr[0];
+  if (hdr[1] & kErrBadIndptr) return SMLM_ERR_BAD_INDPTR;
+  if (hdr[1] & kErrBadIndex) return SMLM_ERR_BAD_INDEX;
+  if (hdr[1] & kErrBadPointer) return SMLM_ERR_BAD_POINTER;
+  return SMLM_OK;
+}
+
+int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int32_t* seg_ids,
+                   const float* seg_scale, void* plan, int n_table, int T, int nseg, int d_in, int d_out,
+                   int dtype, int is_row_major, int accumulate, void* stream) {
+  if (T < 0 || nseg < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || nseg == 0) return SMLM_OK;
+  if (y == nullptr || x == nullptr || w_table == nullptr || plan == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(y) || !aligned16(x) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (d_in >= d_out) {
+    if (!small_dim_ok(d_out) || !large_dim_ok(d_in)) return SMLM_ERR_NO_KERNEL;
+    if (accumulate) return SMLM_ERR_NO_KERNEL;
+    return run_shrink(y, x, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, dtype,
+                      is_row_major, st);
+  }
+  if (!small_dim_ok(d_in) || !large_dim_ok(d_out)) return SMLM_ERR_NO_KERNEL;
+  return run_expand(y, x, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, dtype,
+                    is_row_major, accumulate, st);
+}
+
+int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
+                  const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
+                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, void* stream) {
+  if (T < 0 || nseg < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || nseg == 0) return SMLM_OK;
+  if (y == nullptr || x == nullptr || v == nullptr || wa_table == nullptr || wb_table == nullptr ||
+      plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc = run_shrink(v, x, wa_table, seg_ids, nullptr, plan, n_table, T, nseg, h_in, rank, dtype, is_row_major,
+                      st);
+  if (rc != SMLM_OK) return rc;
+  return run_expand(y, v, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, rank, h_out, dtype,
+                    is_row_major, accumulate, st);
+}
+
+int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
+                    const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
+                    int transposed, int accumulate, int grad_fp32, void* stream) {
+  if (T < 0 || npart < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (npart == 0) return SMLM_OK;
+  if (g_table == nullptr || p == nullptr || q == nullptr || part_indptr == nullptr || plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
+  return run_wgrad(g_table, p, q, part_indptr, part_scale, nullptr, 0, static_cast<int*>(plan) + 1, npart, T,
+                   rank, h, dtype, transposed, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
+                  const void* x, const void* v, const void* const* wa_table, const void* const* wb_table,
+                  const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
+                  int n_table, int T, int npart, int h_in, int h_out, int rank, int dtype, int is_row_major,
+                  int accumulate_grads, int grad_fp32, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || npart == 0) return SMLM_OK;
+  if (dx == nullptr || dA_table == nullptr || dB_table == nullptr || dv == nullptr || go == nullptr ||
+      x == nullptr || v == nullptr || wa_table == nullptr || wb_table == nullptr || part_indptr == nullptr ||
+      plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(dx) || !aligned16(dv) || !aligned16(go) || !aligned16(x) || !aligned16(v) || !aligned16(plan))
+    return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* err = static_cast<int*>(plan) + 1;
+  // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a
+  // row-major [K = h_out][N = r] operand; the math layout B [r, h_out] is the
+  // column-major one.  The layout flag therefore flips for both backward GEMMs.
+  int rc = run_shrink(dv, go, wb_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank, dtype,
+                      !is_row_major, st);
+  if (rc != SMLM_OK) return rc;
+  // dB = scale * gO^T . V : [h_out, r] in the PEFT layout (transposed store)
+  rc = run_wgrad(dB_table, v, go, part_indptr, part_scale, part_ids, n_table, err, npart, T, rank, h_out, dtype,
+                 is_row_major ? 0 : 1, accumulate_grads, grad_fp32, st);
+  if (rc != SMLM_OK) return rc;
+  // dA = dV^T . X : [r, h_in] in the PEFT layout
+  rc = run_wgrad(dA_table, dv, x, part_indptr, nullptr, nullptr, 0, err, npart, T, rank, h_in, dtype,
+                 is_row_major ? 1 : 0, accumulate_grads, grad_fp32, st);
+  if (rc != SMLM_OK) return rc;
+  // dX = dV . A
+  return run_expand(dx, dv, wa_table, part_ids, nullptr, plan, n_table, T, npart, rank, h_in, dtype,
+                    !is_row_major, 0, st);
+}
+
+}  // extern "C"

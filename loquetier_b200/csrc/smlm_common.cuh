@@ -1,0 +1,179 @@
+// Device-side building blocks shared by the SMLM kernels (sm_100a).
+//
+// Everything here is a thin wrapper over one PTX instruction or one piece of
+// index arithmetic: 16-byte asynchronous copies with zero fill, ldmatrix,
+// the m16n8k16 tensor-core MMA with fp32 accumulation, the shared-memory chunk
+// swizzle, and conversions between fp32 and the two 16-bit storage types.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace smlm {
+
+constexpr int kThreads = 128;       // 4 warps per CTA in every kernel
+constexpr int kBM = 64;             // rows of one piece (a slice of one segment)
+constexpr int kPlanHeaderInts = 4;  // {count, error, max_pieces, T}
+
+// error bits a kernel may OR into the plan header's error word
+constexpr int kErrBadIndptr = 1;    // indptr not monotone, negative or beyond T
+constexpr int kErrBadPointer = 2;   // an adapter pointer is null or not 16-byte aligned
+constexpr int kErrBadIndex = 4;     // an adapter index outside the table
+
+struct __align__(16) Piece {
+  int row0;   // first token row
+  int nrows;  // 1..kBM
+  int seg;    // segment (or train partition) the rows belong to
+  int pad;
+};
+
+// ---------------------------------------------------------------------------
+// shared-memory addressing
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// A tile is stored as rows of `C` 16-byte chunks (C a power of two).  Rows
+// narrower than 128 bytes are grouped so that eight consecutive ldmatrix rows of
+// one chunk column land in eight different 16-byte bank groups.
+template <int C>
+__device__ __forceinline__ int swz(int row, int chunk) {
+  if constexpr (C >= 8) {
+    return chunk ^ (row & 7);
+  } else if constexpr (C == 1) {
+    return chunk;
+  } else {
+    constexpr int rows_per_128 = 8 / C;
+    return chunk ^ ((row / rows_per_128) & (C - 1));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// global -> shared asynchronous copy, 16 bytes, zero-filled when !valid
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+  const int sz = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(sz) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// ldmatrix / mma
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+template <typename T>
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1);
+
+template <>
+__device__ __forceinline__ void mma16816<__half>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <>
+__device__ __forceinline__ void mma16816<__nv_bfloat16>(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                                        uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// ---------------------------------------------------------------------------
+// conversions
+// ---------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+template <typename T>
+__device__ __forceinline__ float2 unpack2(uint32_t u);
+template <>
+__device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+template <>
+__device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+
+// Round to the 16-bit storage type and back: what the reference does to every
+// intermediate it materialises.
+template <typename T>
+__device__ __forceinline__ float round_through(float a);
+template <>
+__device__ __forceinline__ float round_through<__half>(float a) {
+  return __half2float(__float2half_rn(a));
+}
+template <>
+__device__ __forceinline__ float round_through<__nv_bfloat16>(float a) {
+  return __bfloat162float(__float2bfloat16_rn(a));
+}
+
+// ---------------------------------------------------------------------------
+// adapter lookup: per-segment pointer table, or an adapter table indexed by a
+// per-segment adapter id.  Records a fault instead of touching a bad address.
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ const void* adapter_ptr(const void* const* table, const int32_t* ids, int n_table,
+                                                   int seg, int* err) {
+  int idx = seg;
+  if (ids != nullptr) {
+    idx = ids[seg];
+    if (idx < 0 || idx >= n_table) {
+      atomicOr(err, kErrBadIndex);
+      return nullptr;
+    }
+  }
+  const void* p = table[idx];
+  if (p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) != 0) {
+    atomicOr(err, kErrBadPointer);
+    return nullptr;
+  }
+  return p;
+}
+
+__device__ __forceinline__ float adapter_scale(const float* scale, const int32_t* ids, int n_table, int seg) {
+  if (scale == nullptr) return 1.0f;
+  int idx = seg;
+  if (ids != nullptr) {
+    idx = ids[seg];
+    if (idx < 0 || idx >= n_table) return 0.0f;
+  }
+  return scale[idx];
+}
+
+}  // namespace smlm

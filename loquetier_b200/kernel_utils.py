@@ -1,0 +1,126 @@
+"""Host side of the SMLM path, mirroring src/loquetier_src/kernel_utils.py:
+``BatchLenInfo`` (row-range bookkeeping, :11-98) and the ``add_lora`` autograd
+function (:101-147) with the same call signature and return structure.
+
+Differences that stay inside the reference's contract:
+* forward plans the batch once and runs shrink and expand from that plan; no
+  stream synchronisation, ``v`` is kept for the backward instead of recomputed;
+* backward runs native kernels.  The reference's formulas only type-check for the
+  math layout while its forward passes the PEFT layout
+  (A [r, h_in], B [h_out, r]); this backward returns the gradients in the layout
+  of the weights that forward used, which for the math layout are exactly the
+  reference's expressions."""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+from torch.autograd.function import Function, FunctionCtx
+
+from . import ops
+
+
+class BatchLenInfo:
+    """Lengths of one flattened batch whose rows are ordered
+    train | eval + prefill | decode."""
+
+    def __init__(self, trains: List[Tuple[int, ...]], prefills: List[int], decode: int,
+                 evals: List[Tuple[int, ...]], indptr_device: torch.device,
+                 indptr_dtype: torch.dtype = torch.int32):
+        self._train_batches = trains
+        self._eval_batches = evals
+        self._prefills = list(prefills)
+        self._decode = decode
+        tl = np.asarray([int(t[0]) * int(t[1]) for t in trains], dtype=np.int64)
+        if tl.size:
+            self._train_partition = np.concatenate([[0], np.cumsum(tl)])
+            self._tlen = self._train_partition[-1]
+        else:
+            self._train_partition = []
+            self._tlen = 0
+        if len(evals) > 0:
+            el = np.asarray([int(e[0]) * int(e[1]) for e in evals], dtype=np.int64)
+            self._eval_partition = np.cumsum(np.concatenate([[self._tlen], el]))
+        else:
+            self._eval_partition = []
+        if len(prefills) > 0:
+            cs = np.concatenate([[0], np.cumsum(np.asarray(prefills, dtype=np.int64))])
+            self._indptr = torch.tensor(cs, dtype=indptr_dtype, device=indptr_device)
+            self._doff = cs[-1] + self._tlen
+        else:
+            self._indptr = None
+            self._doff = self._tlen
+
+    train_batches = property(lambda self: self._train_batches)
+    train_partition = property(lambda self: self._train_partition)
+    eval_batches = property(lambda self: self._eval_batches)
+    eval_partition = property(lambda self: self._eval_partition)
+    prefills = property(lambda self: self._prefills)
+    decode = property(lambda self: self._decode)
+    tlen = property(lambda self: self._tlen)
+    doff = property(lambda self: self._doff)
+    indptr = property(lambda self: self._indptr)
+
+
+def _ptr_table(tensors: Sequence[torch.Tensor], device) -> torch.Tensor:
+    return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device=device)
+
+
+class add_lora(Function):
+    """``add_lora.apply(y_shape, x, wa_ptr, wb_ptr, s, lora_rank, train_len,
+    train_partition, *trainable)`` with ``trainable`` = (A_0, B_0, A_1, B_1, ...),
+    one pair per train partition, in the PEFT layout."""
+
+    # set by callers that already planned the batch (the LoRA linear does, once per
+    # step); consumed by the next forward whose ``s`` is the very same tensor
+    _shared_plan: Optional[ops.Plan] = None
+
+    @staticmethod
+    def forward(y_shape, x, wa_ptr, wb_ptr, s, lora_rank, train_len, train_partition, *args):
+        y = torch.empty(y_shape, dtype=x.dtype, device=x.device)
+        v = torch.empty((x.size(0), lora_rank), dtype=x.dtype, device=x.device)
+        plan = add_lora._shared_plan
+        if plan is None or plan.indptr is not s or plan.T != x.size(0):
+            plan = ops.Plan(s, x.size(0))
+        if x.size(0) > 0 and s.numel() > 1:
+            ops.fwd(y, x, v, wa_ptr, wb_ptr, plan, lora_rank, is_row_major=False)
+        add_lora._last_v = v
+        return y
+
+    @staticmethod
+    def setup_context(ctx: FunctionCtx, inputs: Tuple, output: torch.Tensor):
+        _, x, _, _, _, rank, tl, tp, *weight_list = inputs
+        ctx.tp = tp
+        ctx.rank = rank
+        tl = int(tl)
+        v = add_lora._last_v
+        add_lora._last_v = None
+        ctx.save_for_backward(x[:tl, ...], v[:tl, ...], *weight_list)
+
+    @staticmethod
+    def backward(ctx: FunctionCtx, grad_output: torch.Tensor):
+        x, v, *weight_list = ctx.saved_tensors
+        tp = ctx.tp
+        if len(weight_list) == 0:
+            return None, None, None, None, None, None, None, None
+        assert len(weight_list) % 2 == 0
+        # one (A, B) pair per train partition, as the reference zips them
+        npart = min(len(weight_list) // 2, len(tp) - 1)
+        dev = grad_output.device
+        go = grad_output.contiguous()
+        grad_x = torch.zeros((go.size(0), x.size(1)), dtype=go.dtype, device=dev)
+        tl = int(tp[npart])
+        if tl == 0:
+            return (None, grad_x, None, None, None, None, None, None,
+                    *[torch.zeros_like(w) for w in weight_list])
+        part = torch.tensor([int(t) for t in tp[:npart + 1]], dtype=torch.int32, device=dev)
+        plan = ops.Plan(part, tl)
+        was, wbs = weight_list[0:2 * npart:2], weight_list[1:2 * npart:2]
+        grads = [torch.empty_like(w) for w in weight_list[:2 * npart]]
+        dv = torch.empty((tl, ctx.rank), dtype=go.dtype, device=dev)
+        ops.bwd(grad_x, _ptr_table(grads[::2], dev), _ptr_table(grads[1::2], dev), dv, go,
+                x.contiguous(), v.contiguous(), _ptr_table(was, dev), _ptr_table(wbs, dev), plan, ctx.rank,
+                is_row_major=False)
+        grads += [None] * (len(weight_list) - 2 * npart)
+        return None, grad_x, None, None, None, None, None, None, *grads

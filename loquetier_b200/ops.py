@@ -1,0 +1,115 @@
+"""Torch-facing wrappers of the C ABI: they only translate tensors into pointers,
+sizes and the current CUDA stream.  Device memory (outputs, the plan buffer) is
+allocated by torch; the library itself never allocates and never synchronises."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import cabi
+from .cabi import check, lib
+
+_DT = {torch.float16: cabi.SMLM_F16, torch.bfloat16: cabi.SMLM_BF16}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        # same wording as the reference's dispatcher (loquetier_ops.cc:318)
+        raise RuntimeError(f"No suitable kernel. dtype={t.dtype}") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _chk_cuda_contig(t: torch.Tensor, name: str, dim: int):
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if t.dim() != dim:
+        raise RuntimeError(f"{name} must be a {dim}D tensor")
+
+
+class Plan:
+    """Work list of one batch: built on the device from the segment index pointer,
+    shared by every SMLM call of the batch (all projections, shrink and expand)."""
+
+    __slots__ = ("buf", "indptr", "nseg", "T")
+
+    def __init__(self, indptr: torch.Tensor, T: int):
+        _chk_cuda_contig(indptr, "s", 1)
+        if indptr.dtype != torch.int32:
+            raise RuntimeError("s must be int32")
+        self.indptr = indptr
+        self.nseg = int(indptr.numel()) - 1
+        self.T = int(T)
+        nbytes = lib.smlm_b200_plan_bytes(self.T, max(self.nseg, 0))
+        self.buf = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=indptr.device)
+        with torch.cuda.device(indptr.device):
+            check(lib.smlm_b200_plan(self.buf.data_ptr(), nbytes, indptr.data_ptr(), self.nseg, self.T,
+                                     _stream(indptr)), "smlm_b200_plan")
+
+    def status(self):
+        """Synchronises.  Returns (n_pieces, status code)."""
+        import ctypes
+        n = ctypes.c_int(0)
+        with torch.cuda.device(self.buf.device):
+            rc = lib.smlm_b200_plan_status(self.buf.data_ptr(), ctypes.byref(n), _stream(self.buf))
+        return n.value, rc
+
+    def raise_if_failed(self):
+        _, rc = self.status()
+        check(rc, "smlm plan")
+
+
+def gemm(y, x, w_table, plan: Plan, is_row_major=False, seg_ids=None, seg_scale=None, accumulate=False):
+    """One segmented GEMM (one reference operator call)."""
+    with torch.cuda.device(x.device):
+        check(lib.smlm_b200_gemm(y.data_ptr(), x.data_ptr(), w_table.data_ptr(), _p(seg_ids), _p(seg_scale),
+                                 plan.buf.data_ptr(), int(w_table.numel()), int(x.size(0)), plan.nseg,
+                                 int(x.size(1)), int(y.size(1)), _dtype_code(x), int(bool(is_row_major)),
+                                 int(bool(accumulate)), _stream(x)), "smlm_b200_gemm")
+    return y
+
+
+def fwd(y, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, seg_ids=None, seg_scale=None,
+        accumulate=False):
+    """Fused shrink + expand (+ scale, + accumulate into y); writes v [T, rank]."""
+    with torch.cuda.device(x.device):
+        check(lib.smlm_b200_fwd(y.data_ptr(), x.data_ptr(), v.data_ptr(), wa_table.data_ptr(),
+                                wb_table.data_ptr(), _p(seg_ids), _p(seg_scale), plan.buf.data_ptr(),
+                                int(wa_table.numel()), int(x.size(0)), plan.nseg, int(x.size(1)),
+                                int(y.size(1)), int(rank), _dtype_code(x), int(bool(is_row_major)),
+                                int(bool(accumulate)), _stream(x)), "smlm_b200_fwd")
+    return y
+
+
+def wgrad(g_table, p, q, part_indptr, plan: Plan, transposed: bool, part_scale=None, accumulate=False,
+          grad_fp32=False):
+    with torch.cuda.device(p.device):
+        check(lib.smlm_b200_wgrad(g_table.data_ptr(), p.data_ptr(), q.data_ptr(), part_indptr.data_ptr(),
+                                  _p(part_scale), plan.buf.data_ptr(), int(part_indptr.numel()) - 1,
+                                  int(p.size(0)), int(p.size(1)), int(q.size(1)), _dtype_code(p),
+                                  int(bool(transposed)), int(bool(accumulate)), int(bool(grad_fp32)), _stream(p)),
+              "smlm_b200_wgrad")
+
+
+def bwd(dx, dA_table, dB_table, dv, go, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False,
+        part_ids=None, part_scale=None, accumulate_grads=False, grad_fp32=False):
+    """Backward over the train partitions ``plan.indptr``; rows = go.size(0)."""
+    with torch.cuda.device(go.device):
+        check(lib.smlm_b200_bwd(dx.data_ptr(), dA_table.data_ptr(), dB_table.data_ptr(), dv.data_ptr(),
+                                go.data_ptr(), x.data_ptr(), v.data_ptr(), wa_table.data_ptr(),
+                                wb_table.data_ptr(), _p(part_ids), _p(part_scale), plan.indptr.data_ptr(),
+                                plan.buf.data_ptr(), int(wa_table.numel()), plan.T, plan.nseg,
+                                int(x.size(1)), int(go.size(1)), int(rank), _dtype_code(go),
+                                int(bool(is_row_major)), int(bool(accumulate_grads)), int(bool(grad_fp32)),
+                                _stream(go)), "smlm_b200_bwd")

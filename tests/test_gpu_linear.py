@@ -1,0 +1,147 @@
+"""The LoRA linear and the add_lora autograd function on the GPU, against the
+vectors the reference's own MixedLoraLinear produced and against the oracle."""
+import numpy as np
+import pytest
+import torch
+from torch import nn
+
+from helpers import assert_close, load_npz
+from oracle import smlm_oracle as O
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _build_linear(z, scale_mode, dtype):
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    h_in, h_out, r, n_ad, scale = z["meta"]
+    h_in, h_out, r, n_ad = int(h_in), int(h_out), int(r), int(n_ad)
+    base = nn.Linear(h_in, h_out, bias=False, dtype=dtype, device=DEV)
+    with torch.no_grad():
+        base.weight.copy_(z["w_base"].to(dtype))
+    ads = [NamedLoraLayer(f"a{i}", z[f"wa{i}"].to(DEV).to(dtype).contiguous(),
+                          z[f"wb{i}"].to(DEV).to(dtype).contiguous(), nn.Identity(),
+                          None if scale < 0 else float(scale)) for i in range(n_ad)]
+    ctx = MixedLoraContext()
+    lin = MixedLoraLinear(ctx, base, ads, r, dtype, is_scaled=scale < 0)
+    lens, ids = z["lens"].tolist(), z["ids"].tolist()
+    seg = torch.cumsum(torch.tensor([0] + lens, dtype=torch.int32, device=DEV), 0, dtype=torch.int32)
+    blen = BatchLenInfo([], [], 0, [], torch.device(DEV))
+    ctx.update(blen, ids, torch.tensor(lens, dtype=torch.int32, device=DEV), seg, [])
+    return lin, ctx
+
+
+@pytest.mark.parametrize("name", ["linear_c1_bf16", "linear_c1_fp16_prescaled", "linear_ragged_bf16"])
+@pytest.mark.parametrize("path", ["fused", "reference_ops"])
+def test_linear_matches_reference_golden(name, path):
+    z = load_npz(name)
+    lin, _ = _build_linear(z, None, z["dtype"])
+    x = z["x"].to(DEV)
+    with torch.no_grad():
+        y = lin(x) if path == "fused" else lin.forward_reference_ops(x)
+    assert_close(y, z["y"], what=f"{name}/{path}")
+
+
+def test_linear_c1_fp32_answer_in_16bit():
+    """The CPU plumbing configuration (fp32 on the CPU in the reference) run in
+    bf16 and fp16 on the GPU against the fp32 answer."""
+    z = load_npz("linear_c1_fp32")
+    for dt in (torch.bfloat16, torch.float16):
+        lin, _ = _build_linear(z, None, dt)
+        with torch.no_grad():
+            y = lin(z["x"].to(DEV).to(dt))
+        assert_close(y, z["y"], rtol=2e-2, atol=2e-2, what=f"c1 {dt}")
+
+
+@pytest.mark.parametrize("path", ["fused", "reference_ops"])
+def test_linear_training_step_vs_oracle(path):
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    dt = torch.bfloat16
+    h_in, h_out, r, n_ad = 256, 320, 16, 4
+    g = torch.Generator().manual_seed(11)
+    # rows: two train requests (adapters 2 and 0), one prefill (adapter 1), three decodes
+    trains = [(1, 40), (2, 24)]
+    lens, ids = [40, 48, 17, 1, 2], [2, 0, 1, 0, 3]
+    T = sum(lens)
+    x = torch.randn((T, h_in), generator=g).to(dt)
+    wbase = (torch.randn((h_out, h_in), generator=g) * 0.02).to(dt)
+    was = [(torch.randn((r, h_in), generator=g) / 16).to(dt) for _ in range(n_ad)]
+    wbs = [(torch.randn((h_out, r), generator=g) * 0.02).to(dt) for _ in range(n_ad)]
+    go = torch.randn((T, h_out), generator=g).to(dt)
+    scale = [2.0, 0.5, 1.0, 4.0]
+
+    base = nn.Linear(h_in, h_out, bias=False, dtype=dt, device=DEV)
+    with torch.no_grad():
+        base.weight.copy_(wbase)
+    base.weight.requires_grad_(False)
+    ads = [NamedLoraLayer(f"a{i}", was[i].to(DEV).contiguous(), wbs[i].to(DEV).contiguous(), nn.Identity(),
+                          scale[i]) for i in range(n_ad)]
+    ctx = MixedLoraContext()
+    lin = MixedLoraLinear(ctx, base, ads, r, dt)
+    lin.set_trainable([2, 0])
+    blen = BatchLenInfo(trains, [17], 3, [], torch.device(DEV))
+    seg = torch.cumsum(torch.tensor([0] + lens, dtype=torch.int32, device=DEV), 0, dtype=torch.int32)
+    ctx.update(blen, ids, torch.tensor(lens, dtype=torch.int32, device=DEV), seg, [2, 0])
+    xd = x.to(DEV).requires_grad_(True)
+    y = lin(xd) if path == "fused" else lin.forward_reference_ops(xd)
+    y.backward(go.to(DEV))
+    torch.cuda.synchronize()
+
+    # oracle: fp32 autograd of the same function on the rounded inputs
+    x32 = x.float().requires_grad_(True)
+    A = [w.float().requires_grad_(True) for w in was]
+    B = [w.float().requires_grad_(True) for w in wbs]
+    seg_h = np.concatenate([[0], np.cumsum(lens)])
+    outs = []
+    for i, a in enumerate(ids):
+        xs = x32[seg_h[i]:seg_h[i + 1]]
+        outs.append(xs @ wbase.float().t() + scale[a] * ((xs @ A[a].t()) @ B[a].t()))
+    y32 = torch.cat(outs)
+    # only the train rows carry gradient in the reference (grad_x is zero elsewhere,
+    # weights of non-train rows are not parameters)
+    tl = 88
+    (y32[:tl] * go.float()[:tl]).sum().backward()
+    assert_close(y, y32.detach(), what="y")
+    gx = xd.grad.float().cpu()
+    lora_gx = x32.grad[:tl] - go.float()[:tl] @ wbase.float()
+    base_gx = (go.float() @ wbase.float())
+    want_gx = base_gx.clone()
+    want_gx[:tl] += lora_gx
+    s = float(want_gx.abs().max())
+    assert_close(gx, want_gx, rtol=1e-2, atol=1e-2 * s, what="grad_x")
+    for idx in (2, 0):
+        ga = lin.get_parameter(f"lora-{idx}-A").grad
+        gb = lin.get_parameter(f"lora-{idx}-B").grad
+        assert_close(ga, A[idx].grad, rtol=1e-2, atol=1e-2 * float(A[idx].grad.abs().max()), what=f"dA{idx}")
+        assert_close(gb, B[idx].grad, rtol=1e-2, atol=1e-2 * float(B[idx].grad.abs().max()), what=f"dB{idx}")
+
+
+def test_add_lora_signature_and_return_structure():
+    from loquetier_b200.kernel_utils import add_lora
+    dt = torch.float16
+    g = torch.Generator().manual_seed(3)
+    T, h_in, h_out, r = 50, 64, 72, 8
+    x = torch.randn((T, h_in), generator=g).to(dt).to(DEV).requires_grad_(True)
+    wa = [nn.Parameter((torch.randn((r, h_in), generator=g) / 8).to(dt).to(DEV)) for _ in range(2)]
+    wb = [nn.Parameter((torch.randn((h_out, r), generator=g) * 0.1).to(dt).to(DEV)) for _ in range(2)]
+    s = torch.tensor([0, 20, 50], dtype=torch.int32, device=DEV)
+    wa_ptr = torch.tensor([w.data_ptr() for w in wa], dtype=torch.int64, device=DEV)
+    wb_ptr = torch.tensor([w.data_ptr() for w in wb], dtype=torch.int64, device=DEV)
+    y = add_lora.apply((T, h_out), x, wa_ptr, wb_ptr, s, r, 20, [0, 20], wa[0], wb[0])
+    go = torch.randn((T, h_out), generator=g).to(dt).to(DEV)
+    y.backward(go)
+    torch.cuda.synchronize()
+    assert x.grad.shape == x.shape and (x.grad[20:] == 0).all() and not (x.grad[:20] == 0).all()
+    assert wa[0].grad is not None and wb[0].grad is not None and wa[1].grad is None
+    gx, grads = O.add_lora_backward(go.cpu(), x.detach().cpu(), [wa[0].detach().cpu()], [wb[0].detach().cpu()],
+                                    [0, 20], is_row_major=False)
+    assert_close(x.grad, gx, what="grad_x")
+    assert_close(wa[0].grad, grads[0], rtol=1e-2, atol=1e-2 * float(grads[0].abs().max()) + 1e-2, what="dA")
+    assert_close(wb[0].grad, grads[1], rtol=1e-2, atol=1e-2 * float(grads[1].abs().max()) + 1e-2, what="dB")
+    # no trainable weights: backward returns None for every input
+    x2 = x.detach().clone().requires_grad_(True)
+    y2 = add_lora.apply((T, h_out), x2, wa_ptr, wb_ptr, s, r, 0, [])
+    y2.sum().backward()
+    assert x2.grad is None or (x2.grad == 0).all()

@@ -1,0 +1,275 @@
+"""GPU parity of the SMLM path against the CPU oracle, through the C ABI.
+Tolerance for 16-bit storage with fp32 accumulation: rtol 1e-2, atol 1e-2;
+bookkeeping (plans, untouched rows, determinism) is bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close, load_npz
+from oracle import smlm_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+EDGE_LENS = [0, 1, 15, 16, 17, 31, 33, 0, 64, 65, 1, 1, 127, 2]
+
+
+def _case(seed, lens, n_ad, h_in, h_out, rank, dtype, rm=False, ids=None):
+    rng = np.random.default_rng(seed)
+    ids = list(rng.integers(0, n_ad, size=len(lens))) if ids is None else ids
+    return O.make_case(seed, lens, [int(i) for i in ids], n_ad, h_in, h_out, rank, dtype, is_row_major=rm)
+
+
+# ---------------------------------------------------------------------------
+# plan
+# ---------------------------------------------------------------------------
+
+def test_plan_pieces_bit_exact():
+    from loquetier_b200 import ops
+    rng = np.random.default_rng(0)
+    for trial in range(6):
+        nseg = [1, 5, 70, 1024, 1500, 3000][trial]
+        lens = rng.integers(0, 200, size=nseg)
+        if trial == 2:
+            lens[:3] = [2048, 1024, 777]
+        seg = np.concatenate([[3], 3 + np.cumsum(lens)]).astype(np.int32)
+        T = int(seg[-1]) + 5
+        s = torch.tensor(seg, device="cuda")
+        plan = ops.Plan(s, T)
+        n, rc = plan.status()
+        assert rc == 0
+        want = []
+        for i in range(nseg):
+            a, b = int(seg[i]), int(seg[i + 1])
+            for r0 in range(a, b, 64):
+                want.append((r0, min(64, b - r0), i, 0))
+        assert n == len(want)
+        got = plan.buf[4:4 + 4 * n].cpu().view(-1, 4).tolist()
+        assert [tuple(g) for g in got] == want
+
+
+@pytest.mark.parametrize("seg", [[0, 5, 3], [-1, 4], [0, 4, 11]])
+def test_plan_rejects_bad_indptr(seg):
+    from loquetier_b200 import ops
+    plan = ops.Plan(torch.tensor(seg, dtype=torch.int32, device="cuda"), 10)
+    n, rc = plan.status()
+    assert n == 0 and rc == 7
+
+
+# ---------------------------------------------------------------------------
+# forward
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rm", [False, True])
+@pytest.mark.parametrize("rank", [8, 16, 24, 32, 64, 128])
+def test_forward_edge_lengths(dtype, rm, rank):
+    from gpu_util import check_forward
+    c = _case(100 + rank, EDGE_LENS, 5, 200, 328, rank, dtype, rm)
+    check_forward(c)
+
+
+@pytest.mark.parametrize("h_in,h_out", [(64, 64), (4096, 1024), (1000, 264), (14336, 4096), (4096, 14336)])
+def test_forward_shapes(h_in, h_out):
+    from gpu_util import check_forward
+    c = _case(7, [70, 1, 3, 130, 1, 1, 64], 4, h_in, h_out, 16, torch.bfloat16)
+    check_forward(c)
+    check_forward(c, indexed=True)
+
+
+def test_forward_scale_and_accumulate():
+    from gpu_util import check_forward
+    c = _case(8, [40, 1, 90, 17], 3, 512, 768, 16, torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    y0 = torch.randn((sum(c["lens"]), 768), generator=g).to(torch.bfloat16)
+    check_forward(c, scale=[2.0, 0.5, 1.25])
+    check_forward(c, scale=[2.0, 0.5, 1.25], indexed=True, accumulate=True, y_init=y0)
+
+
+def test_rows_outside_segments_untouched_and_deterministic():
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    c = to_dev(_case(9, [33, 1, 64], 3, 256, 384, 16, torch.float16))
+    T = 110
+    x = torch.randn((T, 256), device=dev(), dtype=torch.float16)
+    seg = torch.tensor([4, 37, 38, 102], dtype=torch.int32, device=dev())
+    plan = ops.Plan(seg, T)
+    wa = ptr_table([c["wa_d"][i] for i in c["ids"]])
+    wb = ptr_table([c["wb_d"][i] for i in c["ids"]])
+    outs = []
+    for _ in range(2):
+        y = torch.full((T, 384), 7.0, dtype=torch.float16, device=dev())
+        v = torch.full((T, 16), 3.0, dtype=torch.float16, device=dev())
+        ops.fwd(y, x, v, wa, wb, plan, 16)
+        outs.append((y.clone(), v.clone()))
+    torch.cuda.synchronize()
+    y, v = outs[0]
+    assert (y[:4] == 7).all() and (y[102:] == 7).all() and (v[:4] == 3).all() and (v[102:] == 3).all()
+    assert not (y[4:102] == 7).all()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_bad_adapter_pointer_is_reported_not_dereferenced():
+    from gpu_util import dev
+    from loquetier_b200 import ops
+    T = 20
+    x = torch.randn((T, 64), device=dev(), dtype=torch.bfloat16)
+    y = torch.zeros((T, 16), device=dev(), dtype=torch.bfloat16)
+    seg = torch.tensor([0, 20], dtype=torch.int32, device=dev())
+    plan = ops.Plan(seg, T)
+    ops.gemm(y, x, torch.tensor([0], dtype=torch.int64, device=dev()), plan)
+    n, rc = plan.status()
+    assert rc == 8 and (y == 0).all()
+    plan2 = ops.Plan(seg, T)
+    w = torch.randn((16, 64), device=dev(), dtype=torch.bfloat16)
+    ops.gemm(y, x, torch.tensor([w.data_ptr()], dtype=torch.int64, device=dev()), plan2,
+             seg_ids=torch.tensor([3], dtype=torch.int32, device=dev()))
+    assert plan2.status()[1] == 9
+
+
+def test_unsupported_shapes_raise():
+    from gpu_util import dev
+    from loquetier_b200 import ops
+    from loquetier_b200.cabi import SmlmError
+    x = torch.zeros((8, 256), device=dev(), dtype=torch.bfloat16)
+    y = torch.zeros((8, 256), device=dev(), dtype=torch.bfloat16)
+    seg = torch.tensor([0, 8], dtype=torch.int32, device=dev())
+    plan = ops.Plan(seg, 8)
+    w = torch.zeros(1, dtype=torch.int64, device=dev())
+    with pytest.raises(SmlmError, match="No suitable kernel"):
+        ops.gemm(y, x, w, plan)
+    with pytest.raises(RuntimeError, match="No suitable kernel"):
+        ops.gemm(y.float(), x.float(), w, plan)
+
+
+# ---------------------------------------------------------------------------
+# the reference's operator names
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("name", ["addlora_edges_bf16", "addlora_edges_fp16"])
+def test_reference_named_op_matches_golden(name):
+    from gpu_util import dev, ptr_table
+    from loquetier_b200 import kernels
+    z = load_npz(name)
+    h_in, h_out, r, n_ad, T = (int(v) for v in z["meta"])
+    ids, seg = z["ids"].tolist(), z["seg"].tolist()
+    wa = [z[f"wa{i}"].to(dev()) for i in range(n_ad)]
+    wb = [z[f"wb{i}"].to(dev()) for i in range(n_ad)]
+    x = z["x"].to(dev())
+    s = torch.tensor(seg, dtype=torch.int32, device=dev())
+    tmp = torch.empty(kernels.smlm_forward_cutlass_tmp_size(len(ids)), dtype=torch.uint8, device=dev())
+    v = torch.zeros((T, r), dtype=x.dtype, device=dev())
+    y = torch.zeros((T, h_out), dtype=x.dtype, device=dev())
+    kernels.smlm_forward_cutlass(v, x, ptr_table([wa[i] for i in ids]), s, tmp, False)
+    kernels.smlm_forward_cutlass(y, v, ptr_table([wb[i] for i in ids]), s, tmp, False)
+    assert_close(y[seg[0]:seg[-1]], z["y"], what="y vs reference golden")
+    assert (y[:seg[0]] == 0).all() and (y[seg[-1]:] == 0).all()
+    with pytest.raises(RuntimeError, match="CHECK_EQ"):
+        kernels.smlm_forward_cutlass(v, x, ptr_table([wa[i] for i in ids]), s, tmp[:-1], False)
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        kernels.smlm_forward_cutlass(v, x.t(), ptr_table([wa[i] for i in ids]), s, tmp, False)
+
+
+# ---------------------------------------------------------------------------
+# backward
+# ---------------------------------------------------------------------------
+
+def _run_bwd(c, part, scale=None, grad_fp32=False, accumulate=False):
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    d = to_dev(c)
+    npart = len(part) - 1
+    tl = part[-1]
+    rm = c["is_row_major"]
+    pd = torch.tensor(part, dtype=torch.int32, device=dev())
+    plan = ops.Plan(pd, tl)
+    # v from the forward over the partitions
+    wa_t, wb_t = ptr_table(d["wa_d"][:npart]), ptr_table(d["wb_d"][:npart])
+    T = d["x"].shape[0]
+    y = torch.zeros((T, c["h_out"]), dtype=c["dtype"], device=dev())
+    v = torch.zeros((T, c["rank"]), dtype=c["dtype"], device=dev())
+    ops.fwd(y, d["x"], v, wa_t, wb_t, plan, c["rank"], is_row_major=rm)
+    gdt = torch.float32 if grad_fp32 else c["dtype"]
+    init = 1.0 if accumulate else 0.0
+    dA = [torch.full_like(w, init, dtype=gdt) for w in d["wa_d"][:npart]]
+    dB = [torch.full_like(w, init, dtype=gdt) for w in d["wb_d"][:npart]]
+    dx = torch.zeros((T, c["h_in"]), dtype=c["dtype"], device=dev())
+    dv = torch.zeros((tl, c["rank"]), dtype=c["dtype"], device=dev())
+    sc = None if scale is None else torch.tensor(scale, dtype=torch.float32, device=dev())
+    ops.bwd(dx, ptr_table(dA), ptr_table(dB), dv, d["go"], d["x"], v, wa_t, wb_t, plan, c["rank"],
+            is_row_major=rm, part_scale=sc, accumulate_grads=accumulate, grad_fp32=grad_fp32)
+    torch.cuda.synchronize()
+    plan.raise_if_failed()
+    return dx.cpu(), [g.cpu() for g in dA], [g.cpu() for g in dB]
+
+
+def _oracle_bwd(c, part, scale=None):
+    npart = len(part) - 1
+    go = c["go"].to(torch.float32).clone()
+    if scale is not None:
+        for p in range(npart):
+            go[part[p]:part[p + 1]] *= scale[p]
+    gx, grads = O.add_lora_backward(go.to(torch.float32), c["x"].to(torch.float32),
+                                    [w.to(torch.float32) for w in c["wa"][:npart]],
+                                    [w.to(torch.float32) for w in c["wb"][:npart]], part,
+                                    is_row_major=c["is_row_major"], round_mid=False)
+    return gx, grads[0::2], grads[1::2]
+
+
+def _grad_close(got, want, what):
+    # gradients are sums over up to thousands of tokens: scale the absolute
+    # tolerance with the magnitude of the result
+    s = max(1.0, float(want.abs().max()))
+    assert_close(got, want, rtol=1e-2, atol=1e-2 * s, what=what)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rm", [False, True])
+@pytest.mark.parametrize("rank", [8, 16, 64])
+def test_backward_vs_oracle(dtype, rm, rank):
+    part = [0, 33, 33, 130, 131, 300]
+    c = _case(200 + rank, [310], 5, 264, 200, rank, dtype, rm, ids=[0])
+    dx, dA, dB = _run_bwd(c, part)
+    gx, gA, gB = _oracle_bwd(c, part)
+    _grad_close(dx[:300], gx[:300], "dX")
+    assert (dx[300:] == 0).all()
+    for p in range(5):
+        _grad_close(dA[p], gA[p], f"dA{p}")
+        _grad_close(dB[p], gB[p], f"dB{p}")
+
+
+def test_backward_scale_fp32_accumulate():
+    part = [0, 100, 257]
+    c = _case(300, [257], 2, 512, 320, 16, torch.bfloat16, False, ids=[0])
+    dx, dA, dB = _run_bwd(c, part, scale=[2.0, 0.5], grad_fp32=True, accumulate=True)
+    gx, gA, gB = _oracle_bwd(c, part, scale=[2.0, 0.5])
+    _grad_close(dx, gx, "dX")
+    for p in range(2):
+        assert dA[p].dtype == torch.float32
+        _grad_close(dA[p] - 1.0, gA[p], f"dA{p}")
+        _grad_close(dB[p] - 1.0, gB[p], f"dB{p}")
+
+
+@pytest.mark.parametrize("name", ["bwd_math_bf16", "bwd_math_fp16"])
+def test_backward_matches_reference_golden(name):
+    """The reference's own backward (math layout) on its own inputs."""
+    z = load_npz(name)
+    h_in, h_out, r, npart, T = (int(v) for v in z["meta"])
+    part = z["part"].tolist()
+    c = dict(x=z["x"], go=z["go"], wa=[z[f"wa{p}"] for p in range(npart)],
+             wb=[z[f"wb{p}"] for p in range(npart)], seg=[0, T], ids=[0], lens=[T], h_in=h_in, h_out=h_out,
+             rank=r, dtype=z["dtype"], is_row_major=True)
+    dx, dA, dB = _run_bwd(c, part)
+    _grad_close(dx, z["gx"], "dX")
+    for p in range(npart):
+        _grad_close(dA[p], z[f"dA{p}"], f"dA{p}")
+        _grad_close(dB[p], z[f"dB{p}"], f"dB{p}")
+
+
+def test_backward_deterministic():
+    part = [0, 700, 1500]
+    c = _case(301, [1500], 2, 1024, 512, 16, torch.bfloat16, False, ids=[0])
+    a = _run_bwd(c, part)
+    b = _run_bwd(c, part)
+    assert torch.equal(a[0], b[0])
+    for g1, g2 in zip(a[1] + a[2], b[1] + b[2]):
+        assert torch.equal(g1, g2)

@@ -1,0 +1,120 @@
+"""CPU-only checks of the host side: bookkeeping against the reference's vectors,
+property tests against the oracle, and the C-ABI library's exported symbols."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import load_bookkeeping
+from oracle import smlm_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    hdr = open(os.path.join(ROOT, "include", "smlm_b200.h")).read()
+    declared = sorted(set(re.findall(r"\b(smlm_b200_\w+)\s*\(", hdr)))
+    assert len(declared) >= 9
+    from loquetier_b200 import cabi
+    for name in declared:
+        assert hasattr(cabi.lib, name), name
+        assert name in cabi.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(cabi.SIGNATURES) == declared
+    # pure host entry points can be called without a GPU
+    assert cabi.lib.smlm_b200_version() >= 1
+    assert cabi.lib.smlm_b200_tmp_size(70) == O.smlm_tmp_size(70) == 4200
+    assert cabi.lib.smlm_b200_tmp_size(0) == 0
+    assert cabi.lib.smlm_b200_plan_bytes(8192, 100) == 16 + 16 * (8192 // 64 + 100 + 1)
+    assert cabi.lib.smlm_b200_status_string(3) == b"No suitable kernel."
+
+
+def test_argument_validation_needs_no_gpu():
+    from loquetier_b200 import cabi
+    L = cabi.lib
+    # dtype, shapes and alignment are rejected before any CUDA call
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 5, 0, 0, None) == 2
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 256, 256, 1, 0, 0, None) == 3
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 12, 1, 0, 0, None) == 3
+    assert L.smlm_b200_gemm(16, 24, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, None) == 4
+    assert L.smlm_b200_gemm(None, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, None) == 1
+    assert L.smlm_b200_gemm(None, None, None, None, None, None, 0, 0, 0, 64, 16, 1, 0, 0, None) == 0
+    assert L.smlm_b200_plan(16, 8, 16, 4, 100, None) == 5
+    assert L.smlm_b200_fwd(16, 16, 16, 16, 16, None, None, 16, 1, 8, 1, 64, 64, 130, 1, 0, 0, None) == 3
+    with pytest.raises(cabi.SmlmError, match="No suitable kernel"):
+        cabi.check(3, "x")
+
+
+def test_batch_len_info_matches_reference():
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    for row in load_bookkeeping()["batch_len_info"]:
+        c = row["case"]
+        b = BatchLenInfo([tuple(t) for t in c["trains"]], c["prefills"], c["decode"],
+                         [tuple(t) for t in c["evals"]], torch.device("cpu"))
+        assert [int(v) for v in b.train_partition] == row["train_partition"]
+        assert int(b.tlen) == row["tlen"] and int(b.doff) == row["doff"] and b.decode == row["decode"]
+        assert [int(v) for v in b.eval_partition] == row["eval_partition"]
+        assert [int(v) for v in b.prefills] == row["prefills"]
+        if row["indptr"] is None:
+            assert b.indptr is None
+        else:
+            assert b.indptr.tolist() == row["indptr"] and str(b.indptr.dtype) == row["indptr_dtype"]
+
+
+def test_segment_builder_matches_reference():
+    from loquetier_b200.enums import InferStatus
+    from loquetier_b200.segments import SegmentRequest, build_segment_batch, order_requests
+    for row in load_bookkeeping()["segments"]:
+        groups = {"train": [], "eval": [], "prefill": [], "decode": []}
+        for kind, lid, n in row["spec"]:
+            st = {"train": InferStatus.Train, "eval": InferStatus.Prefill, "prefill": InferStatus.Prefill,
+                  "decode": InferStatus.Decode}[kind]
+            groups[kind].append(SegmentRequest(st, lid, n, is_eval=(kind == "eval")))
+        ordered = order_requests(groups["train"], groups["eval"], groups["prefill"], groups["decode"])
+        sb = build_segment_batch(ordered, "cpu")
+        assert sb.lora_ids == row["lora_ids"]
+        assert sb.lora_len.tolist() == row["lora_len"] and str(sb.lora_len.dtype) == row["lora_len_dtype"]
+        assert sb.segment.tolist() == row["segment"] and str(sb.segment.dtype) == row["segment_dtype"]
+        assert sb.train_idx == row["train_idx"] and sb.n_tokens == row["n_tokens"]
+
+
+def test_segment_builder_properties():
+    hyp = pytest.importorskip("hypothesis")
+    from hypothesis import given, settings, strategies as st
+    from loquetier_b200.enums import InferStatus
+    from loquetier_b200.segments import SegmentRequest, merge_segments, order_requests
+
+    req = st.tuples(st.sampled_from(["train", "eval", "prefill", "decode"]), st.integers(0, 5), st.integers(1, 40))
+
+    @settings(max_examples=200, deadline=None)
+    @given(st.lists(req, min_size=0, max_size=40))
+    def prop(spec):
+        groups = {"train": [], "eval": [], "prefill": [], "decode": []}
+        og = {"train": [], "eval": [], "prefill": [], "decode": []}
+        for kind, lid, n in spec:
+            n = 1 if kind == "decode" else n
+            stt = {"train": InferStatus.Train, "eval": InferStatus.Prefill, "prefill": InferStatus.Prefill,
+                   "decode": InferStatus.Decode}[kind]
+            groups[kind].append(SegmentRequest(stt, lid, n))
+            og[kind].append((lid, n))
+        ordered = order_requests(groups["train"], groups["eval"], groups["prefill"], groups["decode"])
+        ids, lens = merge_segments(ordered)
+        oids, olens, oseg = O.merge_segments(O.order_requests(og["train"], og["eval"], og["prefill"], og["decode"]))
+        assert ids == oids and lens == olens
+        assert sum(lens) == sum(r.n_tokens for r in ordered)
+        assert all(a != b for a, b in zip(ids, ids[1:])) and all(n > 0 for n in lens)
+
+    prop()
+
+
+def test_prepare_weight_pads_rank_and_bakes_scale():
+    from loquetier_b200.mixed_lora import prepare_weight
+    w = torch.arange(12, dtype=torch.float32).reshape(3, 4)
+    p = prepare_weight(w, 8, torch.float32, "cpu", rank_dim=0, scaling=2.0)
+    assert p.shape == (8, 4) and torch.equal(p[:3], w * 2) and (p[3:] == 0).all()
+    q = prepare_weight(w.t().contiguous(), 8, torch.bfloat16, "cpu", rank_dim=1)
+    assert q.shape == (4, 8) and q.dtype == torch.bfloat16 and (q[:, 3:] == 0).all()
+    same = prepare_weight(w, 3, torch.float16, "cpu")
+    assert same.shape == (3, 4) and same.is_contiguous()
