@@ -172,9 +172,9 @@ class Workload:
         if self.tl:
             self.pplan = self.ops.Plan(self.part, self.tl)
 
-    # one plan per index pointer, then 2 forward and 4 backward kernels per projection
+    # one plan per index pointer, then 1 forward and 3 backward kernels per projection
     launches_per_step = property(lambda self: 1 + (1 if self.tl else 0)
-                                 + len(self.proj) * (2 + (4 if self.tl else 0)))
+                                 + len(self.proj) * (1 + (3 if self.tl else 0)))
 
     def step(self):
         """The hot path: plans once, then fused forward and backward per projection."""
@@ -282,27 +282,23 @@ def kernel_breakdown(wl, torch, reps=5):
             ops.bwd(p["dx"], p["dA_t"], p["dB_t"], p["dv"], p["go"], p["x"], p["v"], p["wa"], p["wb"], wl.pplan,
                     r, part_ids=wl.part_ids, part_scale=wl.scale)
     classes = {
-        "shrink_kernel(fwd v=x.A^T)": (
-            lambda p: ops.gemm(p["v"], p["x"], p["wa"], wl.plan, seg_ids=wl.ids),
-            lambda p: e * (T * p["h_in"] + T * r + used * r * p["h_in"])),
-        "expand_kernel(fwd y=s.v.B^T)": (
-            lambda p: ops.gemm(p["y"], p["v"], p["wb"], wl.plan, seg_ids=wl.ids, seg_scale=wl.scale),
-            lambda p: e * (T * p["h_out"] + T * r + used * r * p["h_out"])),
+        "fused_kernel(fwd x->v->y)": (
+            lambda p: ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids,
+                              seg_scale=wl.scale),
+            lambda p: e * (T * p["h_in"] + T * p["h_out"] + T * r + used * r * (p["h_in"] + p["h_out"]))),
     }
     if n:
         classes.update({
-            "shrink_kernel(bwd dV=gO.B)": (
-                lambda p: ops.gemm(p["dv"], p["go"], p["wb"], wl.pplan, is_row_major=True, seg_ids=wl.part_ids,
-                                   seg_scale=wl.scale),
-                lambda p: e * (n * p["h_out"] + n * r + used_ft * r * p["h_out"])),
+            # the backward's fused launch is the same kernel with the roles of the panels swapped
+            "fused_kernel(bwd gO->dV->dX)": (
+                lambda p: ops.fwd(p["dx"], p["go"], p["dv"], p["wb"], p["wa"], wl.pplan, r, is_row_major=True,
+                                  seg_ids=wl.part_ids, seg_scale=wl.scale),
+                lambda p: e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
             "wgrad_kernel(dB=gO^T.V)": (
                 lambda p: ops.wgrad(p["dB_t"], p["v"], p["go"], wl.part, wl.pplan, transposed=True),
                 lambda p: e * (n * p["h_out"] + n * r + used_ft * r * p["h_out"])),
             "wgrad_kernel(dA=dV^T.X)": (
                 lambda p: ops.wgrad(p["dA_t"], p["dv"], p["x"], wl.part, wl.pplan, transposed=False),
-                lambda p: e * (n * p["h_in"] + n * r + used_ft * r * p["h_in"])),
-            "expand_kernel(bwd dX=dV.A)": (
-                lambda p: ops.gemm(p["dx"], p["dv"], p["wa"], wl.pplan, is_row_major=True, seg_ids=wl.part_ids),
                 lambda p: e * (n * p["h_in"] + n * r + used_ft * r * p["h_in"])),
         })
     out = {}

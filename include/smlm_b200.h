@@ -41,7 +41,8 @@ enum {
   SMLM_ERR_CUDA = 6,             /* the CUDA runtime rejected a launch */
   SMLM_ERR_BAD_INDPTR = 7,       /* reported by smlm_b200_plan_status */
   SMLM_ERR_BAD_POINTER = 8,      /* reported by smlm_b200_plan_status */
-  SMLM_ERR_BAD_INDEX = 9         /* reported by smlm_b200_plan_status */
+  SMLM_ERR_BAD_INDEX = 9,        /* reported by smlm_b200_plan_status */
+  SMLM_ERR_TIMEOUT = 10          /* reported by smlm_b200_plan_status: a bounded wait in a kernel gave up */
 };
 
 enum { SMLM_F16 = 0, SMLM_BF16 = 1 };

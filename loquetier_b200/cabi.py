@@ -18,7 +18,7 @@ SMLM_BF16 = 1
 STATUS_NAMES = {
     0: "SMLM_OK", 1: "SMLM_ERR_INVALID_ARGUMENT", 2: "SMLM_ERR_DTYPE", 3: "SMLM_ERR_NO_KERNEL",
     4: "SMLM_ERR_MISALIGNED", 5: "SMLM_ERR_WORKSPACE", 6: "SMLM_ERR_CUDA", 7: "SMLM_ERR_BAD_INDPTR",
-    8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX",
+    8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX", 10: "SMLM_ERR_TIMEOUT",
 }
 
 # name -> (restype, argtypes); mirrors include/smlm_b200.h one to one

@@ -1,11 +1,13 @@
 // C ABI of the SMLM path: argument checks, kernel selection and launches.
 // Declarations and the reference interfaces they stand in for: include/smlm_b200.h.
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <algorithm>
 
 #include "../../include/smlm_b200.h"
 #include "smlm_expand.cuh"
+#include "smlm_fused.cuh"
 #include "smlm_plan.cuh"
 #include "smlm_shrink.cuh"
 #include "smlm_wgrad.cuh"
@@ -14,7 +16,44 @@ namespace {
 
 using namespace smlm;
 
-constexpr int kTargetCtas = 148 * 4;  // aim for four resident CTAs on each of the 148 SMs
+constexpr int kNumSMs = 148;
+constexpr int kTargetCtas = 148 * 2;  // aim for at least two resident CTAs on each of the 148 SMs
+
+// ---- tensor maps ------------------------------------------------------------
+// cuTensorMapEncodeTiled is a host-only driver routine; it is looked up through the
+// runtime on first use so that the library itself does not link against libcuda.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess) {
+      cudaGetLastError();
+      p = nullptr;
+    }
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Row-major [rows, cols] matrix of 16-bit elements, boxes of [box_rows, 64] elements
+// (128 bytes wide) stored with the 128-byte swizzle; out-of-range parts read as zero.
+bool make_map_2d(CUtensorMap* m, const void* base, int rows, int cols, int box_rows, int dtype) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * 2};
+  const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(m, dtype == SMLM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+            const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -35,8 +74,9 @@ inline int pick_split(int work_items, int stages_total) {
   return std::max(ks, 1);
 }
 
-template <typename Kern, typename Args>
-int launch(Kern kern, dim3 grid, int cluster_x, int smem_bytes, cudaStream_t stream, const Args& args) {
+template <typename Kern, typename... Args>
+int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cudaStream_t stream,
+           const Args&... args) {
   if (grid.x == 0 || grid.y == 0) return SMLM_OK;
   if (smem_bytes > 48 * 1024) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
@@ -46,7 +86,7 @@ int launch(Kern kern, dim3 grid, int cluster_x, int smem_bytes, cudaStream_t str
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.blockDim = dim3(threads, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -56,7 +96,7 @@ int launch(Kern kern, dim3 grid, int cluster_x, int smem_bytes, cudaStream_t str
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  if (cudaLaunchKernelEx(&cfg, kern, args) != cudaSuccess) {
+  if (cudaLaunchKernelEx(&cfg, kern, args...) != cudaSuccess) {
     cudaGetLastError();
     return SMLM_ERR_CUDA;
   }
@@ -66,19 +106,19 @@ int launch(Kern kern, dim3 grid, int cluster_x, int smem_bytes, cudaStream_t str
 // ---- shrink -----------------------------------------------------------------
 
 template <typename T, int NT, bool RM>
-int launch_shrink(const ShrinkArgs& a, int max_pieces, cudaStream_t stream) {
-  return launch(shrink_kernel<T, NT, RM>, dim3(max_pieces * a.ksplit, 1, 1), a.ksplit,
-                ShrinkSmem<NT, RM>::kTotal, stream, a);
+int launch_shrink(const ShrinkArgs& a, const XMaps& xm, int max_pieces, cudaStream_t stream) {
+  return launch(shrink_kernel<T, NT, RM>, dim3(max_pieces * a.ksplit, 1, 1), kShrinkThreads, a.ksplit,
+                ShrinkSmem<NT, RM>::kTotal, stream, a, xm);
 }
 
 template <typename T, bool RM>
-int dispatch_shrink_nt(const ShrinkArgs& a, int max_pieces, cudaStream_t stream) {
+int dispatch_shrink_nt(const ShrinkArgs& a, const XMaps& xm, int max_pieces, cudaStream_t stream) {
   const int nt = (a.N + 7) / 8;
-  if (nt <= 1) return launch_shrink<T, 1, RM>(a, max_pieces, stream);
-  if (nt <= 2) return launch_shrink<T, 2, RM>(a, max_pieces, stream);
-  if (nt <= 4) return launch_shrink<T, 4, RM>(a, max_pieces, stream);
-  if (nt <= 8) return launch_shrink<T, 8, RM>(a, max_pieces, stream);
-  return launch_shrink<T, 16, RM>(a, max_pieces, stream);
+  if (nt <= 1) return launch_shrink<T, 1, RM>(a, xm, max_pieces, stream);
+  if (nt <= 2) return launch_shrink<T, 2, RM>(a, xm, max_pieces, stream);
+  if (nt <= 4) return launch_shrink<T, 4, RM>(a, xm, max_pieces, stream);
+  if (nt <= 8) return launch_shrink<T, 8, RM>(a, xm, max_pieces, stream);
+  return launch_shrink<T, 16, RM>(a, xm, max_pieces, stream);
 }
 
 int run_shrink(void* d, const void* x, const void* const* w_table, const int32_t* ids, const float* scale,
@@ -90,18 +130,21 @@ int run_shrink(void* d, const void* x, const void* const* w_table, const int32_t
   a.n_table = n_table; a.N = N; a.K = K;
   const int mp = max_pieces_of(T, nseg);
   a.ksplit = pick_split(mp, (K + kKC - 1) / kKC);
+  XMaps xm;
+  for (int i = 0; i < 4; ++i)
+    if (!make_map_2d(&xm.m[i], x, T, K, 8 << i, dtype)) return SMLM_ERR_CUDA;
   if (dtype == SMLM_F16)
-    return row_major ? dispatch_shrink_nt<__half, true>(a, mp, stream)
-                     : dispatch_shrink_nt<__half, false>(a, mp, stream);
-  return row_major ? dispatch_shrink_nt<__nv_bfloat16, true>(a, mp, stream)
-                   : dispatch_shrink_nt<__nv_bfloat16, false>(a, mp, stream);
+    return row_major ? dispatch_shrink_nt<__half, true>(a, xm, mp, stream)
+                     : dispatch_shrink_nt<__half, false>(a, xm, mp, stream);
+  return row_major ? dispatch_shrink_nt<__nv_bfloat16, true>(a, xm, mp, stream)
+                   : dispatch_shrink_nt<__nv_bfloat16, false>(a, xm, mp, stream);
 }
 
 // ---- expand -----------------------------------------------------------------
 
 template <typename T, int KT, bool RM>
 int launch_expand(const ExpandArgs& a, int max_pieces, cudaStream_t stream) {
-  return launch(expand_kernel<T, KT, RM>, dim3(max_pieces, (a.N + kNCH - 1) / kNCH, 1), 1,
+  return launch(expand_kernel<T, KT, RM>, dim3(max_pieces, (a.N + kNCH - 1) / kNCH, 1), kThreads, 1,
                 ExpandSmem<KT>::kTotal, stream, a);
 }
 
@@ -129,12 +172,67 @@ int run_expand(void* d, const void* x, const void* const* w_table, const int32_t
                    : dispatch_expand_kt<__nv_bfloat16, false>(a, mp, stream);
 }
 
+// ---- fused shrink + expand ----------------------------------------------------
+
+template <typename T, int R16, bool RM>
+int launch_fused(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cudaStream_t stream) {
+  return launch(fused_kernel<T, R16, RM>, dim3(max_pieces * a.ksplit, 1, 1), kFusedThreads, a.ksplit,
+                FusedSmem<R16, RM>::kTotal, stream, a, tm);
+}
+
+template <typename T, bool RM>
+int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cudaStream_t stream) {
+  const int r16 = (a.R + 15) / 16;
+  if (r16 <= 1) return launch_fused<T, 1, RM>(a, tm, max_pieces, stream);
+  if (r16 <= 2) return launch_fused<T, 2, RM>(a, tm, max_pieces, stream);
+  if (r16 <= 4) return launch_fused<T, 4, RM>(a, tm, max_pieces, stream);
+  return launch_fused<T, 8, RM>(a, tm, max_pieces, stream);
+}
+
+// OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
+int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
+              const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
+              int N2, int dtype, int row_major, int scale_mid, int accumulate, cudaStream_t stream) {
+  FusedArgs a;
+  a.out = out; a.mid = mid; a.w1_table = w1_table; a.w2_table = w2_table; a.ids = ids; a.scale = scale;
+  a.plan = static_cast<int*>(plan);
+  a.n_table = n_table; a.K1 = K1; a.R = R; a.N2 = N2; a.scale_mid = scale_mid; a.accumulate = accumulate;
+  const int mp = max_pieces_of(T, nseg);
+  // One CTA per SM.  A piece can be split over the KS CTAs of a cluster; pick the KS that
+  // minimises (waves of 148 CTAs) x (work per CTA + fixed cost of set-up and the cluster reduce).
+  const int r16b = (R + 15) / 16;
+  const int r16 = r16b > 4 ? 8 : (r16b > 2 ? 4 : r16b);
+  const int kc = 64 * fused_chunks(r16);
+  const int ksteps = (K1 + kc - 1) / kc, nslabs = (N2 + fused_slab(r16) - 1) / fused_slab(r16);
+  int ks = 1;
+  double best = 1e30;
+  for (int k = 1; k <= 8; ++k) {
+    if (k > 1 && (ksteps < k || nslabs < k)) break;
+    const int waves = (std::max(mp, 1) * k + kNumSMs - 1) / kNumSMs;
+    const double cost = waves * (1.0 / k + (k > 1 ? 0.15 : 0.08));
+    if (cost < best - 1e-9) {
+      best = cost;
+      ks = k;
+    }
+  }
+  a.ksplit = ks;
+  FusedMaps tm;
+  if (!make_map_2d(&tm.in8, in, T, K1, 8, dtype) || !make_map_2d(&tm.in16, in, T, K1, 16, dtype) ||
+      !make_map_2d(&tm.out, out, T, N2, 16, dtype))
+    return SMLM_ERR_CUDA;
+  if (dtype == SMLM_F16)
+    return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, stream)
+                     : dispatch_fused_r<__half, false>(a, tm, mp, stream);
+  return row_major ? dispatch_fused_r<__nv_bfloat16, true>(a, tm, mp, stream)
+                   : dispatch_fused_r<__nv_bfloat16, false>(a, tm, mp, stream);
+}
+
 // ---- wgrad ------------------------------------------------------------------
 
 template <typename T, int RT>
 int launch_wgrad(const WgradArgs& a, cudaStream_t stream) {
-  return launch(wgrad_kernel<T, RT>, dim3(a.npart * a.ksplit, (a.H + kWgCols - 1) / kWgCols, 1), a.ksplit,
-                WgradSmem<RT>::kTotal, stream, a);
+  return launch(wgrad_kernel<T, RT>, dim3(a.npart * a.ksplit, (a.H + kWgCols - 1) / kWgCols, 1), kThreads,
+                a.ksplit, WgradSmem<RT>::kTotal, stream, a);
 }
 
 template <typename T>
@@ -181,6 +279,7 @@ const char* smlm_b200_status_string(int status) {
     case SMLM_ERR_BAD_INDPTR: return "segment index pointer is not monotone within [0, T]";
     case SMLM_ERR_BAD_POINTER: return "adapter pointer is null or not 16-byte aligned";
     case SMLM_ERR_BAD_INDEX: return "adapter index outside the table";
+    case SMLM_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
     default: return "unknown status";
   }
 }
@@ -218,6 +317,7 @@ int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream) {
   if (hdr[1] & kErrBadIndptr) return SMLM_ERR_BAD_INDPTR;
   if (hdr[1] & kErrBadIndex) return SMLM_ERR_BAD_INDEX;
   if (hdr[1] & kErrBadPointer) return SMLM_ERR_BAD_POINTER;
+  if (hdr[1] & kErrTimeout) return SMLM_ERR_TIMEOUT;
   return SMLM_OK;
 }
 
@@ -252,12 +352,8 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc = run_shrink(v, x, wa_table, seg_ids, nullptr, plan, n_table, T, nseg, h_in, rank, dtype, is_row_major,
-                      st);
-  if (rc != SMLM_OK) return rc;
-  return run_expand(y, v, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, rank, h_out, dtype,
-                    is_row_major, accumulate, st);
+  return run_fused(y, v, x, wa_table, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, h_in, rank, h_out,
+                   dtype, is_row_major, /*scale_mid=*/0, accumulate, static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
@@ -294,8 +390,9 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a
   // row-major [K = h_out][N = r] operand; the math layout B [r, h_out] is the
   // column-major one.  The layout flag therefore flips for both backward GEMMs.
-  int rc = run_shrink(dv, go, wb_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank, dtype,
-                      !is_row_major, st);
+  // and dX = dV . A in the same launch.
+  int rc = run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
+                     h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, st);
   if (rc != SMLM_OK) return rc;
   // dB = scale * gO^T . V : [h_out, r] in the PEFT layout (transposed store)
   rc = run_wgrad(dB_table, v, go, part_indptr, part_scale, part_ids, n_table, err, npart, T, rank, h_out, dtype,
@@ -304,10 +401,7 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   // dA = dV^T . X : [r, h_in] in the PEFT layout
   rc = run_wgrad(dA_table, dv, x, part_indptr, nullptr, nullptr, 0, err, npart, T, rank, h_in, dtype,
                  is_row_major ? 1 : 0, accumulate_grads, grad_fp32, st);
-  if (rc != SMLM_OK) return rc;
-  // dX = dV . A
-  return run_expand(dx, dv, wa_table, part_ids, nullptr, plan, n_table, T, npart, rank, h_in, dtype,
-                    !is_row_major, 0, st);
+  return rc;
 }
 
 }  // extern "C"

@@ -20,6 +20,7 @@ constexpr int kPlanHeaderInts = 4;  // {count, error, max_pieces, T}
 constexpr int kErrBadIndptr = 1;    // indptr not monotone, negative or beyond T
 constexpr int kErrBadPointer = 2;   // an adapter pointer is null or not 16-byte aligned
 constexpr int kErrBadIndex = 4;     // an adapter index outside the table
+constexpr int kErrTimeout = 8;      // a bounded wait on a shared-memory barrier ran out
 
 struct __align__(16) Piece {
   int row0;   // first token row
@@ -174,6 +175,97 @@ __device__ __forceinline__ float adapter_scale(const float* scale, const int32_t
     if (idx < 0 || idx >= n_table) return 0.0f;
   }
   return scale[idx];
+}
+
+// ---------------------------------------------------------------------------
+// mbarrier + TMA (bulk asynchronous copies).  Every CTA fetches its own tiles; no
+// copy is shared between CTAs.
+// ---------------------------------------------------------------------------
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after kWaitLimit polls (each poll already suspends the
+// thread for a hardware-defined interval), records kErrTimeout and lets the caller
+// run to completion instead of hanging the GPU.
+constexpr int kWaitLimit = 1 << 18;
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* err, bool& dead) {
+  if (dead) return false;
+  for (int i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  dead = true;
+  atomicOr(err, kErrTimeout);
+  return false;
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+}
+// 2-D tiled TMA load: box at element coordinates (x = innermost, y = row)
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+      ::"r"(dst), "l"(tmap), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+// untiled bulk load: 16-byte aligned addresses, size a multiple of 16
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_store_2d(const void* tmap, int x, int y, uint32_t src) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];\n"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+template <typename T>
+__device__ __forceinline__ void tma_reduce_add_2d(const void* tmap, int x, int y, uint32_t src);
+template <>
+__device__ __forceinline__ void tma_reduce_add_2d<__half>(const void* tmap, int x, int y, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%1, %2}], [%3];\n"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+template <>
+__device__ __forceinline__ void tma_reduce_add_2d<__nv_bfloat16>(const void* tmap, int x, int y, uint32_t src) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%1, %2}], [%3];\n"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(src)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void stsm_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+  asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};\n"
+               ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)
+               : "memory");
 }
 
 }  // namespace smlm

@@ -1,0 +1,478 @@
+// Fused segmented LoRA product  OUT[rows, N2] (+)= s2 * round(s1 * IN[rows, K1] . W1_seg) . W2_seg
+// for every piece (<= 64 rows of one segment): a shrink through the rank-R
+// bottleneck followed at once by the expand, in one kernel, with the rank-R
+// intermediate MID also written out in the storage type.
+//
+//   forward : IN = x,  W1 = A, W2 = B, MID = v,  OUT = y   (the two operator calls of
+//             add_lora.forward, src/loquetier_src/kernel_utils.py:114-120, plus the
+//             scale and add of MixedLoraLinear.forward, models/mixed_lora.py:214-217)
+//   backward: IN = gO, W1 = B, W2 = A, MID = dV, OUT = dX  (kernel_utils.py:142-143)
+//
+// It replaces two launches of the reference's grouped GEMM
+// (kernel_src/csrc/smlm_forward/smlm_forward_cutlass.cuh:82-171) and keeps its
+// numerics: fp32 accumulation, MID rounded to the storage type before the second
+// product.
+//
+// One CTA per SM; one cluster of KS CTAs owns one piece.
+// Phase 1 - the HBM-bound read.  Every CTA streams its slice of the K1 columns of IN
+//   through a ring of large shared-memory stages fed by a producer warp with TMA.
+//   A stage holds 64 rows x (64*CH) columns, fetched as [16 rows x 64 columns] tiled
+//   tensor copies (128-byte swizzle) issued row block by row block, so that each
+//   row's consecutive 128-byte chunks - up to 1 KB - are requested together and DRAM
+//   pages are used whole; the W1 panel slice arrives as untiled bulk copies from its
+//   raw pointer.  Eight consumer warps run ldmatrix + mma.sync m16n8k16.
+// Phase 2.  The CTAs of the cluster add their partial sums through distributed
+//   shared memory in a fixed order (deterministic; no global scratch, no atomics);
+//   every CTA ends up with the whole MID tile.
+// Phase 3 - the HBM-bound write.  Every CTA expands MID against its slice of the N2
+//   columns, one slab at a time (W2 slab double-buffered with 16-byte cp.async), and
+//   each warp hands finished 16 x 128 blocks to TMA as tensor stores - or tensor
+//   reduce-adds when accumulating into OUT.
+#pragma once
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "smlm_common.cuh"
+
+namespace smlm {
+
+namespace cg = cooperative_groups;
+
+constexpr int kFusedConsumers = 8;                           // consumer warps
+constexpr int kFusedThreads = (kFusedConsumers + 1) * 32;    // + one producer warp
+constexpr int kFusedCThreads = kFusedConsumers * 32;
+
+#ifndef SMLM_FUSED_CH
+#define SMLM_FUSED_CH 8
+#endif
+// 64-column chunks of IN per ring stage; high ranks trade width for panel space
+constexpr int fused_chunks(int r16) { return r16 >= 8 ? 2 : (r16 == 4 ? 4 : SMLM_FUSED_CH); }
+constexpr int fused_stages(int) { return 2; }
+constexpr int fused_slab(int r16) { return r16 >= 8 ? 128 : (r16 == 4 ? 256 : 1024); }
+
+struct FusedMaps {
+  CUtensorMap in8;    // IN boxes of 8 rows x 64 columns (pieces of at most 8 rows)
+  CUtensorMap in16;   // IN boxes of 16 rows x 64 columns
+  CUtensorMap out;    // OUT boxes of 16 rows x 64 columns
+};
+
+template <int R16, bool RM>
+struct FusedSmem {
+  static constexpr int NT = R16 * 2;            // n-tiles of 8 in the shrink
+  static constexpr int KP = R16 * 16;           // padded rank
+  static constexpr int CH = fused_chunks(R16);
+  static constexpr int KC = 64 * CH;            // K1 columns per ring stage
+  static constexpr int WPad = KC * 2 + 16;      // bytes between W1 rows in shared memory ([R][K1] layout)
+  static constexpr int kStages = fused_stages(R16);
+  static constexpr int kXBytes = kBM * KC * 2;  // 4 row blocks x CH column chunks of [16][64]
+  static constexpr int kW1Raw = RM ? KC * KP * 2 : KP * WPad;
+  static constexpr int kW1Bytes = (kW1Raw + 1023) / 1024 * 1024;
+  static constexpr int kStage = kXBytes + kW1Bytes;
+  static constexpr int kRing = kStages * kStage;
+  // phase 3 lives in the space of the ring: two W2 slabs, then per warp two 16 x 128 staging blocks
+  static constexpr int SLAB = fused_slab(R16);
+  static constexpr int kW2Slab = SLAB * KP * 2;
+  static constexpr int kOutOff = 2 * kW2Slab;
+  static constexpr int kStageOut = kFusedConsumers * 2 * 4096;
+  static constexpr int kPhase3 = kOutOff + kStageOut;
+  static constexpr int kUnion = kRing > kPhase3 ? kRing : kPhase3;
+  static constexpr int kRedOff = kUnion;
+  static constexpr int kRed = kFusedConsumers * 16 * KP * 4;   // one 16 x KP fp32 block per consumer warp
+  static constexpr int kMidOff = kRedOff + kRed;
+  static constexpr int kMid = kBM * KP * 2;
+  static constexpr int kBarOff = kMidOff + kMid;
+  static constexpr int kTotal = kBarOff + 2 * kStages * 8 + 1024;  // + alignment slack
+  static_assert(kTotal <= 227 * 1024, "shared memory budget");
+  static_assert(kW2Slab % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+};
+
+struct FusedArgs {
+  void* out;                    // [T, N2]
+  void* mid;                    // [T, R]
+  const void* const* w1_table;  // shrink panels
+  const void* const* w2_table;  // expand panels
+  const int32_t* ids;           // per-segment adapter index, or null: tables are per segment
+  const float* scale;           // per adapter (ids != null) or per segment, or null
+  int* plan;
+  int n_table;
+  int K1, R, N2;
+  int ksplit;
+  int scale_mid;                // 1: the scale multiplies MID (backward); 0: it multiplies OUT (forward)
+  int accumulate;               // OUT += instead of OUT =
+};
+
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+
+template <typename T, int R16, bool RM>
+__global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs a,
+                                                                const __grid_constant__ FusedMaps tm) {
+  extern __shared__ unsigned char smem_raw[];
+  using SM = FusedSmem<R16, RM>;
+  constexpr int NT = SM::NT;
+  constexpr int KP = SM::KP;
+  constexpr int S = SM::kStages;
+  constexpr int CH = SM::CH;
+  constexpr int KC = SM::KC;
+  constexpr int WPad = SM::WPad;
+  constexpr int SLAB = SM::SLAB;
+  constexpr int XC = R16 * 2;  // 16-byte chunks per MID row
+  constexpr int NW = kFusedConsumers;
+  const int tid = threadIdx.x;
+  const int lane = tid & 31;
+  const int warp = tid >> 5;
+  const int KS = a.ksplit;
+  const int piece_idx = blockIdx.x / KS;
+  const int z = blockIdx.x - piece_idx * KS;
+
+  const int count = a.plan[0];
+  const Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[piece_idx];
+  if (piece_idx >= count) return;  // the whole cluster leaves together
+  const int nrows = pc.nrows;
+  const int K1 = a.K1, R = a.R, N2 = a.N2;
+  int* err = a.plan + 1;
+
+  const T* w1 = static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
+  const T* w2 = static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
+  const bool w_ok = (w1 != nullptr) && (w2 != nullptr);
+  const float sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
+  const float sc_mid = a.scale_mid ? sc : 1.0f;
+  const float sc_out = a.scale_mid ? 1.0f : sc;
+
+  const int ksteps = (K1 + KC - 1) / KC;
+  const int per = (ksteps + KS - 1) / KS;
+  const int kbeg = z * per;
+  const int nk = w_ok ? max(0, min(ksteps, kbeg + per) - kbeg) : 0;
+
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  unsigned char* smem = smem_raw + (base - raw);
+  const uint32_t full0 = base + SM::kBarOff;
+  const uint32_t empty0 = full0 + S * 8;
+
+  if (tid == 0) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      mbar_init(full0 + s * 8, 1);
+      mbar_init(empty0 + s * 8, NW);
+    }
+    fence_mbar_init();
+  }
+  if ((K1 % 64) != 0) {
+    // the last 64-column chunk is only partly overwritten by the panel copies: start from zeros so
+    // that the columns past K1 (which IN supplies as zeros) never meet a non-finite leftover
+    for (int s = 0; s < S; ++s) {
+      uint4* wz = reinterpret_cast<uint4*>(smem + s * SM::kStage + SM::kXBytes);
+      for (int i = tid; i < SM::kW1Bytes / 16; i += kFusedThreads) wz[i] = make_uint4(0, 0, 0, 0);
+    }
+    fence_proxy_async();
+  }
+  __syncthreads();
+
+  // consumer warp roles: WM row blocks of 16, WK ways along K (phase 1) or along N2 (phase 3)
+  const int WM = nrows <= 16 ? 1 : (nrows <= 32 ? 2 : 4);
+  const int WK = NW / WM;
+  const int wm = warp % WM;
+  const int wk = warp / WM;
+  bool dead = false;
+
+  // ======================= phase 1: shrink over this CTA's K1 slice =======================
+  float acc[NT][4];
+#pragma unroll
+  for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+  if (warp == NW) {
+    const bool small = nrows <= 8;
+    const CUtensorMap* xmap = small ? &tm.in8 : &tm.in16;
+    const uint32_t boxbytes = small ? 1024u : 2048u;
+    const int nblk = small ? 1 : ((nrows + 15) >> 4);
+    for (int it = 0; it < nk; ++it) {
+      const int slot = it % S;
+      const int k0 = (kbeg + it) * KC;
+      const uint32_t xs = base + slot * SM::kStage;
+      const uint32_t ws = xs + SM::kXBytes;
+      const uint32_t fb = full0 + slot * 8;
+      if (it >= S) mbar_wait(empty0 + slot * 8, ((it / S) - 1) & 1, err, dead);
+      const int kcols = min(KC, K1 - k0);
+      const int nch = (kcols + 63) >> 6;
+      const uint32_t wbytes = static_cast<uint32_t>(kcols) * R * 2;
+      if (lane == 0) mbar_expect_tx(fb, boxbytes * nblk * nch + wbytes);
+      __syncwarp();
+      if constexpr (!RM) {
+        for (int n = lane; n < R; n += 32)
+          bulk_load(ws + n * WPad, w1 + static_cast<size_t>(n) * K1 + k0, kcols * 2, fb);
+      } else {
+        if (lane == 0) bulk_load(ws, w1 + static_cast<size_t>(k0) * R, wbytes, fb);
+      }
+      for (int i = lane; i < nblk * nch; i += 32) {
+        const int b = i / nch, c = i - b * nch;
+        tma_load_2d(xs + (b * CH + c) * 2048, xmap, k0 + c * 64, pc.row0 + b * 16, fb);
+      }
+    }
+  } else {
+    const bool active = (wm * 16 < nrows);
+    for (int it = 0; it < nk; ++it) {
+      const int slot = it % S;
+      const uint32_t xs = base + slot * SM::kStage;
+      const uint32_t ws = xs + SM::kXBytes;
+      mbar_wait(full0 + slot * 8, (it / S) & 1, err, dead);
+      if (active) {
+        const int kmax = (min(KC, K1 - (kbeg + it) * KC) + 15) >> 4;
+        for (int kk = wk; kk < kmax; kk += WK) {
+          uint32_t af[4];
+          {
+            const int m = lane >> 3;
+            const int r = (m & 1) * 8 + (lane & 7);
+            const int c = (kk & 3) * 2 + (m >> 1);
+            ldsm_x4(af, xs + (wm * CH + (kk >> 2)) * 2048 + r * 128 + ((c ^ (r & 7)) << 4));
+          }
+#pragma unroll
+          for (int j = 0; j < NT; j += 2) {
+            uint32_t bf[4];
+            const int m = lane >> 3;
+            if constexpr (!RM) {
+              const int n = (j + (m >> 1)) * 8 + (lane & 7);
+              ldsm_x4(bf, ws + n * WPad + ((kk * 2 + (m & 1)) << 4));
+            } else {
+              // panel stored [K1][R] with rows of R elements, exactly as in global memory
+              const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
+              ldsm_x4_t(bf, ws + k * (R * 2) + ((j + (m >> 1)) << 4));
+            }
+            mma16816<T>(acc[j], af, bf[0], bf[1]);
+            mma16816<T>(acc[j + 1], af, bf[2], bf[3]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty0 + slot * 8);
+    }
+  }
+
+  // ======================= phase 2: reduce the K1 slices, build MID =======================
+  float* red = reinterpret_cast<float*>(smem + SM::kRedOff);  // [warp][16][KP]
+  if (warp < NW) {
+    const int g = lane >> 2, t = lane & 3;
+    float* my = red + warp * 16 * KP;
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+      *reinterpret_cast<float2*>(my + g * KP + j * 8 + 2 * t) = make_float2(acc[j][0], acc[j][1]);
+      *reinterpret_cast<float2*>(my + (g + 8) * KP + j * 8 + 2 * t) = make_float2(acc[j][2], acc[j][3]);
+    }
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  if (KS > 1) {
+    cluster_arrive();
+    cluster_wait();
+  } else {
+    __syncthreads();
+  }
+
+  const uint32_t mids = base + SM::kMidOff;  // MID tile [64][KP] in the storage type, swizzled rows
+  {
+    const int load_rows = min(kBM, ((nrows + 15) >> 4) << 4);
+    T* mrow = static_cast<T*>(a.mid) + static_cast<size_t>(pc.row0) * R;
+    constexpr int HP = KP / 2;
+    for (int e = tid; e < load_rows * HP; e += kFusedThreads) {
+      const int r = e / HP;
+      const int n = (e - r * HP) * 2;
+      const int fm = r >> 4, r16 = r & 15;
+      float2 s = make_float2(0.f, 0.f);
+      if (r < nrows && n < R && w_ok) {
+        for (int cz = 0; cz < KS; ++cz) {
+          const float* rr = KS > 1 ? cluster.map_shared_rank(red, cz) : red;
+          for (int q = 0; q < WK; ++q) {
+            const float2 p = *reinterpret_cast<const float2*>(rr + ((q * WM + fm) * 16 + r16) * KP + n);
+            s.x += p.x;
+            s.y += p.y;
+          }
+        }
+      }
+      const uint32_t packed = pack2<T>(s.x * sc_mid, s.y * sc_mid);
+      const int c = n >> 3;
+      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(mids + r * (XC * 16) + (swz<XC>(r, c) << 4) + (n & 7) * 2),
+                   "r"(packed));
+      if (z == 0 && r < nrows && n < R && w_ok)
+        *reinterpret_cast<uint32_t*>(mrow + static_cast<size_t>(r) * R + n) = packed;
+    }
+  }
+  // done reading the peers' partial sums; the matching wait sits at the very end, so that no CTA
+  // leaves (and frees its shared memory) while a peer may still be reading it
+  if (KS > 1) cluster_arrive();
+  __syncthreads();  // MID is complete; the ring is free for phase 3
+
+  // ======================= phase 3: expand over this CTA's N2 slice =======================
+  const int nslabs = (N2 + SLAB - 1) / SLAB;
+  const int sper = (nslabs + KS - 1) / KS;
+  const int sbeg = z * sper;
+  const int ns = w_ok ? max(0, min(nslabs, sbeg + sper) - sbeg) : 0;
+
+  if (warp < NW && ns > 0) {
+    const uint32_t wslab0 = base;  // two slabs in the space the ring occupied
+    const int kchunks = R >> 3;
+    const int ctid = tid;          // consumer threads are 0 .. kFusedCThreads-1
+
+    auto load_slab = [&](int buf, int slab) {
+      const int n0 = slab * SLAB;
+      const int ncols = min(SLAB, N2 - n0);
+      const uint32_t ws = wslab0 + buf * SM::kW2Slab;
+      if constexpr (!RM) {
+        // W2 stored [N2][R]: the slab is one contiguous block of global memory
+        for (int i = ctid; i < ncols * XC; i += kFusedCThreads) {
+          const int n = i / XC, c = i - n * XC;
+          const bool ok = c < kchunks;
+          const T* src = ok ? (w2 + static_cast<size_t>(n0 + n) * R + c * 8) : w2;
+          cp_async16(ws + n * (XC * 16) + (swz<XC>(n, c) << 4), src, ok);
+        }
+      } else {
+        // W2 stored [R][N2]: KP rows of SLAB/8 chunks
+        constexpr int CPR = SLAB / 8;
+        const int cvalid = ncols >> 3;
+        for (int i = ctid; i < KP * CPR; i += kFusedCThreads) {
+          const int k = i / CPR, c = i - k * CPR;
+          if (c >= cvalid) continue;
+          const bool ok = k < R;
+          const T* src = ok ? (w2 + static_cast<size_t>(k) * N2 + n0 + c * 8) : w2;
+          cp_async16(ws + k * (SLAB * 2) + (((c & ~7) | ((c ^ k) & 7)) << 4), src, ok);
+        }
+      }
+    };
+
+    load_slab(0, sbeg);
+    cp_async_commit();
+
+    const int WN = WK;
+    const int wn = wk;
+    const bool has_rows = (wm * 16 < nrows);
+    uint32_t af[R16][4];
+    if (has_rows) {
+#pragma unroll
+      for (int kk = 0; kk < R16; ++kk) {
+        const int m = lane >> 3;
+        const int r = wm * 16 + (m & 1) * 8 + (lane & 7);
+        const int c = kk * 2 + (m >> 1);
+        ldsm_x4(af[kk], mids + r * (XC * 16) + (swz<XC>(r, c) << 4));
+      }
+    }
+    const int rows_here = min(16, nrows - wm * 16);
+    const bool full_block = (rows_here == 16);
+    const uint32_t ostage = base + SM::kOutOff + warp * 8192;
+    T* dbase = static_cast<T*>(a.out) + static_cast<size_t>(pc.row0 + wm * 16) * N2;
+    int obuf = 0;
+
+    for (int si = 0; si < ns; ++si) {
+      const int slab = sbeg + si;
+      const int n0 = slab * SLAB;
+      const int ncols = min(SLAB, N2 - n0);
+      if (si + 1 < ns) load_slab((si + 1) & 1, slab + 1);
+      cp_async_commit();
+      cp_async_wait<1>();
+      named_bar_sync(1, kFusedCThreads);  // slab si has landed for all consumer warps
+      const uint32_t ws = wslab0 + (si & 1) * SM::kW2Slab;
+      const int ngroups = (ncols + 63) >> 6;
+      if (has_rows) {
+        // two groups of 64 columns per iteration: one 16 x 128 block per TMA batch
+        for (int g0 = wn * 2; g0 < ngroups; g0 += WN * 2) {
+          const int ng = min(2, ngroups - g0);
+          if (lane == 0) bulk_wait_read<1>();  // the staging block about to be reused has been read
+          __syncwarp();
+          const uint32_t os = ostage + obuf * 4096;
+#pragma unroll
+          for (int gi = 0; gi < 2; ++gi) {
+            if (gi < ng) {
+              const int grp = g0 + gi;
+              float o[8][4];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+#pragma unroll
+              for (int kk = 0; kk < R16; ++kk) {
+#pragma unroll
+                for (int j = 0; j < 8; j += 2) {
+                  uint32_t bf[4];
+                  const int m = lane >> 3;
+                  if constexpr (!RM) {
+                    const int n = grp * 64 + (j + (m >> 1)) * 8 + (lane & 7);
+                    const int c = kk * 2 + (m & 1);
+                    ldsm_x4(bf, ws + n * (XC * 16) + (swz<XC>(n, c) << 4));
+                  } else {
+                    const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
+                    const int c = grp * 8 + j + (m >> 1);
+                    ldsm_x4_t(bf, ws + k * (SLAB * 2) + (((c & ~7) | ((c ^ k) & 7)) << 4));
+                  }
+                  mma16816<T>(o[j], af[kk], bf[0], bf[1]);
+                  mma16816<T>(o[j + 1], af[kk], bf[2], bf[3]);
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 8; j += 2) {
+                const int m = lane >> 3;
+                const int r = (m & 1) * 8 + (lane & 7);
+                const int c = j + (m >> 1);
+                stsm_x4(os + gi * 2048 + r * 128 + ((c ^ (r & 7)) << 4),
+                        pack2<T>(o[j][0] * sc_out, o[j][1] * sc_out), pack2<T>(o[j][2] * sc_out, o[j][3] * sc_out),
+                        pack2<T>(o[j + 1][0] * sc_out, o[j + 1][1] * sc_out),
+                        pack2<T>(o[j + 1][2] * sc_out, o[j + 1][3] * sc_out));
+              }
+            }
+          }
+          if (full_block) {
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              for (int gi = 0; gi < ng; ++gi) {
+                const int col0 = n0 + (g0 + gi) * 64;
+                if (a.accumulate) tma_reduce_add_2d<T>(&tm.out, col0, pc.row0 + wm * 16, os + gi * 2048);
+                else tma_store_2d(&tm.out, col0, pc.row0 + wm * 16, os + gi * 2048);
+              }
+              bulk_commit();
+            }
+            obuf ^= 1;
+          } else {
+            // ragged tail of the piece: plain 16-byte stores of the rows that exist
+            __syncwarp();
+            for (int gi = 0; gi < ng; ++gi) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const int i = q * 32 + lane;
+                const int r = i >> 3, c = i & 7;
+                const int col = (g0 + gi) * 64 + c * 8;
+                if (r < rows_here && col < ncols) {
+                  uint4 v;
+                  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                               : "r"(os + gi * 2048 + r * 128 + ((c ^ (r & 7)) << 4)));
+                  uint4* dst = reinterpret_cast<uint4*>(dbase + static_cast<size_t>(r) * N2 + n0 + col);
+                  if (a.accumulate) {
+                    const uint4 old = *dst;
+                    const uint32_t* ov = reinterpret_cast<const uint32_t*>(&old);
+                    uint32_t* nv = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                      const float2 p = unpack2<T>(ov[e]);
+                      const float2 n2 = unpack2<T>(nv[e]);
+                      nv[e] = pack2<T>(p.x + n2.x, p.y + n2.y);
+                    }
+                  }
+                  *dst = v;
+                }
+              }
+            }
+            __syncwarp();
+          }
+        }
+      }
+      named_bar_sync(1, kFusedCThreads);  // everyone is done with slab si before it is refilled
+    }
+      if (lane == 0) bulk_wait<0>();  // shared memory must outlive the tensor stores that read it
+    __syncwarp();
+    }
+  if (KS > 1) cluster_wait();
+}
+
+}  // namespace smlm
