@@ -172,9 +172,9 @@ class Workload:
         if self.tl:
             self.pplan = self.ops.Plan(self.part, self.tl)
 
-    # one plan per index pointer, then 1 forward and 3 backward kernels per projection
+    # one plan per index pointer, then 1 forward and 2 backward kernels per projection
     launches_per_step = property(lambda self: 1 + (1 if self.tl else 0)
-                                 + len(self.proj) * (1 + (3 if self.tl else 0)))
+                                 + len(self.proj) * (1 + (2 if self.tl else 0)))
 
     def step(self):
         """The hot path: plans once, then fused forward and backward per projection."""
@@ -294,12 +294,11 @@ def kernel_breakdown(wl, torch, reps=5):
                 lambda p: ops.fwd(p["dx"], p["go"], p["dv"], p["wb"], p["wa"], wl.pplan, r, is_row_major=True,
                                   seg_ids=wl.part_ids, seg_scale=wl.scale),
                 lambda p: e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
-            "wgrad_kernel(dB=gO^T.V)": (
-                lambda p: ops.wgrad(p["dB_t"], p["v"], p["go"], wl.part, wl.pplan, transposed=True),
-                lambda p: e * (n * p["h_out"] + n * r + used_ft * r * p["h_out"])),
-            "wgrad_kernel(dA=dV^T.X)": (
-                lambda p: ops.wgrad(p["dA_t"], p["dv"], p["x"], wl.part, wl.pplan, transposed=False),
-                lambda p: e * (n * p["h_in"] + n * r + used_ft * r * p["h_in"])),
+            "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": (
+                lambda p: ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan,
+                                         r, part_ids=wl.part_ids, part_scale=wl.scale,
+                                         n_table=wl.spec["n_adapters"]),
+                lambda p: e * (n * (p["h_in"] + p["h_out"]) + 2 * n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
         })
     out = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=wl.dev)

@@ -92,15 +92,32 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
                   int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, void* stream);
 
+/* Bytes of the workspace the weight-gradient kernels need for a batch of T token
+ * rows in npart partitions and one (h1 == 0) or two column counts.  The workspace
+ * holds tickets and parked partial sums of partitions that are spread over several
+ * CTAs.  It must be zero-filled ONCE after allocation; every launch leaves it
+ * zeroed again.  Launches that overlap in time must not share a workspace. */
+size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1);
+
 /* Per-partition weight gradient  G_p = scale_p * P[rows_p]^T . Q[rows_p]  with P
  * [T, rank] and Q [T, h]; G_p is [rank, h] (transposed == 0) or [h, rank]
  * (transposed == 1), of the storage type or fp32 (grad_fp32), overwritten or
  * accumulated into.  The dA / dB products of add_lora.backward
- * (kernel_utils.py:144-145).  `plan` is any plan buffer of the batch; only its
- * error word is used. */
+ * (kernel_utils.py:144-145).  `plan` is a plan built on part_indptr. */
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
-                    const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
-                    int transposed, int accumulate, int grad_fp32, void* stream);
+                    const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
+                    int rank, int h, int dtype, int transposed, int accumulate, int grad_fp32, void* stream);
+
+/* Both weight gradients of the backward in one launch:
+ *   dB_p = scale_p * gO[rows_p]^T . V[rows_p]      dA_p = dV[rows_p]^T . X[rows_p]
+ * (kernel_utils.py:144-145; dV is expected to carry the scale already, as
+ * smlm_b200_bwd produces it).  Layout of dA / dB follows is_row_major like the
+ * weights; part_ids (or NULL) selects the per-adapter entry of part_scale. */
+int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
+                         const void* v, const void* go, const int32_t* part_indptr, const int32_t* part_ids,
+                         const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int n_table,
+                         int npart, int T, int h_in, int h_out, int rank, int dtype, int is_row_major,
+                         int accumulate, int grad_fp32, void* stream);
 
 /* Fine-tuning backward of the fused forward over the train partitions
  * part_indptr[npart + 1] (add_lora.backward, kernel_utils.py:129-147):
@@ -110,12 +127,13 @@ int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const in
  * the forward's convention with partitions in the role of segments.  dX rows
  * outside the partitions are not written (the reference returns zeros there,
  * kernel_utils.py:136; the host wrapper clears them).  dA_table / dB_table are
- * device arrays of npart output addresses in the layout of A and B. */
+ * device arrays of npart output addresses in the layout of A and B.  `workspace`:
+ * smlm_b200_wgrad_workspace_bytes(T, npart, rank, h_out, h_in) bytes, see there. */
 int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
                   const void* x, const void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
-                  int n_table, int T, int npart, int h_in, int h_out, int rank, int dtype, int is_row_major,
-                  int accumulate_grads, int grad_fp32, void* stream);
+                  void* workspace, size_t workspace_bytes, int n_table, int T, int npart, int h_in, int h_out,
+                  int rank, int dtype, int is_row_major, int accumulate_grads, int grad_fp32, void* stream);
 
 #ifdef __cplusplus
 }

@@ -230,32 +230,84 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
 // ---- wgrad ------------------------------------------------------------------
 
 template <typename T, int RT>
-int launch_wgrad(const WgradArgs& a, cudaStream_t stream) {
-  return launch(wgrad_kernel<T, RT>, dim3(a.npart * a.ksplit, (a.H + kWgCols - 1) / kWgCols, 1), kThreads,
-                a.ksplit, WgradSmem<RT>::kTotal, stream, a);
+int launch_wgrad(const WgradArgs& a, const WgradMaps& tm, int groups, cudaStream_t stream) {
+  return launch(wgrad_kernel<T, RT>, dim3(groups, a.job[0].slabs + a.job[1].slabs, 1), kWgThreads, 1,
+                WgradSmem<RT>::kTotal, stream, a, tm);
 }
 
-template <typename T>
-int dispatch_wgrad_rt(const WgradArgs& a, cudaStream_t stream) {
-  const int rt = (a.R + 15) / 16;
-  if (rt <= 1) return launch_wgrad<T, 1>(a, stream);
-  if (rt <= 2) return launch_wgrad<T, 2>(a, stream);
-  if (rt <= 4) return launch_wgrad<T, 4>(a, stream);
-  return launch_wgrad<T, 8>(a, stream);
+struct WgradJobDesc {
+  void* const* g_table;
+  const void* p;
+  const void* q;
+  int H;
+  int transposed;
+  int use_scale;
+};
+
+inline int wgrad_rt(int R) {
+  const int rtb = (R + 15) / 16;
+  return rtb > 4 ? 8 : (rtb > 2 ? 4 : rtb);
 }
 
-int run_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
-              const float* scale, const int32_t* ids, int n_table, int* err, int npart, int T, int R, int H,
-              int dtype, int transposed, int accumulate, int grad_fp32, cudaStream_t stream) {
+// How a batch of T token rows in npart partitions is cut for the two jobs' column counts.
+struct WgradShape {
+  int slab, slabs_total, group, groups;
+  size_t ticket_bytes, scratch_bytes;
+};
+
+WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1) {
+  WgradShape s;
+  const int rt = wgrad_rt(R);
+  s.slab = 4 * wgrad_cols_per_warp(rt);
+  s.slabs_total = (h0 + s.slab - 1) / s.slab + (h1 > 0 ? (h1 + s.slab - 1) / s.slab : 0);
+  const int mp = std::max(1, max_pieces_of(T, npart));
+  // one wave of two CTAs per SM, each with at most kWgMaxGroup pieces
+  long long g = (static_cast<long long>(mp) * s.slabs_total + 2 * kNumSMs - 1) / (2 * kNumSMs);
+  g = std::max(1LL, std::min<long long>(g, kWgMaxGroup));
+  s.group = static_cast<int>(g);
+  s.groups = (mp + s.group - 1) / s.group;
+  s.ticket_bytes = (static_cast<size_t>(npart) * s.slabs_total * 4 * sizeof(int) + 255) / 256 * 256;
+  s.scratch_bytes = static_cast<size_t>(s.groups) * 2 * s.slabs_total * (rt * 16) * s.slab * sizeof(float);
+  return s;
+}
+
+// One launch for one or two jobs (job1 == nullptr: one).
+int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t* part_indptr, const float* scale,
+              const int32_t* ids, int n_table, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
+              int R, int dtype, int accumulate, int grad_fp32, cudaStream_t stream) {
   WgradArgs a;
-  a.g_table = g_table; a.p = p; a.q = q; a.part_indptr = part_indptr; a.scale = scale; a.ids = ids;
-  a.n_table = n_table; a.err = err; a.npart = npart; a.T = T; a.R = R; a.H = H;
-  a.transposed = transposed; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
-  const int slabs = (H + kWgCols - 1) / kWgCols;
-  // token chunks of an average partition bound the useful split
-  const int avg_chunks = std::max(1, (T / std::max(npart, 1) + kWgTok - 1) / kWgTok);
-  a.ksplit = pick_split(npart * slabs, avg_chunks);
-  return dtype == SMLM_F16 ? dispatch_wgrad_rt<__half>(a, stream) : dispatch_wgrad_rt<__nv_bfloat16>(a, stream);
+  WgradMaps tm;
+  const int rt = wgrad_rt(R);
+  const WgradShape sh = wgrad_shape(T, npart, R, job0->H, job1 ? job1->H : 0);
+  if (workspace == nullptr || workspace_bytes < sh.ticket_bytes + sh.scratch_bytes) return SMLM_ERR_WORKSPACE;
+  if (!aligned16(workspace)) return SMLM_ERR_MISALIGNED;
+  const WgradJobDesc* jobs[2] = {job0, job1};
+  for (int j = 0; j < 2; ++j) {
+    WgradJob& w = a.job[j];
+    if (jobs[j] == nullptr) {
+      w.g_table = nullptr; w.p = nullptr; w.H = 0; w.transposed = 0; w.use_scale = 0; w.slabs = 0;
+      tm.q[j] = tm.q[0];
+      continue;
+    }
+    w.g_table = jobs[j]->g_table; w.p = jobs[j]->p; w.H = jobs[j]->H; w.transposed = jobs[j]->transposed;
+    w.use_scale = jobs[j]->use_scale; w.slabs = (jobs[j]->H + sh.slab - 1) / sh.slab;
+    if (!make_map_2d(&tm.q[j], jobs[j]->q, T, jobs[j]->H, 16, dtype)) return SMLM_ERR_CUDA;
+  }
+  a.part_indptr = part_indptr; a.scale = scale; a.ids = ids; a.n_table = n_table;
+  a.plan = static_cast<int*>(plan);
+  a.tickets = static_cast<int*>(workspace);
+  a.scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + sh.ticket_bytes);
+  a.npart = npart; a.T = T; a.R = R; a.group = sh.group; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
+  if (dtype == SMLM_F16) {
+    if (rt == 1) return launch_wgrad<__half, 1>(a, tm, sh.groups, stream);
+    if (rt == 2) return launch_wgrad<__half, 2>(a, tm, sh.groups, stream);
+    if (rt == 4) return launch_wgrad<__half, 4>(a, tm, sh.groups, stream);
+    return launch_wgrad<__half, 8>(a, tm, sh.groups, stream);
+  }
+  if (rt == 1) return launch_wgrad<__nv_bfloat16, 1>(a, tm, sh.groups, stream);
+  if (rt == 2) return launch_wgrad<__nv_bfloat16, 2>(a, tm, sh.groups, stream);
+  if (rt == 4) return launch_wgrad<__nv_bfloat16, 4>(a, tm, sh.groups, stream);
+  return launch_wgrad<__nv_bfloat16, 8>(a, tm, sh.groups, stream);
 }
 
 inline bool small_dim_ok(int v) { return v >= 8 && v <= 128 && (v % 8) == 0; }
@@ -356,25 +408,52 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
                    dtype, is_row_major, /*scale_mid=*/0, accumulate, static_cast<cudaStream_t>(stream));
 }
 
+size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1) {
+  if (T < 0 || npart < 0 || rank <= 0 || h0 <= 0 || h1 < 0) return 0;
+  const WgradShape sh = wgrad_shape(T, npart, rank, h0, h1);
+  return sh.ticket_bytes + sh.scratch_bytes;
+}
+
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
-                    const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
-                    int transposed, int accumulate, int grad_fp32, void* stream) {
+                    const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
+                    int rank, int h, int dtype, int transposed, int accumulate, int grad_fp32, void* stream) {
   if (T < 0 || npart < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
-  if (npart == 0) return SMLM_OK;
+  if (npart == 0 || T == 0) return SMLM_OK;
   if (g_table == nullptr || p == nullptr || q == nullptr || part_indptr == nullptr || plan == nullptr)
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
-  return run_wgrad(g_table, p, q, part_indptr, part_scale, nullptr, 0, static_cast<int*>(plan) + 1, npart, T,
-                   rank, h, dtype, transposed, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+  const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
+  return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, workspace, workspace_bytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
+                         const void* v, const void* go, const int32_t* part_indptr, const int32_t* part_ids,
+                         const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int n_table,
+                         int npart, int T, int h_in, int h_out, int rank, int dtype, int is_row_major,
+                         int accumulate, int grad_fp32, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (npart == 0 || T == 0) return SMLM_OK;
+  if (dA_table == nullptr || dB_table == nullptr || dv == nullptr || x == nullptr || v == nullptr ||
+      go == nullptr || part_indptr == nullptr || plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(dv) || !aligned16(x) || !aligned16(v) || !aligned16(go) || !aligned16(plan))
+    return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
+  const WgradJobDesc jb = {dB_table, v, go, h_out, is_row_major ? 0 : 1, part_scale != nullptr};
+  const WgradJobDesc ja = {dA_table, dv, x, h_in, is_row_major ? 1 : 0, 0};
+  return run_wgrad(&jb, &ja, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
                   const void* x, const void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
-                  int n_table, int T, int npart, int h_in, int h_out, int rank, int dtype, int is_row_major,
-                  int accumulate_grads, int grad_fp32, void* stream) {
+                  void* workspace, size_t workspace_bytes, int n_table, int T, int npart, int h_in, int h_out,
+                  int rank, int dtype, int is_row_major, int accumulate_grads, int grad_fp32, void* stream) {
   if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (T == 0 || npart == 0) return SMLM_OK;
@@ -386,7 +465,6 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
     return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int* err = static_cast<int*>(plan) + 1;
   // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a
   // row-major [K = h_out][N = r] operand; the math layout B [r, h_out] is the
   // column-major one.  The layout flag therefore flips for both backward GEMMs.
@@ -394,13 +472,11 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   int rc = run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
                      h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, st);
   if (rc != SMLM_OK) return rc;
-  // dB = scale * gO^T . V : [h_out, r] in the PEFT layout (transposed store)
-  rc = run_wgrad(dB_table, v, go, part_indptr, part_scale, part_ids, n_table, err, npart, T, rank, h_out, dtype,
-                 is_row_major ? 0 : 1, accumulate_grads, grad_fp32, st);
-  if (rc != SMLM_OK) return rc;
-  // dA = dV^T . X : [r, h_in] in the PEFT layout
-  rc = run_wgrad(dA_table, dv, x, part_indptr, nullptr, nullptr, 0, err, npart, T, rank, h_in, dtype,
-                 is_row_major ? 1 : 0, accumulate_grads, grad_fp32, st);
+  // dB = scale * gO^T . V ([h_out, r] in the PEFT layout: transposed store) and
+  // dA = dV^T . X ([r, h_in] in the PEFT layout; dV already carries the scale), in one launch
+  return smlm_b200_wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, part_ids, part_scale, plan, workspace,
+                              workspace_bytes, n_table, npart, T, h_in, h_out, rank, dtype, is_row_major,
+                              accumulate_grads, grad_fp32, stream);
   return rc;
 }
 

@@ -92,24 +92,57 @@ def fwd(y, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, 
     return y
 
 
+_WORKSPACES = {}
+
+
+def wgrad_workspace(device, T: int, npart: int, rank: int, h0: int, h1: int = 0) -> torch.Tensor:
+    """Zero-filled scratch of the weight-gradient kernels, cached per device and grown
+    on demand.  The kernels leave it zeroed, so it is cleared only when (re)allocated.
+    One workspace per device: calls that may overlap on different streams need their
+    own (allocate one with ``torch.zeros`` and pass it explicitly)."""
+    need = int(lib.smlm_b200_wgrad_workspace_bytes(int(T), int(npart), int(rank), int(h0), int(h1)))
+    ws = _WORKSPACES.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _WORKSPACES[device] = ws
+    return ws
+
+
 def wgrad(g_table, p, q, part_indptr, plan: Plan, transposed: bool, part_scale=None, accumulate=False,
-          grad_fp32=False):
+          grad_fp32=False, workspace=None):
+    ws = workspace if workspace is not None else wgrad_workspace(p.device, plan.T, plan.nseg, p.size(1), q.size(1))
     with torch.cuda.device(p.device):
         check(lib.smlm_b200_wgrad(g_table.data_ptr(), p.data_ptr(), q.data_ptr(), part_indptr.data_ptr(),
-                                  _p(part_scale), plan.buf.data_ptr(), int(part_indptr.numel()) - 1,
-                                  int(p.size(0)), int(p.size(1)), int(q.size(1)), _dtype_code(p),
-                                  int(bool(transposed)), int(bool(accumulate)), int(bool(grad_fp32)), _stream(p)),
-              "smlm_b200_wgrad")
+                                  _p(part_scale), plan.buf.data_ptr(), ws.data_ptr(), ws.numel(),
+                                  int(part_indptr.numel()) - 1, plan.T, int(p.size(1)), int(q.size(1)),
+                                  _dtype_code(p), int(bool(transposed)), int(bool(accumulate)),
+                                  int(bool(grad_fp32)), _stream(p)), "smlm_b200_wgrad")
+
+
+def wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, plan: Plan, rank: int, is_row_major=False,
+               part_ids=None, part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None):
+    """dA and dB of every train partition in one launch."""
+    ws = workspace if workspace is not None else wgrad_workspace(go.device, plan.T, plan.nseg, rank, go.size(1),
+                                                                 x.size(1))
+    with torch.cuda.device(go.device):
+        check(lib.smlm_b200_wgrad_pair(dA_table.data_ptr(), dB_table.data_ptr(), dv.data_ptr(), x.data_ptr(),
+                                       v.data_ptr(), go.data_ptr(), part_indptr.data_ptr(), _p(part_ids),
+                                       _p(part_scale), plan.buf.data_ptr(), ws.data_ptr(), ws.numel(), int(n_table),
+                                       int(part_indptr.numel()) - 1, plan.T, int(x.size(1)), int(go.size(1)),
+                                       int(rank), _dtype_code(go), int(bool(is_row_major)), int(bool(accumulate)),
+                                       int(bool(grad_fp32)), _stream(go)), "smlm_b200_wgrad_pair")
 
 
 def bwd(dx, dA_table, dB_table, dv, go, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False,
-        part_ids=None, part_scale=None, accumulate_grads=False, grad_fp32=False):
+        part_ids=None, part_scale=None, accumulate_grads=False, grad_fp32=False, workspace=None):
     """Backward over the train partitions ``plan.indptr``; rows = go.size(0)."""
+    ws = workspace if workspace is not None else wgrad_workspace(go.device, plan.T, plan.nseg, rank, go.size(1),
+                                                                 x.size(1))
     with torch.cuda.device(go.device):
         check(lib.smlm_b200_bwd(dx.data_ptr(), dA_table.data_ptr(), dB_table.data_ptr(), dv.data_ptr(),
                                 go.data_ptr(), x.data_ptr(), v.data_ptr(), wa_table.data_ptr(),
                                 wb_table.data_ptr(), _p(part_ids), _p(part_scale), plan.indptr.data_ptr(),
-                                plan.buf.data_ptr(), int(wa_table.numel()), plan.T, plan.nseg,
-                                int(x.size(1)), int(go.size(1)), int(rank), _dtype_code(go),
+                                plan.buf.data_ptr(), ws.data_ptr(), ws.numel(), int(wa_table.numel()), plan.T,
+                                plan.nseg, int(x.size(1)), int(go.size(1)), int(rank), _dtype_code(go),
                                 int(bool(is_row_major)), int(bool(accumulate_grads)), int(bool(grad_fp32)),
                                 _stream(go)), "smlm_b200_bwd")
