@@ -42,7 +42,8 @@ enum {
   SMLM_ERR_BAD_INDPTR = 7,       /* reported by smlm_b200_plan_status */
   SMLM_ERR_BAD_POINTER = 8,      /* reported by smlm_b200_plan_status */
   SMLM_ERR_BAD_INDEX = 9,        /* reported by smlm_b200_plan_status */
-  SMLM_ERR_TIMEOUT = 10          /* reported by smlm_b200_plan_status: a bounded wait in a kernel gave up */
+  SMLM_ERR_TIMEOUT = 10,         /* reported by smlm_b200_plan_status: a bounded wait in a kernel gave up */
+  SMLM_ERR_STATIC_LIMIT = 11     /* smlm_b200_wgrad_static: the problem needs more than the built-in scratch */
 };
 
 enum { SMLM_F16 = 0, SMLM_BF16 = 1 };
@@ -107,6 +108,34 @@ size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
                     const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
                     int rank, int h, int dtype, int transposed, int accumulate, int grad_fp32, void* stream);
+
+/* smlm_b200_wgrad for callers that cannot hand over device memory of their own.
+ * (No counterpart in the reference: its backward is torch matmuls and allocates freely.)
+ *
+ * Who needs it: code that runs where allocating is not an option - a serving loop
+ * that carved up all device memory at start-up and must not call the allocator on the
+ * request path, a plugin that receives its buffers from a host application and owns
+ * no allocator, an embedding framework whose caching pool must see every allocation.
+ * Such callers can pass inputs and outputs but have nowhere to get the workspace of
+ * smlm_b200_wgrad from.  This variant keeps the workspace in a fixed array inside the
+ * library's device image instead and calls no allocating routine at all.
+ *
+ * Same arguments and results as smlm_b200_wgrad, minus the workspace.  Limits and rules:
+ *  - the array is SMLM_STATIC_WGRAD_BYTES (16 MiB) and every GPU that loads the library
+ *    holds it until the process exits; a problem whose workspace
+ *    (smlm_b200_wgrad_workspace_bytes(T, npart, rank, h, 0)) is larger is refused with
+ *    SMLM_ERR_STATIC_LIMIT before anything is launched;
+ *  - the first call on each device looks up the array's device address (with that
+ *    device current).  Make that first call outside any stream capture;
+ *  - all calls on a device share the one array, which keeps the previous call's
+ *    contents; the tickets, the only part that must start from zero, are cleared on
+ *    `stream` at the start of every call.  Two calls that may run on the GPU at the
+ *    same time (different streams, or graphs replayed concurrently) race on it - keep
+ *    them ordered, or use smlm_b200_wgrad with separate workspaces. */
+#define SMLM_STATIC_WGRAD_BYTES (16u << 20)
+int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
+                           const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
+                           int transposed, int accumulate, int grad_fp32, void* stream);
 
 /* Both weight gradients of the backward in one launch:
  *   dB_p = scale_p * gO[rows_p]^T . V[rows_p]      dA_p = dV[rows_p]^T . X[rows_p]

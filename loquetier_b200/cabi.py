@@ -18,7 +18,7 @@ SMLM_BF16 = 1
 STATUS_NAMES = {
     0: "SMLM_OK", 1: "SMLM_ERR_INVALID_ARGUMENT", 2: "SMLM_ERR_DTYPE", 3: "SMLM_ERR_NO_KERNEL",
     4: "SMLM_ERR_MISALIGNED", 5: "SMLM_ERR_WORKSPACE", 6: "SMLM_ERR_CUDA", 7: "SMLM_ERR_BAD_INDPTR",
-    8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX", 10: "SMLM_ERR_TIMEOUT",
+    8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX", 10: "SMLM_ERR_TIMEOUT", 11: "SMLM_ERR_STATIC_LIMIT",
 }
 
 # name -> (restype, argtypes); mirrors include/smlm_b200.h one to one
@@ -35,6 +35,7 @@ SIGNATURES = {
                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "smlm_b200_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 8 + [c_void_p]),
+    "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 10 + [c_void_p]),
     "smlm_b200_bwd": (c_int, [c_void_p] * 14 + [c_size_t] + [c_int] * 10 + [c_void_p]),
 }

@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <mutex>
 
 #include "../../include/smlm_b200.h"
 #include "smlm_expand.cuh"
@@ -310,6 +311,41 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   return launch_wgrad<__nv_bfloat16, 8>(a, tm, sh.groups, stream);
 }
 
+// ---- built-in scratch for callers that cannot allocate ------------------------------
+// Some hosts of this library run where device allocation is off the table: inside a
+// latency-critical serving loop that has pre-carved all of its memory, in a plugin that
+// is handed buffers but owns no allocator, or under a framework whose memory pool must
+// not be bypassed.  For them the weight-gradient kernel's workspace lives in this fixed
+// array in the library's own device image.  Every GPU that loads the library carries the
+// array (kStaticWgradBytes) until the process exits.
+constexpr size_t kStaticWgradBytes = SMLM_STATIC_WGRAD_BYTES;
+static __device__ __align__(256) unsigned char g_wgrad_static_scratch[kStaticWgradBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; kernels need its device address, which is
+// looked up once per device (with that device current) and remembered.
+int static_scratch_of_current_device(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return SMLM_ERR_CUDA;
+  }
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_wgrad_static_scratch) != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return SMLM_ERR_CUDA;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return SMLM_OK;
+}
+
 inline bool small_dim_ok(int v) { return v >= 8 && v <= 128 && (v % 8) == 0; }
 inline bool large_dim_ok(int v) { return v >= 8 && (v % 8) == 0; }
 
@@ -332,6 +368,9 @@ const char* smlm_b200_status_string(int status) {
     case SMLM_ERR_BAD_POINTER: return "adapter pointer is null or not 16-byte aligned";
     case SMLM_ERR_BAD_INDEX: return "adapter index outside the table";
     case SMLM_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case SMLM_ERR_STATIC_LIMIT:
+      return "problem too large for the library's built-in 16 MiB scratch; use the entry point that takes a "
+             "workspace";
     default: return "unknown status";
   }
 }
@@ -427,6 +466,32 @@ int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const in
   const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
   return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, workspace, workspace_bytes, npart, T,
                    rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
+                           const float* part_scale, void* plan, int npart, int T, int rank, int h, int dtype,
+                           int transposed, int accumulate, int grad_fp32, void* stream) {
+  if (T < 0 || npart < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (npart == 0 || T == 0) return SMLM_OK;
+  if (g_table == nullptr || p == nullptr || q == nullptr || part_indptr == nullptr || plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
+  const WgradShape sh = wgrad_shape(T, npart, rank, h, 0);
+  if (sh.ticket_bytes + sh.scratch_bytes > kStaticWgradBytes) return SMLM_ERR_STATIC_LIMIT;
+  void* scratch = nullptr;
+  const int rc = static_scratch_of_current_device(&scratch);
+  if (rc != SMLM_OK) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  // the array keeps whatever the previous call left; only the tickets have to start at zero
+  if (cudaMemsetAsync(scratch, 0, sh.ticket_bytes, st) != cudaSuccess) {
+    cudaGetLastError();
+    return SMLM_ERR_CUDA;
+  }
+  const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
+  return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, scratch, kStaticWgradBytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, st);
 }
 
 int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
