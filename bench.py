@@ -166,6 +166,8 @@ class Workload:
         self.plan = None
         self.pplan = None
         self.ops = ops
+        self.accumulate_grads = False
+        self.overlap = True
 
     def build_plans(self):
         self.plan = self.ops.Plan(self.seg, self.T)
@@ -177,16 +179,25 @@ class Workload:
                                  + len(self.proj) * (1 + (2 if self.tl else 0)))
 
     def step(self):
-        """The hot path: plans once, then fused forward and backward per projection."""
+        """The hot path: plans once, then for every projection the fused forward, the fused
+        dV/dX backward and the weight gradients.  The projections are independent of each other,
+        so the launches of one kind are issued back to back and marked independent: the read
+        phase of one overlaps the write phase of the one before.  The weight gradients come last
+        because they consume v and dV."""
         ops = self.ops
         self.build_plans()
         r = self.spec["rank"]
-        for p in self.proj:
+        for i, p in enumerate(self.proj):
             ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], self.plan, r, seg_ids=self.ids,
-                    seg_scale=self.scale)
-            if self.tl:
-                ops.bwd(p["dx"], p["dA_t"], p["dB_t"], p["dv"], p["go"], p["x"], p["v"], p["wa"], p["wb"],
-                        self.pplan, r, part_ids=self.part_ids, part_scale=self.scale)
+                    seg_scale=self.scale, independent=self.overlap and i > 0)
+        if self.tl:
+            for p in self.proj:
+                ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], self.pplan, r, part_ids=self.part_ids,
+                           part_scale=self.scale, independent=self.overlap)
+            for p in self.proj:
+                ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], self.part, self.pplan, r,
+                               part_ids=self.part_ids, part_scale=self.scale, n_table=self.spec["n_adapters"],
+                               accumulate=self.accumulate_grads)
 
 
 # ---------------------------------------------------------------------------
@@ -283,19 +294,19 @@ def kernel_breakdown(wl, torch, reps=5):
                     r, part_ids=wl.part_ids, part_scale=wl.scale)
     classes = {
         "fused_kernel(fwd x->v->y)": (
-            lambda p: ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids,
-                              seg_scale=wl.scale),
+            lambda p, i: ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids,
+                                 seg_scale=wl.scale, independent=wl.overlap and i > 0),
             lambda p: e * (T * p["h_in"] + T * p["h_out"] + T * r + used * r * (p["h_in"] + p["h_out"]))),
     }
     if n:
         classes.update({
-            # the backward's fused launch is the same kernel with the roles of the panels swapped
             "fused_kernel(bwd gO->dV->dX)": (
-                lambda p: ops.fwd(p["dx"], p["go"], p["dv"], p["wb"], p["wa"], wl.pplan, r, is_row_major=True,
-                                  seg_ids=wl.part_ids, seg_scale=wl.scale),
+                lambda p, i: ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], wl.pplan, r,
+                                        part_ids=wl.part_ids, part_scale=wl.scale,
+                                        independent=wl.overlap and i > 0),
                 lambda p: e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
             "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": (
-                lambda p: ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan,
+                lambda p, i: ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan,
                                          r, part_ids=wl.part_ids, part_scale=wl.scale,
                                          n_table=wl.spec["n_adapters"]),
                 lambda p: e * (n * (p["h_in"] + p["h_out"]) + 2 * n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
@@ -308,8 +319,8 @@ def kernel_breakdown(wl, torch, reps=5):
             flush.zero_()  # evict L2 between repetitions of the same class
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for p in wl.proj:
-                fn(p)
+            for i, p in enumerate(wl.proj):
+                fn(p, i)
             e1.record()
             torch.cuda.synchronize()
             if it > 0:
@@ -448,6 +459,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="do not mark launches independent of each other")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-kernel-class timing pass")
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
@@ -502,15 +514,25 @@ def main():
         dist = dist_mod
 
     wl = Workload(spec, dev)
-    allreduce = None
-    if a.workload == "c5" and dist is not None:
+    wl.overlap = not a.no_overlap
+    bucket = None
+    if a.workload == "c5":
+        # data-parallel fine-tuning: dA/dB of all adapters live in one flat bucket that the backward
+        # kernels accumulate into and that is all-reduced once per step
         from loquetier_b200.dp import GradBucket
-        allreduce = GradBucket(wl, dist)
+        bucket = GradBucket([(p["h_in"], p["h_out"]) for p in wl.proj], spec["n_adapters"], spec["rank"], wl.dt, dev)
+        for i, p in enumerate(wl.proj):
+            p["dA_t"], p["dB_t"] = bucket.tables(i, wl.part_ids)
+            p["dA"], p["dB"] = bucket.dA[i], bucket.dB[i]
+        wl.accumulate_grads = True
+        cfg["allreduce_bytes_per_step"] = bucket.nbytes
 
     def eager_step():
+        if bucket is not None:
+            bucket.zero()
         wl.step()
-        if allreduce is not None:
-            allreduce.reduce()
+        if bucket is not None:
+            bucket.reduce()
 
     eager_step()
     torch.cuda.synchronize()
@@ -518,7 +540,7 @@ def main():
     if wl.pplan is not None:
         wl.pplan.raise_if_failed()
 
-    use_graph = not a.no_graph and allreduce is None
+    use_graph = not a.no_graph and not (bucket is not None and world > 1)
     if use_graph:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())

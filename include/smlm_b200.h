@@ -88,10 +88,19 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
  * the two operator calls of add_lora.forward (kernel_utils.py:114-120) and, with
  * seg_scale / accumulate, the scale and add of MixedLoraLinear.forward
  * (mixed_lora.py:214-217).  `v` [T, rank] is written in the storage type like the
- * reference's intermediate (kernel_utils.py:117) and is what the backward needs. */
+ * reference's intermediate (kernel_utils.py:117) and is what the backward needs.
+ *
+ * `independent` = 1 is a promise by the caller: this call reads nothing that the
+ * previous kernel enqueued on `stream` writes (for example q_proj, k_proj and
+ * v_proj of one layer, which share their input).  The launch may then start while
+ * that kernel is still running - its read phase overlaps the predecessor's write
+ * phase, which is how both directions of HBM are kept busy - and it still completes
+ * after it, so stream order holds for everything enqueued later.  With 0 the launch
+ * waits for its predecessor like any kernel. */
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
-                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, void* stream);
+                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, int independent,
+                  void* stream);
 
 /* Bytes of the workspace the weight-gradient kernels need for a batch of T token
  * rows in npart partitions and one (h1 == 0) or two column counts.  The workspace
@@ -148,10 +157,19 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
                          int npart, int T, int h_in, int h_out, int rank, int dtype, int is_row_major,
                          int accumulate, int grad_fp32, void* stream);
 
+/* First half of the backward: dV = scale * gO . B (written to dv [T, rank]) and
+ * dX = dV . A for the rows of every train partition (kernel_utils.py:142-143), one
+ * launch.  `plan` is built on the partition index pointer; `independent` as in
+ * smlm_b200_fwd. */
+int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
+                     const int32_t* part_ids, const float* part_scale, void* plan, int n_table, int T, int npart,
+                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, void* stream);
+
 /* Fine-tuning backward of the fused forward over the train partitions
  * part_indptr[npart + 1] (add_lora.backward, kernel_utils.py:129-147):
  *   dV = scale * gO . B     (written to dv [T, rank], storage type)
  *   dB_p = scale * gO^T . V   dA_p = dV^T . X   dX = dV . A
+ * i.e. smlm_b200_bwd_dx followed by smlm_b200_wgrad_pair.
  * `plan` is a plan built on part_indptr.  wa_table / wb_table / part_ids follow
  * the forward's convention with partitions in the role of segments.  dX rows
  * outside the partitions are not written (the reference returns zeros there,

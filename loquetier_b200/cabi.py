@@ -31,8 +31,8 @@ SIGNATURES = {
     "smlm_b200_plan_status": (c_int, [c_void_p, ctypes.POINTER(c_int), c_void_p]),
     "smlm_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "smlm_b200_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_fwd": (c_int, [c_void_p] * 8 + [c_int] * 10 + [c_void_p]),
+    "smlm_b200_bwd_dx": (c_int, [c_void_p] * 8 + [c_int] * 9 + [c_void_p]),
     "smlm_b200_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),

@@ -90,13 +90,17 @@ int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cud
   cfg.blockDim = dim3(threads, 1, 1);
   cfg.dynamicSmemBytes = smem_bytes;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = cluster_x;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // every kernel of the library calls pdl_wait() before it touches memory that an earlier kernel
+  // of the stream may have written, so it may be scheduled while its predecessor drains
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   if (cudaLaunchKernelEx(&cfg, kern, args...) != cudaSuccess) {
     cudaGetLastError();
     return SMLM_ERR_CUDA;
@@ -193,11 +197,13 @@ int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cu
 // OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
 int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
               const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
-              int N2, int dtype, int row_major, int scale_mid, int accumulate, cudaStream_t stream) {
+              int N2, int dtype, int row_major, int scale_mid, int accumulate, int independent,
+              cudaStream_t stream) {
   FusedArgs a;
   a.out = out; a.mid = mid; a.w1_table = w1_table; a.w2_table = w2_table; a.ids = ids; a.scale = scale;
   a.plan = static_cast<int*>(plan);
   a.n_table = n_table; a.K1 = K1; a.R = R; a.N2 = N2; a.scale_mid = scale_mid; a.accumulate = accumulate;
+  a.independent = independent;
   const int mp = max_pieces_of(T, nseg);
   // One CTA per SM.  A piece can be split over the KS CTAs of a cluster; pick the KS that
   // minimises (waves of 148 CTAs) x (work per CTA + fixed cost of set-up and the cluster reduce).
@@ -209,7 +215,8 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   double best = 1e30;
   for (int k = 1; k <= 8; ++k) {
     if (k > 1 && (ksteps < k || nslabs < k)) break;
-    const int waves = (std::max(mp, 1) * k + kNumSMs - 1) / kNumSMs;
+    const int slots = kNumSMs * fused_ctas_per_sm(r16);
+    const int waves = (std::max(mp, 1) * k + slots - 1) / slots;
     const double cost = waves * (1.0 / k + (k > 1 ? 0.15 : 0.08));
     if (cost < best - 1e-9) {
       best = cost;
@@ -434,7 +441,8 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
 
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
-                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, void* stream) {
+                  int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, int independent,
+                  void* stream) {
   if (T < 0 || nseg < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (T == 0 || nseg == 0) return SMLM_OK;
@@ -444,7 +452,8 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
   if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
   return run_fused(y, v, x, wa_table, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, h_in, rank, h_out,
-                   dtype, is_row_major, /*scale_mid=*/0, accumulate, static_cast<cudaStream_t>(stream));
+                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0,
+                   static_cast<cudaStream_t>(stream));
 }
 
 size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1) {
@@ -514,35 +523,41 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
                    rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
 }
 
+int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
+                     const int32_t* part_ids, const float* part_scale, void* plan, int n_table, int T, int npart,
+                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || npart == 0) return SMLM_OK;
+  if (dx == nullptr || dv == nullptr || go == nullptr || wa_table == nullptr || wb_table == nullptr ||
+      plan == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(dx) || !aligned16(dv) || !aligned16(go) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
+  // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a row-major
+  // [K = h_out][N = r] operand; the math layout B [r, h_out] is the column-major one.  The layout
+  // flag therefore flips for both products of this launch (dX = dV . A likewise).
+  return run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
+                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0,
+                   static_cast<cudaStream_t>(stream));
+}
+
 int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
                   const void* x, const void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
                   void* workspace, size_t workspace_bytes, int n_table, int T, int npart, int h_in, int h_out,
                   int rank, int dtype, int is_row_major, int accumulate_grads, int grad_fp32, void* stream) {
-  if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
-  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
-  if (T == 0 || npart == 0) return SMLM_OK;
-  if (dx == nullptr || dA_table == nullptr || dB_table == nullptr || dv == nullptr || go == nullptr ||
-      x == nullptr || v == nullptr || wa_table == nullptr || wb_table == nullptr || part_indptr == nullptr ||
-      plan == nullptr)
+  if (T == 0 || npart == 0) return (T < 0 || npart < 0) ? SMLM_ERR_INVALID_ARGUMENT : SMLM_OK;
+  if (dA_table == nullptr || dB_table == nullptr || x == nullptr || v == nullptr || part_indptr == nullptr)
     return SMLM_ERR_INVALID_ARGUMENT;
-  if (!aligned16(dx) || !aligned16(dv) || !aligned16(go) || !aligned16(x) || !aligned16(v) || !aligned16(plan))
-    return SMLM_ERR_MISALIGNED;
-  if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a
-  // row-major [K = h_out][N = r] operand; the math layout B [r, h_out] is the
-  // column-major one.  The layout flag therefore flips for both backward GEMMs.
-  // and dX = dV . A in the same launch.
-  int rc = run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
-                     h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, st);
+  const int rc = smlm_b200_bwd_dx(dx, dv, go, wa_table, wb_table, part_ids, part_scale, plan, n_table, T, npart,
+                                  h_in, h_out, rank, dtype, is_row_major, 0, stream);
   if (rc != SMLM_OK) return rc;
   // dB = scale * gO^T . V ([h_out, r] in the PEFT layout: transposed store) and
   // dA = dV^T . X ([r, h_in] in the PEFT layout; dV already carries the scale), in one launch
   return smlm_b200_wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, part_ids, part_scale, plan, workspace,
                               workspace_bytes, n_table, npart, T, h_in, h_out, rank, dtype, is_row_major,
                               accumulate_grads, grad_fp32, stream);
-  return rc;
 }
 
 }  // extern "C"

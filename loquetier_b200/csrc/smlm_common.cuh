@@ -262,6 +262,14 @@ template <int N>
 __device__ __forceinline__ void bulk_wait() {
   asm volatile("cp.async.bulk.wait_group %0;\n" ::"n"(N) : "memory");
 }
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization
+// attribute may start while its predecessor in the stream is still running.  pdl_wait()
+// blocks until the predecessor has completed and its writes are visible; pdl_trigger()
+// tells the scheduler that the successor may be started now.  Without the launch
+// attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+
 __device__ __forceinline__ void stsm_x4(uint32_t addr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
   asm volatile("stmatrix.sync.aligned.m8n8.x4.shared.b16 [%0], {%1,%2,%3,%4};\n"
                ::"r"(addr), "r"(r0), "r"(r1), "r"(r2), "r"(r3)

@@ -51,6 +51,8 @@ __global__ void __launch_bounds__(kThreads) expand_kernel(const ExpandArgs a) {
   const int lane = tid & 31;
   const int warp = tid >> 5;
 
+  pdl_wait();
+  pdl_trigger();
   const int count = a.plan[0];
   const int piece_idx = blockIdx.x;
   if (piece_idx >= count) return;

@@ -46,9 +46,12 @@ constexpr int kFusedCThreads = kFusedConsumers * 32;
 #define SMLM_FUSED_CH 8
 #endif
 // 64-column chunks of IN per ring stage; high ranks trade width for panel space
-constexpr int fused_chunks(int r16) { return r16 >= 8 ? 2 : (r16 == 4 ? 4 : SMLM_FUSED_CH); }
+// Rank <= 16 is sized so that two CTAs fit on one SM: an independent successor launch can then
+// move in and read while this launch is still writing.
+constexpr int fused_chunks(int r16) { return r16 >= 8 ? 2 : (r16 == 4 ? 4 : (r16 == 2 ? SMLM_FUSED_CH : 4)); }
 constexpr int fused_stages(int) { return 2; }
-constexpr int fused_slab(int r16) { return r16 >= 8 ? 128 : (r16 == 4 ? 256 : 1024); }
+constexpr int fused_slab(int r16) { return r16 >= 8 ? 128 : (r16 == 4 ? 256 : (r16 == 2 ? 1024 : 512)); }
+constexpr int fused_ctas_per_sm(int r16) { return r16 == 1 ? 2 : 1; }
 
 struct FusedMaps {
   CUtensorMap in8;    // IN boxes of 8 rows x 64 columns (pieces of at most 8 rows)
@@ -82,7 +85,7 @@ struct FusedSmem {
   static constexpr int kMid = kBM * KP * 2;
   static constexpr int kBarOff = kMidOff + kMid;
   static constexpr int kTotal = kBarOff + 2 * kStages * 8 + 1024;  // + alignment slack
-  static_assert(kTotal <= 227 * 1024, "shared memory budget");
+  static_assert(kTotal <= (fused_ctas_per_sm(R16) == 2 ? 113 : 227) * 1024, "shared memory budget");
   static_assert(kW2Slab % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
@@ -99,6 +102,7 @@ struct FusedArgs {
   int ksplit;
   int scale_mid;                // 1: the scale multiplies MID (backward); 0: it multiplies OUT (forward)
   int accumulate;               // OUT += instead of OUT =
+  int independent;              // 1: reads nothing the previous kernel of the stream wrote
 };
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
@@ -112,7 +116,7 @@ __device__ __forceinline__ void cluster_wait() {
 }
 
 template <typename T, int R16, bool RM>
-__global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs a,
+__global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_kernel(const FusedArgs a,
                                                                 const __grid_constant__ FusedMaps tm) {
   extern __shared__ unsigned char smem_raw[];
   using SM = FusedSmem<R16, RM>;
@@ -132,9 +136,17 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
   const int piece_idx = blockIdx.x / KS;
   const int z = blockIdx.x - piece_idx * KS;
 
+  // A launch that depends on its predecessor waits for it here.  An independent one starts at
+  // once - it overlaps its read phase with the predecessor's write phase - and waits just before
+  // it exits instead, so that completion still happens in stream order.
+  if (!a.independent) pdl_wait();
+  pdl_trigger();  // the next launch of the stream may be scheduled as soon as there is room
   const int count = a.plan[0];
   const Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[piece_idx];
-  if (piece_idx >= count) return;  // the whole cluster leaves together
+  if (piece_idx >= count) {  // the whole cluster leaves together
+    if (a.independent) pdl_wait();
+    return;
+  }
   const int nrows = pc.nrows;
   const int K1 = a.K1, R = a.R, N2 = a.N2;
   int* err = a.plan + 1;
@@ -150,6 +162,9 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
   const int per = (ksteps + KS - 1) / KS;
   const int kbeg = z * per;
   const int nk = w_ok ? max(0, min(ksteps, kbeg + per) - kbeg) : 0;
+  // CTAs walk their K slice from different starting points so that, at any moment, the machine as
+  // a whole reads many different column bands of IN (and all DRAM channels) instead of one
+  const int krot = nk > 0 ? (piece_idx * 5) % nk : 0;
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -195,7 +210,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
     const int nblk = small ? 1 : ((nrows + 15) >> 4);
     for (int it = 0; it < nk; ++it) {
       const int slot = it % S;
-      const int k0 = (kbeg + it) * KC;
+      const int kstep = kbeg + (it + krot < nk ? it + krot : it + krot - nk);
+      const int k0 = kstep * KC;
       const uint32_t xs = base + slot * SM::kStage;
       const uint32_t ws = xs + SM::kXBytes;
       const uint32_t fb = full0 + slot * 8;
@@ -224,7 +240,8 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
       const uint32_t ws = xs + SM::kXBytes;
       mbar_wait(full0 + slot * 8, (it / S) & 1, err, dead);
       if (active) {
-        const int kmax = (min(KC, K1 - (kbeg + it) * KC) + 15) >> 4;
+        const int kstep = kbeg + (it + krot < nk ? it + krot : it + krot - nk);
+        const int kmax = (min(KC, K1 - kstep * KC) + 15) >> 4;
         for (int kk = wk; kk < kmax; kk += WK) {
           uint32_t af[4];
           {
@@ -344,7 +361,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
       }
     };
 
-    load_slab(0, sbeg);
+    // same idea for the write phase: start at a different slab per piece
+    const int srot = (piece_idx * 3) % ns;
+    auto slab_of = [&](int si) { return sbeg + (si + srot < ns ? si + srot : si + srot - ns); };
+    load_slab(0, slab_of(0));
     cp_async_commit();
 
     const int WN = WK;
@@ -367,10 +387,10 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
     int obuf = 0;
 
     for (int si = 0; si < ns; ++si) {
-      const int slab = sbeg + si;
+      const int slab = slab_of(si);
       const int n0 = slab * SLAB;
       const int ncols = min(SLAB, N2 - n0);
-      if (si + 1 < ns) load_slab((si + 1) & 1, slab + 1);
+      if (si + 1 < ns) load_slab((si + 1) & 1, slab_of(si + 1));
       cp_async_commit();
       cp_async_wait<1>();
       named_bar_sync(1, kFusedCThreads);  // slab si has landed for all consumer warps
@@ -469,10 +489,11 @@ __global__ void __launch_bounds__(kFusedThreads, 1) fused_kernel(const FusedArgs
       }
       named_bar_sync(1, kFusedCThreads);  // everyone is done with slab si before it is refilled
     }
-      if (lane == 0) bulk_wait<0>();  // shared memory must outlive the tensor stores that read it
+    if (lane == 0) bulk_wait<0>();  // shared memory must outlive the tensor stores that read it
     __syncwarp();
-    }
+  }
   if (KS > 1) cluster_wait();
+  if (a.independent) pdl_wait();
 }
 
 }  // namespace smlm

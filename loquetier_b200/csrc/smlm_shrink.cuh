@@ -76,6 +76,8 @@ __global__ void __launch_bounds__(kShrinkThreads) shrink_kernel(const ShrinkArgs
   const int piece_idx = blockIdx.x / KS;
   const int z = blockIdx.x - piece_idx * KS;  // == rank in the cluster (cluster dims are (KS,1,1))
 
+  pdl_wait();
+  pdl_trigger();
   const int count = a.plan[0];
   const Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[piece_idx];
   if (piece_idx >= count) return;  // whole cluster leaves together

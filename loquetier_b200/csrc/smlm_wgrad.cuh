@@ -116,6 +116,8 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
   const int ncols = min(SLAB, H - col0);
   int* err = a.plan + 1;
 
+  pdl_wait();
+  pdl_trigger();
   const int count = a.plan[0];
   const int pbeg = grp * G;
   const int np = max(0, min(count, pbeg + G) - pbeg);  // pieces of this CTA

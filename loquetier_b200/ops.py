@@ -81,15 +81,30 @@ def gemm(y, x, w_table, plan: Plan, is_row_major=False, seg_ids=None, seg_scale=
 
 
 def fwd(y, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, seg_ids=None, seg_scale=None,
-        accumulate=False):
-    """Fused shrink + expand (+ scale, + accumulate into y); writes v [T, rank]."""
+        accumulate=False, independent=False):
+    """Fused shrink + expand (+ scale, + accumulate into y); writes v [T, rank].
+
+    ``independent=True`` promises that this call reads nothing the previous kernel on
+    the stream writes; the launch then overlaps with that kernel's write phase."""
     with torch.cuda.device(x.device):
         check(lib.smlm_b200_fwd(y.data_ptr(), x.data_ptr(), v.data_ptr(), wa_table.data_ptr(),
                                 wb_table.data_ptr(), _p(seg_ids), _p(seg_scale), plan.buf.data_ptr(),
                                 int(wa_table.numel()), int(x.size(0)), plan.nseg, int(x.size(1)),
                                 int(y.size(1)), int(rank), _dtype_code(x), int(bool(is_row_major)),
-                                int(bool(accumulate)), _stream(x)), "smlm_b200_fwd")
+                                int(bool(accumulate)), int(bool(independent)), _stream(x)), "smlm_b200_fwd")
     return y
+
+
+def bwd_dx(dx, dv, go, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, part_ids=None,
+           part_scale=None, independent=False):
+    """dV = scale * gO . B and dX = dV . A over the train partitions of ``plan``."""
+    with torch.cuda.device(go.device):
+        check(lib.smlm_b200_bwd_dx(dx.data_ptr(), dv.data_ptr(), go.data_ptr(), wa_table.data_ptr(),
+                                   wb_table.data_ptr(), _p(part_ids), _p(part_scale), plan.buf.data_ptr(),
+                                   int(wa_table.numel()), plan.T, plan.nseg, int(dx.size(1)), int(go.size(1)),
+                                   int(rank), _dtype_code(go), int(bool(is_row_major)), int(bool(independent)),
+                                   _stream(go)), "smlm_b200_bwd_dx")
+    return dx
 
 
 _WORKSPACES = {}

@@ -273,3 +273,37 @@ def test_backward_deterministic():
     assert torch.equal(a[0], b[0])
     for g1, g2 in zip(a[1] + a[2], b[1] + b[2]):
         assert torch.equal(g1, g2)
+
+
+def test_independent_launches_match_serial_ones():
+    """Launches marked independent may overlap with their predecessor; results must be
+    the same bits as when every launch waits for the one before."""
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    cases = [to_dev(_case(400 + i, [700, 64, 3, 1, 1200, 33], 6, 1024, 2048 if i % 2 else 512, 16, torch.bfloat16))
+             for i in range(4)]
+    T = cases[0]["x"].shape[0]
+    plan = ops.Plan(cases[0]["seg_d"], T)
+    part = torch.tensor([0, 700, 764], dtype=torch.int32, device=dev())
+    pplan = ops.Plan(part, 764)
+    tabs = [(ptr_table(c["wa_d"]), ptr_table(c["wb_d"])) for c in cases]
+    outs = {}
+    for mode in (False, True):
+        ys, vs, dxs, dvs = [], [], [], []
+        for i, c in enumerate(cases):
+            y = torch.zeros((T, c["h_out"]), dtype=torch.bfloat16, device=dev())
+            v = torch.zeros((T, 16), dtype=torch.bfloat16, device=dev())
+            ops.fwd(y, c["x"], v, tabs[i][0], tabs[i][1], plan, 16, seg_ids=c["ids_d"], independent=mode and i > 0)
+            ys.append(y); vs.append(v)
+        for i, c in enumerate(cases):
+            dx = torch.zeros((T, c["h_in"]), dtype=torch.bfloat16, device=dev())
+            dv = torch.zeros((764, 16), dtype=torch.bfloat16, device=dev())
+            ops.bwd_dx(dx, dv, c["go"], tabs[i][0], tabs[i][1], pplan, 16, part_ids=c["ids_d"][:2].contiguous(),
+                       independent=mode)
+            dxs.append(dx); dvs.append(dv)
+        torch.cuda.synchronize()
+        plan.raise_if_failed(); pplan.raise_if_failed()
+        outs[mode] = ys + vs + dxs + dvs
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.equal(a, b)
+    assert float(outs[True][0].abs().max()) > 0

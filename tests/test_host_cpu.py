@@ -42,7 +42,7 @@ def test_argument_validation_needs_no_gpu():
     assert L.smlm_b200_gemm(None, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, None) == 1
     assert L.smlm_b200_gemm(None, None, None, None, None, None, 0, 0, 0, 64, 16, 1, 0, 0, None) == 0
     assert L.smlm_b200_plan(16, 8, 16, 4, 100, None) == 5
-    assert L.smlm_b200_fwd(16, 16, 16, 16, 16, None, None, 16, 1, 8, 1, 64, 64, 130, 1, 0, 0, None) == 3
+    assert L.smlm_b200_fwd(16, 16, 16, 16, 16, None, None, 16, 1, 8, 1, 64, 64, 130, 1, 0, 0, 0, None) == 3
     with pytest.raises(cabi.SmlmError, match="No suitable kernel"):
         cabi.check(3, "x")
 
