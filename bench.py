@@ -194,10 +194,13 @@ class Workload:
             for p in self.proj:
                 ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], self.pplan, r, part_ids=self.part_ids,
                            part_scale=self.scale, independent=self.overlap)
-            for p in self.proj:
+            for i, p in enumerate(self.proj):
+                # one workspace per projection, so that consecutive launches may overlap
+                ws = ops.wgrad_workspace(self.dev, self.tl, self.npart, r, p["h_out"], p["h_in"], slot=i)
                 ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], self.part, self.pplan, r,
                                part_ids=self.part_ids, part_scale=self.scale, n_table=self.spec["n_adapters"],
-                               accumulate=self.accumulate_grads)
+                               accumulate=self.accumulate_grads, workspace=ws,
+                               independent=self.overlap and i > 0)
 
 
 # ---------------------------------------------------------------------------
@@ -307,8 +310,11 @@ def kernel_breakdown(wl, torch, reps=5):
                 lambda p: e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
             "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": (
                 lambda p, i: ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan,
-                                         r, part_ids=wl.part_ids, part_scale=wl.scale,
-                                         n_table=wl.spec["n_adapters"]),
+                                            r, part_ids=wl.part_ids, part_scale=wl.scale,
+                                            n_table=wl.spec["n_adapters"],
+                                            workspace=ops.wgrad_workspace(wl.dev, n, wl.npart, r, p["h_out"],
+                                                                          p["h_in"], slot=i),
+                                            independent=wl.overlap and i > 0),
                 lambda p: e * (n * (p["h_in"] + p["h_out"]) + 2 * n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
         })
     out = {}

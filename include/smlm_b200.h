@@ -150,12 +150,14 @@ int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, c
  *   dB_p = scale_p * gO[rows_p]^T . V[rows_p]      dA_p = dV[rows_p]^T . X[rows_p]
  * (kernel_utils.py:144-145; dV is expected to carry the scale already, as
  * smlm_b200_bwd produces it).  Layout of dA / dB follows is_row_major like the
- * weights; part_ids (or NULL) selects the per-adapter entry of part_scale. */
+ * weights; part_ids (or NULL) selects the per-adapter entry of part_scale.
+ * `independent` as in smlm_b200_fwd, with one more condition: the call must not share
+ * its workspace with the previous kernel of the stream. */
 int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
                          const void* v, const void* go, const int32_t* part_indptr, const int32_t* part_ids,
                          const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int n_table,
                          int npart, int T, int h_in, int h_out, int rank, int dtype, int is_row_major,
-                         int accumulate, int grad_fp32, void* stream);
+                         int accumulate, int grad_fp32, int independent, void* stream);
 
 /* First half of the backward: dV = scale * gO . B (written to dv [T, rank]) and
  * dX = dV . A for the rows of every train partition (kernel_utils.py:142-143), one

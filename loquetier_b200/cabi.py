@@ -36,7 +36,7 @@ SIGNATURES = {
     "smlm_b200_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
-    "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 10 + [c_void_p]),
+    "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 11 + [c_void_p]),
     "smlm_b200_bwd": (c_int, [c_void_p] * 14 + [c_size_t] + [c_int] * 10 + [c_void_p]),
 }
 

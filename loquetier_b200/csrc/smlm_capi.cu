@@ -7,10 +7,8 @@
 #include <mutex>
 
 #include "../../include/smlm_b200.h"
-#include "smlm_expand.cuh"
 #include "smlm_fused.cuh"
 #include "smlm_plan.cuh"
-#include "smlm_shrink.cuh"
 #include "smlm_wgrad.cuh"
 
 namespace {
@@ -108,75 +106,6 @@ int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cud
   return SMLM_OK;
 }
 
-// ---- shrink -----------------------------------------------------------------
-
-template <typename T, int NT, bool RM>
-int launch_shrink(const ShrinkArgs& a, const XMaps& xm, int max_pieces, cudaStream_t stream) {
-  return launch(shrink_kernel<T, NT, RM>, dim3(max_pieces * a.ksplit, 1, 1), kShrinkThreads, a.ksplit,
-                ShrinkSmem<NT, RM>::kTotal, stream, a, xm);
-}
-
-template <typename T, bool RM>
-int dispatch_shrink_nt(const ShrinkArgs& a, const XMaps& xm, int max_pieces, cudaStream_t stream) {
-  const int nt = (a.N + 7) / 8;
-  if (nt <= 1) return launch_shrink<T, 1, RM>(a, xm, max_pieces, stream);
-  if (nt <= 2) return launch_shrink<T, 2, RM>(a, xm, max_pieces, stream);
-  if (nt <= 4) return launch_shrink<T, 4, RM>(a, xm, max_pieces, stream);
-  if (nt <= 8) return launch_shrink<T, 8, RM>(a, xm, max_pieces, stream);
-  return launch_shrink<T, 16, RM>(a, xm, max_pieces, stream);
-}
-
-int run_shrink(void* d, const void* x, const void* const* w_table, const int32_t* ids, const float* scale,
-               void* plan, int n_table, int T, int nseg, int K, int N, int dtype, int row_major,
-               cudaStream_t stream) {
-  ShrinkArgs a;
-  a.d = d; a.x = x; a.w_table = w_table; a.ids = ids; a.scale = scale;
-  a.plan = static_cast<int*>(plan);
-  a.n_table = n_table; a.N = N; a.K = K;
-  const int mp = max_pieces_of(T, nseg);
-  a.ksplit = pick_split(mp, (K + kKC - 1) / kKC);
-  XMaps xm;
-  for (int i = 0; i < 4; ++i)
-    if (!make_map_2d(&xm.m[i], x, T, K, 8 << i, dtype)) return SMLM_ERR_CUDA;
-  if (dtype == SMLM_F16)
-    return row_major ? dispatch_shrink_nt<__half, true>(a, xm, mp, stream)
-                     : dispatch_shrink_nt<__half, false>(a, xm, mp, stream);
-  return row_major ? dispatch_shrink_nt<__nv_bfloat16, true>(a, xm, mp, stream)
-                   : dispatch_shrink_nt<__nv_bfloat16, false>(a, xm, mp, stream);
-}
-
-// ---- expand -----------------------------------------------------------------
-
-template <typename T, int KT, bool RM>
-int launch_expand(const ExpandArgs& a, int max_pieces, cudaStream_t stream) {
-  return launch(expand_kernel<T, KT, RM>, dim3(max_pieces, (a.N + kNCH - 1) / kNCH, 1), kThreads, 1,
-                ExpandSmem<KT>::kTotal, stream, a);
-}
-
-template <typename T, bool RM>
-int dispatch_expand_kt(const ExpandArgs& a, int max_pieces, cudaStream_t stream) {
-  const int kt = (a.K + 15) / 16;
-  if (kt <= 1) return launch_expand<T, 1, RM>(a, max_pieces, stream);
-  if (kt <= 2) return launch_expand<T, 2, RM>(a, max_pieces, stream);
-  if (kt <= 4) return launch_expand<T, 4, RM>(a, max_pieces, stream);
-  return launch_expand<T, 8, RM>(a, max_pieces, stream);
-}
-
-int run_expand(void* d, const void* x, const void* const* w_table, const int32_t* ids, const float* scale,
-               void* plan, int n_table, int T, int nseg, int K, int N, int dtype, int row_major, int accumulate,
-               cudaStream_t stream) {
-  ExpandArgs a;
-  a.d = d; a.x = x; a.w_table = w_table; a.ids = ids; a.scale = scale;
-  a.plan = static_cast<int*>(plan);
-  a.n_table = n_table; a.N = N; a.K = K; a.accumulate = accumulate;
-  const int mp = max_pieces_of(T, nseg);
-  if (dtype == SMLM_F16)
-    return row_major ? dispatch_expand_kt<__half, true>(a, mp, stream)
-                     : dispatch_expand_kt<__half, false>(a, mp, stream);
-  return row_major ? dispatch_expand_kt<__nv_bfloat16, true>(a, mp, stream)
-                   : dispatch_expand_kt<__nv_bfloat16, false>(a, mp, stream);
-}
-
 // ---- fused shrink + expand ----------------------------------------------------
 
 template <typename T, int R16, bool RM>
@@ -197,13 +126,14 @@ int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cu
 // OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
 int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
               const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
-              int N2, int dtype, int row_major, int scale_mid, int accumulate, int independent,
+              int N2, int dtype, int row_major, int scale_mid, int accumulate, int independent, int mode,
               cudaStream_t stream) {
   FusedArgs a;
   a.out = out; a.mid = mid; a.w1_table = w1_table; a.w2_table = w2_table; a.ids = ids; a.scale = scale;
   a.plan = static_cast<int*>(plan);
   a.n_table = n_table; a.K1 = K1; a.R = R; a.N2 = N2; a.scale_mid = scale_mid; a.accumulate = accumulate;
   a.independent = independent;
+  a.mode = mode;
   const int mp = max_pieces_of(T, nseg);
   // One CTA per SM.  A piece can be split over the KS CTAs of a cluster; pick the KS that
   // minimises (waves of 148 CTAs) x (work per CTA + fixed cost of set-up and the cluster reduce).
@@ -211,13 +141,24 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   const int r16 = r16b > 4 ? 8 : (r16b > 2 ? 4 : r16b);
   const int kc = 64 * fused_chunks(r16);
   const int ksteps = (K1 + kc - 1) / kc, nslabs = (N2 + fused_slab(r16) - 1) / fused_slab(r16);
+  // Estimated launch time in microseconds for a split of k (constants fitted to device-side
+  // timelines on B200): set-up, a read phase that is bound either by the latency of its ring
+  // stages or by what one SM can ingest, the reduce across the cluster, and a write phase
+  // bound the same way.
   int ks = 1;
   double best = 1e30;
-  for (int k = 1; k <= 8; ++k) {
-    if (k > 1 && (ksteps < k || nslabs < k)) break;
+  const double stage_kb = 64.0 * kc * 2 / 1024.0 * 1.28, slab_kb = 64.0 * fused_slab(r16) * 2 / 1024.0;
+  for (int k = 1; k <= 4; ++k) {
+    if (k > 1 && ((mode != kFusedExpandOnly && ksteps < k) || (mode != kFusedShrinkOnly && nslabs < k))) break;
     const int slots = kNumSMs * fused_ctas_per_sm(r16);
-    const int waves = (std::max(mp, 1) * k + slots - 1) / slots;
-    const double cost = waves * (1.0 / k + (k > 1 ? 0.15 : 0.08));
+    const int ctas = std::max(mp, 1) * k;
+    const int waves = (ctas + slots - 1) / slots;
+    const double load = std::max(1.0, std::min<double>(ctas, slots) / kNumSMs);  // CTAs sharing one SM
+    const int nk = (ksteps + k - 1) / k, ns = (nslabs + k - 1) / k;
+    const double ph1 = mode == kFusedExpandOnly ? 0.0 : std::max(2.5 + 0.9 * nk, load * nk * stage_kb / 35.0);
+    const double ph3 = mode == kFusedShrinkOnly ? 0.0 : std::max(1.0 + 1.2 * ns, load * ns * slab_kb / 33.0);
+    const double ph2 = (k > 1 && mode != kFusedExpandOnly) ? 1.0 * k : 0.6;
+    const double cost = waves * (2.0 + ph1 + ph2 + ph3);
     if (cost < best - 1e-9) {
       best = cost;
       ks = k;
@@ -225,8 +166,14 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   }
   a.ksplit = ks;
   FusedMaps tm;
-  if (!make_map_2d(&tm.in8, in, T, K1, 8, dtype) || !make_map_2d(&tm.in16, in, T, K1, 16, dtype) ||
-      !make_map_2d(&tm.out, out, T, N2, 16, dtype))
+  // a half-only launch has no IN (expand only) or no OUT (shrink only): describe the tensor it does
+  // have in the unused slots, they are never dereferenced
+  const void* in_t = mode == kFusedExpandOnly ? out : in;
+  const int in_cols = mode == kFusedExpandOnly ? N2 : K1;
+  void* out_t = mode == kFusedShrinkOnly ? const_cast<void*>(in) : out;
+  const int out_cols = mode == kFusedShrinkOnly ? K1 : N2;
+  if (!make_map_2d(&tm.in8, in_t, T, in_cols, 8, dtype) || !make_map_2d(&tm.in16, in_t, T, in_cols, 16, dtype) ||
+      !make_map_2d(&tm.out, out_t, T, out_cols, 16, dtype))
     return SMLM_ERR_CUDA;
   if (dtype == SMLM_F16)
     return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, stream)
@@ -282,7 +229,7 @@ WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1) {
 // One launch for one or two jobs (job1 == nullptr: one).
 int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t* part_indptr, const float* scale,
               const int32_t* ids, int n_table, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
-              int R, int dtype, int accumulate, int grad_fp32, cudaStream_t stream) {
+              int R, int dtype, int accumulate, int grad_fp32, int independent, cudaStream_t stream) {
   WgradArgs a;
   WgradMaps tm;
   const int rt = wgrad_rt(R);
@@ -306,6 +253,7 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   a.tickets = static_cast<int*>(workspace);
   a.scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + sh.ticket_bytes);
   a.npart = npart; a.T = T; a.R = R; a.group = sh.group; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
+  a.independent = independent;
   if (dtype == SMLM_F16) {
     if (rt == 1) return launch_wgrad<__half, 1>(a, tm, sh.groups, stream);
     if (rt == 2) return launch_wgrad<__half, 2>(a, tm, sh.groups, stream);
@@ -429,14 +377,16 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
   if (!aligned16(y) || !aligned16(x) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   if (d_in >= d_out) {
+    // shrink: the small dimension is the output width; y plays the part of MID
     if (!small_dim_ok(d_out) || !large_dim_ok(d_in)) return SMLM_ERR_NO_KERNEL;
     if (accumulate) return SMLM_ERR_NO_KERNEL;
-    return run_shrink(y, x, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, dtype,
-                      is_row_major, st);
+    return run_fused(nullptr, y, x, w_table, nullptr, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, 64,
+                     dtype, is_row_major, 1, 0, 0, kFusedShrinkOnly, st);
   }
+  // expand: the small dimension is the input width; x plays the part of MID
   if (!small_dim_ok(d_in) || !large_dim_ok(d_out)) return SMLM_ERR_NO_KERNEL;
-  return run_expand(y, x, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, dtype,
-                    is_row_major, accumulate, st);
+  return run_fused(y, const_cast<void*>(x), nullptr, nullptr, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, 64,
+                   d_in, d_out, dtype, is_row_major, 0, accumulate, 0, kFusedExpandOnly, st);
 }
 
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
@@ -452,7 +402,7 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
   if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
   return run_fused(y, v, x, wa_table, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, h_in, rank, h_out,
-                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0,
+                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0, kFusedBoth,
                    static_cast<cudaStream_t>(stream));
 }
 
@@ -474,7 +424,7 @@ int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const in
   if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
   const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
   return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, workspace, workspace_bytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+                   rank, dtype, accumulate, grad_fp32, 0, static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
@@ -500,14 +450,14 @@ int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, c
   }
   const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
   return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, scratch, kStaticWgradBytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, st);
+                   rank, dtype, accumulate, grad_fp32, 0, st);
 }
 
 int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
                          const void* v, const void* go, const int32_t* part_indptr, const int32_t* part_ids,
                          const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int n_table,
                          int npart, int T, int h_in, int h_out, int rank, int dtype, int is_row_major,
-                         int accumulate, int grad_fp32, void* stream) {
+                         int accumulate, int grad_fp32, int independent, void* stream) {
   if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (npart == 0 || T == 0) return SMLM_OK;
@@ -520,7 +470,7 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
   const WgradJobDesc jb = {dB_table, v, go, h_out, is_row_major ? 0 : 1, part_scale != nullptr};
   const WgradJobDesc ja = {dA_table, dv, x, h_in, is_row_major ? 1 : 0, 0};
   return run_wgrad(&jb, &ja, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, static_cast<cudaStream_t>(stream));
+                   rank, dtype, accumulate, grad_fp32, independent != 0, static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
@@ -538,7 +488,7 @@ int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_t
   // [K = h_out][N = r] operand; the math layout B [r, h_out] is the column-major one.  The layout
   // flag therefore flips for both products of this launch (dX = dV . A likewise).
   return run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
-                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0,
+                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0, kFusedBoth,
                    static_cast<cudaStream_t>(stream));
 }
 
@@ -557,7 +507,7 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   // dA = dV^T . X ([r, h_in] in the PEFT layout; dV already carries the scale), in one launch
   return smlm_b200_wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, part_ids, part_scale, plan, workspace,
                               workspace_bytes, n_table, npart, T, h_in, h_out, rank, dtype, is_row_major,
-                              accumulate_grads, grad_fp32, stream);
+                              accumulate_grads, grad_fp32, 0, stream);
 }
 
 }  // extern "C"

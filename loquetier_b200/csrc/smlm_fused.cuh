@@ -8,6 +8,10 @@
 //             scale and add of MixedLoraLinear.forward, models/mixed_lora.py:214-217)
 //   backward: IN = gO, W1 = B, W2 = A, MID = dV, OUT = dX  (kernel_utils.py:142-143)
 //
+// The same kernel also runs either half alone (FusedArgs::mode), which is one call of the
+// reference operator smlm_forward_cutlass: shrink only (MID is the result) or expand only
+// (MID is the input).
+//
 // It replaces two launches of the reference's grouped GEMM
 // (kernel_src/csrc/smlm_forward/smlm_forward_cutlass.cuh:82-171) and keeps its
 // numerics: fp32 accumulation, MID rounded to the storage type before the second
@@ -103,7 +107,14 @@ struct FusedArgs {
   int scale_mid;                // 1: the scale multiplies MID (backward); 0: it multiplies OUT (forward)
   int accumulate;               // OUT += instead of OUT =
   int independent;              // 1: reads nothing the previous kernel of the stream wrote
+  int mode;                     // kFusedBoth, or one half only (one reference operator call):
+                                // kFusedShrinkOnly: MID = s * IN . W1, nothing else;
+                                // kFusedExpandOnly: OUT (+)= s * MID . W2 with MID read, not written
 };
+
+constexpr int kFusedBoth = 0;
+constexpr int kFusedShrinkOnly = 1;
+constexpr int kFusedExpandOnly = 2;
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");
@@ -151,17 +162,22 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const int K1 = a.K1, R = a.R, N2 = a.N2;
   int* err = a.plan + 1;
 
-  const T* w1 = static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
-  const T* w2 = static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
-  const bool w_ok = (w1 != nullptr) && (w2 != nullptr);
+  const int mode = a.mode;
+  const T* w1 = mode == kFusedExpandOnly
+                    ? nullptr
+                    : static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
+  const T* w2 = mode == kFusedShrinkOnly
+                    ? nullptr
+                    : static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
+  const bool w_ok = (w1 != nullptr || mode == kFusedExpandOnly) && (w2 != nullptr || mode == kFusedShrinkOnly);
   const float sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
-  const float sc_mid = a.scale_mid ? sc : 1.0f;
-  const float sc_out = a.scale_mid ? 1.0f : sc;
+  const float sc_mid = (a.scale_mid || mode == kFusedShrinkOnly) ? sc : 1.0f;
+  const float sc_out = (a.scale_mid || mode == kFusedShrinkOnly) ? 1.0f : sc;
 
   const int ksteps = (K1 + KC - 1) / KC;
   const int per = (ksteps + KS - 1) / KS;
   const int kbeg = z * per;
-  const int nk = w_ok ? max(0, min(ksteps, kbeg + per) - kbeg) : 0;
+  const int nk = (w_ok && mode != kFusedExpandOnly) ? max(0, min(ksteps, kbeg + per) - kbeg) : 0;
   // CTAs walk their K slice from different starting points so that, at any moment, the machine as
   // a whole reads many different column bands of IN (and all DRAM channels) instead of one
   const int krot = nk > 0 ? (piece_idx * 5) % nk : 0;
@@ -284,7 +300,8 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
     }
   }
   cg::cluster_group cluster = cg::this_cluster();
-  if (KS > 1) {
+  const bool reduce_cluster = KS > 1 && mode != kFusedExpandOnly;
+  if (reduce_cluster) {
     cluster_arrive();
     cluster_wait();
   } else {
@@ -300,35 +317,40 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       const int r = e / HP;
       const int n = (e - r * HP) * 2;
       const int fm = r >> 4, r16 = r & 15;
-      float2 s = make_float2(0.f, 0.f);
-      if (r < nrows && n < R && w_ok) {
-        for (int cz = 0; cz < KS; ++cz) {
-          const float* rr = KS > 1 ? cluster.map_shared_rank(red, cz) : red;
-          for (int q = 0; q < WK; ++q) {
-            const float2 p = *reinterpret_cast<const float2*>(rr + ((q * WM + fm) * 16 + r16) * KP + n);
-            s.x += p.x;
-            s.y += p.y;
+      const bool inside = r < nrows && n < R && w_ok;
+      uint32_t packed = 0;
+      if (mode == kFusedExpandOnly) {
+        if (inside) packed = *reinterpret_cast<const uint32_t*>(mrow + static_cast<size_t>(r) * R + n);
+      } else {
+        float2 s = make_float2(0.f, 0.f);
+        if (inside) {
+          for (int cz = 0; cz < KS; ++cz) {
+            const float* rr = KS > 1 ? cluster.map_shared_rank(red, cz) : red;
+            for (int q = 0; q < WK; ++q) {
+              const float2 p = *reinterpret_cast<const float2*>(rr + ((q * WM + fm) * 16 + r16) * KP + n);
+              s.x += p.x;
+              s.y += p.y;
+            }
           }
         }
+        packed = pack2<T>(s.x * sc_mid, s.y * sc_mid);
+        if (z == 0 && inside) *reinterpret_cast<uint32_t*>(mrow + static_cast<size_t>(r) * R + n) = packed;
       }
-      const uint32_t packed = pack2<T>(s.x * sc_mid, s.y * sc_mid);
       const int c = n >> 3;
       asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(mids + r * (XC * 16) + (swz<XC>(r, c) << 4) + (n & 7) * 2),
                    "r"(packed));
-      if (z == 0 && r < nrows && n < R && w_ok)
-        *reinterpret_cast<uint32_t*>(mrow + static_cast<size_t>(r) * R + n) = packed;
     }
   }
   // done reading the peers' partial sums; the matching wait sits at the very end, so that no CTA
   // leaves (and frees its shared memory) while a peer may still be reading it
-  if (KS > 1) cluster_arrive();
+  if (reduce_cluster) cluster_arrive();
   __syncthreads();  // MID is complete; the ring is free for phase 3
 
   // ======================= phase 3: expand over this CTA's N2 slice =======================
   const int nslabs = (N2 + SLAB - 1) / SLAB;
   const int sper = (nslabs + KS - 1) / KS;
   const int sbeg = z * sper;
-  const int ns = w_ok ? max(0, min(nslabs, sbeg + sper) - sbeg) : 0;
+  const int ns = (w_ok && mode != kFusedShrinkOnly) ? max(0, min(nslabs, sbeg + sper) - sbeg) : 0;
 
   if (warp < NW && ns > 0) {
     const uint32_t wslab0 = base;  // two slabs in the space the ring occupied
@@ -492,7 +514,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
     if (lane == 0) bulk_wait<0>();  // shared memory must outlive the tensor stores that read it
     __syncwarp();
   }
-  if (KS > 1) cluster_wait();
+  if (reduce_cluster) cluster_wait();
   if (a.independent) pdl_wait();
 }
 

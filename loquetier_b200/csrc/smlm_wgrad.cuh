@@ -35,7 +35,7 @@ namespace smlm {
 
 constexpr int kWgThreads = kThreads + 32;  // four consumer warps + one producer warp
 constexpr int kWgTok = 64;                 // tokens per ring stage (= one piece)
-constexpr int kWgStages = 3;
+constexpr int kWgStages = 2;               // two CTAs fit on one SM
 constexpr int kWgMaxGroup = 64;            // pieces per CTA at most
 
 // columns of Q per warp, chosen so that the accumulators stay within 64 registers
@@ -82,6 +82,8 @@ struct WgradArgs {
   int group;                   // pieces per CTA (G)
   int accumulate;              // G += instead of G =
   int out_fp32;                // G holds fp32 instead of the operand type
+  int independent;             // 1: reads nothing the previous kernel of the stream wrote, and
+                               //    shares no workspace with it
 };
 
 struct WgradMaps {
@@ -116,7 +118,9 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
   const int ncols = min(SLAB, H - col0);
   int* err = a.plan + 1;
 
-  pdl_wait();
+  // dependent launches wait for their predecessor here; independent ones overlap with it and
+  // wait just before they exit, so that completion stays in stream order
+  if (!a.independent) pdl_wait();
   pdl_trigger();
   const int count = a.plan[0];
   const int pbeg = grp * G;
@@ -147,7 +151,10 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
       }
     }
   }
-  if (np == 0) return;
+  if (np == 0) {
+    if (a.independent) pdl_wait();
+    return;
+  }
 
   if (tid < np) {
     const Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[pbeg + tid];
@@ -389,6 +396,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
       run0 = it + 1;
     }
   }
+  if (a.independent) pdl_wait();
 }
 
 }  // namespace smlm

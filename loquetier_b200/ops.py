@@ -110,16 +110,16 @@ def bwd_dx(dx, dv, go, wa_table, wb_table, plan: Plan, rank: int, is_row_major=F
 _WORKSPACES = {}
 
 
-def wgrad_workspace(device, T: int, npart: int, rank: int, h0: int, h1: int = 0) -> torch.Tensor:
+def wgrad_workspace(device, T: int, npart: int, rank: int, h0: int, h1: int = 0, slot: int = 0) -> torch.Tensor:
     """Zero-filled scratch of the weight-gradient kernels, cached per device and grown
     on demand.  The kernels leave it zeroed, so it is cleared only when (re)allocated.
     One workspace per device: calls that may overlap on different streams need their
-    own (allocate one with ``torch.zeros`` and pass it explicitly)."""
+    own: ask for a different ``slot``."""
     need = int(lib.smlm_b200_wgrad_workspace_bytes(int(T), int(npart), int(rank), int(h0), int(h1)))
-    ws = _WORKSPACES.get(device)
+    ws = _WORKSPACES.get((device, slot))
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
-        _WORKSPACES[device] = ws
+        _WORKSPACES[(device, slot)] = ws
     return ws
 
 
@@ -135,8 +135,10 @@ def wgrad(g_table, p, q, part_indptr, plan: Plan, transposed: bool, part_scale=N
 
 
 def wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, plan: Plan, rank: int, is_row_major=False,
-               part_ids=None, part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None):
-    """dA and dB of every train partition in one launch."""
+               part_ids=None, part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None,
+               independent=False):
+    """dA and dB of every train partition in one launch.  ``independent=True``: reads nothing the
+    previous kernel on the stream writes and does not share ``workspace`` with it."""
     ws = workspace if workspace is not None else wgrad_workspace(go.device, plan.T, plan.nseg, rank, go.size(1),
                                                                  x.size(1))
     with torch.cuda.device(go.device):
@@ -145,7 +147,8 @@ def wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, plan: Plan, rank: 
                                        _p(part_scale), plan.buf.data_ptr(), ws.data_ptr(), ws.numel(), int(n_table),
                                        int(part_indptr.numel()) - 1, plan.T, int(x.size(1)), int(go.size(1)),
                                        int(rank), _dtype_code(go), int(bool(is_row_major)), int(bool(accumulate)),
-                                       int(bool(grad_fp32)), _stream(go)), "smlm_b200_wgrad_pair")
+                                       int(bool(grad_fp32)), int(bool(independent)), _stream(go)),
+              "smlm_b200_wgrad_pair")
 
 
 def bwd(dx, dA_table, dB_table, dv, go, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False,
