@@ -58,6 +58,9 @@ const char* smlm_b200_status_string(int status);
  * writes into that buffer. */
 size_t smlm_b200_tmp_size(int num_problems);
 
+/* Rows per piece the plan uses for a batch of T token rows (64 at most; a multiple of 8). */
+int smlm_b200_piece_rows(int T);
+
 /* Bytes of the plan buffer for a batch of T token rows in nseg segments. */
 size_t smlm_b200_plan_bytes(int T, int nseg);
 

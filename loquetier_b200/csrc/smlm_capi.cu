@@ -16,6 +16,7 @@ namespace {
 using namespace smlm;
 
 constexpr int kNumSMs = 148;
+
 constexpr int kTargetCtas = 148 * 2;  // aim for at least two resident CTAs on each of the 148 SMs
 
 // ---- tensor maps ------------------------------------------------------------
@@ -56,7 +57,16 @@ bool make_map_2d(CUtensorMap* m, const void* base, int rows, int cols, int box_r
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-inline int max_pieces_of(int T, int nseg) { return T / kBM + nseg; }
+// Rows per piece for a batch of T rows.  The plan builder and every launch derive it from T alone,
+// so they always agree.  64 everywhere: cutting 8192 rows into 56-row pieces would give each of the
+// 148 SMs one piece of a uniform batch, but with ragged segments the remainders spill into a second
+// wave and the launch got slower (measured), so the height stays at the maximum.
+inline int piece_rows_for(int T) {
+  (void)T;
+  return kBM;
+}
+
+inline int max_pieces_of(int T, int nseg) { return T / piece_rows_for(T) + nseg; }
 
 inline int pow2_at_least(int v) {
   int p = 1;
@@ -173,7 +183,7 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   void* out_t = mode == kFusedShrinkOnly ? const_cast<void*>(in) : out;
   const int out_cols = mode == kFusedShrinkOnly ? K1 : N2;
   if (!make_map_2d(&tm.in8, in_t, T, in_cols, 8, dtype) || !make_map_2d(&tm.in16, in_t, T, in_cols, 16, dtype) ||
-      !make_map_2d(&tm.out, out_t, T, out_cols, 16, dtype))
+      !make_map_2d(&tm.out, out_t, T, out_cols, 16, dtype) || !make_map_2d(&tm.out8, out_t, T, out_cols, 8, dtype))
     return SMLM_ERR_CUDA;
   if (dtype == SMLM_F16)
     return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, stream)
@@ -310,6 +320,8 @@ extern "C" {
 
 int smlm_b200_version(void) { return 1; }
 
+int smlm_b200_piece_rows(int T) { return T < 0 ? 0 : piece_rows_for(T); }
+
 const char* smlm_b200_status_string(int status) {
   switch (status) {
     case SMLM_OK: return "ok";
@@ -345,7 +357,7 @@ int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int
   if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
   plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg));
+      static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T));
   if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
   return SMLM_OK;
 }

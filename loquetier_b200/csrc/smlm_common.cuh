@@ -13,8 +13,8 @@
 namespace smlm {
 
 constexpr int kThreads = 128;       // 4 warps per CTA in every kernel
-constexpr int kBM = 64;             // rows of one piece (a slice of one segment)
-constexpr int kPlanHeaderInts = 4;  // {count, error, max_pieces, T}
+constexpr int kBM = 64;             // most rows a piece (a slice of one segment) can have
+constexpr int kPlanHeaderInts = 4;  // {count, error, max_pieces, rows per piece}
 
 // error bits a kernel may OR into the plan header's error word
 constexpr int kErrBadIndptr = 1;    // indptr not monotone, negative or beyond T

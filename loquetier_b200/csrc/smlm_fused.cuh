@@ -61,6 +61,7 @@ struct FusedMaps {
   CUtensorMap in8;    // IN boxes of 8 rows x 64 columns (pieces of at most 8 rows)
   CUtensorMap in16;   // IN boxes of 16 rows x 64 columns
   CUtensorMap out;    // OUT boxes of 16 rows x 64 columns
+  CUtensorMap out8;   // OUT boxes of 8 rows x 64 columns (last block of a piece of 8k rows)
 };
 
 template <int R16, bool RM>
@@ -220,10 +221,11 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
   if (warp == NW) {
-    const bool small = nrows <= 8;
-    const CUtensorMap* xmap = small ? &tm.in8 : &tm.in16;
-    const uint32_t boxbytes = small ? 1024u : 2048u;
-    const int nblk = small ? 1 : ((nrows + 15) >> 4);
+    // rows are fetched in blocks of 16, the last block with the 8-row box when that covers it:
+    // nothing beyond the piece's rows (rounded up to 8) is read
+    const int nblk = (nrows + 15) >> 4;
+    const bool last8 = ((nrows - 1) & 15) < 8;
+    const uint32_t rowbytes = static_cast<uint32_t>(nblk * 16 - (last8 ? 8 : 0)) * 128u;  // per 64-column chunk
     for (int it = 0; it < nk; ++it) {
       const int slot = it % S;
       const int kstep = kbeg + (it + krot < nk ? it + krot : it + krot - nk);
@@ -235,7 +237,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       const int kcols = min(KC, K1 - k0);
       const int nch = (kcols + 63) >> 6;
       const uint32_t wbytes = static_cast<uint32_t>(kcols) * R * 2;
-      if (lane == 0) mbar_expect_tx(fb, boxbytes * nblk * nch + wbytes);
+      if (lane == 0) mbar_expect_tx(fb, rowbytes * nch + wbytes);
       __syncwarp();
       if constexpr (!RM) {
         for (int n = lane; n < R; n += 32)
@@ -245,7 +247,8 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       }
       for (int i = lane; i < nblk * nch; i += 32) {
         const int b = i / nch, c = i - b * nch;
-        tma_load_2d(xs + (b * CH + c) * 2048, xmap, k0 + c * 64, pc.row0 + b * 16, fb);
+        tma_load_2d(xs + (b * CH + c) * 2048, (last8 && b == nblk - 1) ? &tm.in8 : &tm.in16, k0 + c * 64,
+                    pc.row0 + b * 16, fb);
       }
     }
   } else {
@@ -403,7 +406,8 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       }
     }
     const int rows_here = min(16, nrows - wm * 16);
-    const bool full_block = (rows_here == 16);
+    const bool full_block = (rows_here == 16) || (rows_here == 8);
+    const CUtensorMap* omap = rows_here == 8 ? &tm.out8 : &tm.out;
     const uint32_t ostage = base + SM::kOutOff + warp * 8192;
     T* dbase = static_cast<T*>(a.out) + static_cast<size_t>(pc.row0 + wm * 16) * N2;
     int obuf = 0;
@@ -469,8 +473,8 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
             if (lane == 0) {
               for (int gi = 0; gi < ng; ++gi) {
                 const int col0 = n0 + (g0 + gi) * 64;
-                if (a.accumulate) tma_reduce_add_2d<T>(&tm.out, col0, pc.row0 + wm * 16, os + gi * 2048);
-                else tma_store_2d(&tm.out, col0, pc.row0 + wm * 16, os + gi * 2048);
+                if (a.accumulate) tma_reduce_add_2d<T>(omap, col0, pc.row0 + wm * 16, os + gi * 2048);
+                else tma_store_2d(omap, col0, pc.row0 + wm * 16, os + gi * 2048);
               }
               bulk_commit();
             }

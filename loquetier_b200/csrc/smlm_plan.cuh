@@ -1,4 +1,5 @@
-// Work-list builder: cuts every segment of a batch into pieces of at most kBM rows.
+// Work-list builder: cuts every segment of a batch into pieces of at most `bm` rows
+// (bm <= kBM, a multiple of 8, chosen by the host so that the pieces fill whole waves of SMs).
 //
 // The segment index pointer lives in device memory (the caller of the reference
 // operator passes it that way, kernel_src/csrc/loquetier_ops.cc:277-281), so the
@@ -8,7 +9,7 @@
 // (indptr, per-segment weights), but the output is a list of row ranges instead of
 // grouped-GEMM problem descriptors.
 //
-// Plan buffer layout: int header[4] = {count, error, max_pieces, T}, then
+// Plan buffer layout: int header[4] = {count, error, max_pieces, bm}, then
 // Piece[max_pieces].  An indptr that is negative, decreasing or reaches past T
 // yields count = 0 and the kErrBadIndptr bit, so that no consumer touches memory.
 #pragma once
@@ -20,7 +21,7 @@ constexpr int kPlanThreads = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restrict__ plan,
                                                                    const int32_t* __restrict__ indptr, int nseg,
-                                                                   int T, int max_pieces) {
+                                                                   int T, int max_pieces, int bm) {
   __shared__ int s_off[kPlanThreads + 1];
   __shared__ int s_warp[32];
   __shared__ int s_base;
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
       plan[0] = 0;
       plan[1] = kErrBadIndptr;
       plan[2] = max_pieces;
-      plan[3] = T;
+      plan[3] = bm;
     }
     return;
   }
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
       a = indptr[i];
       len = indptr[i + 1] - a;
     }
-    const int np = (len + kBM - 1) / kBM;
+    const int np = (len + bm - 1) / bm;
     // inclusive scan inside the warp
     int v = np;
 #pragma unroll
@@ -97,11 +98,11 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
       const int seg = base + j;
       const int sa = indptr[seg], sb = indptr[seg + 1];
       const int k = q - s_off[j];
-      const int r0 = sa + k * kBM;
+      const int r0 = sa + k * bm;
       if (out_base + q < max_pieces) {
         Piece p;
         p.row0 = r0;
-        p.nrows = min(kBM, sb - r0);
+        p.nrows = min(bm, sb - r0);
         p.seg = seg;
         p.pad = 0;
         pieces[out_base + q] = p;
@@ -116,7 +117,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
     plan[0] = total <= max_pieces ? total : 0;
     plan[1] = total <= max_pieces ? 0 : kErrBadIndptr;
     plan[2] = max_pieces;
-    plan[3] = T;
+    plan[3] = bm;
   }
 }
 

@@ -294,8 +294,9 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
       emit(i0);
     } else {
       // the partition's pieces are consecutive in the plan; which groups hold them?
-      const int first_piece = pbeg + i0 - (pcs[i0].row0 - ra) / kBM;
-      const int last_piece = first_piece + (rb - ra + kBM - 1) / kBM - 1;
+      const int bm = a.plan[3];
+      const int first_piece = pbeg + i0 - (pcs[i0].row0 - ra) / bm;
+      const int last_piece = first_piece + (rb - ra + bm - 1) / bm - 1;
       const int first_g = first_piece / G, last_g = last_piece / G;
       float* mine = a.scratch + (static_cast<size_t>(grp * 2 + (starts ? 1 : 0)) * slabs_total + slab_global) *
                                     SM::kPartialFloats + warp * kWarpFloats;

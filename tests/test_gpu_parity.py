@@ -37,11 +37,14 @@ def test_plan_pieces_bit_exact():
         plan = ops.Plan(s, T)
         n, rc = plan.status()
         assert rc == 0
+        from loquetier_b200 import cabi
+        bm = cabi.lib.smlm_b200_piece_rows(T)
+        assert 16 <= bm <= 64 and bm % 8 == 0
         want = []
         for i in range(nseg):
             a, b = int(seg[i]), int(seg[i + 1])
-            for r0 in range(a, b, 64):
-                want.append((r0, min(64, b - r0), i, 0))
+            for r0 in range(a, b, bm):
+                want.append((r0, min(bm, b - r0), i, 0))
         assert n == len(want)
         got = plan.buf[4:4 + 4 * n].cpu().view(-1, 4).tolist()
         assert [tuple(g) for g in got] == want
