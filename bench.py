@@ -168,6 +168,9 @@ class Workload:
         self.ops = ops
         self.accumulate_grads = False
         self.overlap = True
+        self.n_streams = 3
+        self.side = []
+        self.torch = torch
 
     def build_plans(self):
         self.plan = self.ops.Plan(self.seg, self.T)
@@ -187,50 +190,83 @@ class Workload:
         ops = self.ops
         self.build_plans()
         r = self.spec["rank"]
+        torch = self.torch
+        main = torch.cuda.current_stream()
+        ns = max(0, min(self.n_streams, len(self.proj))) if self.tl else 0
+        if len(self.side) < ns:
+            self.side = [torch.cuda.Stream() for _ in range(ns)]
+        if ns:
+            fork = torch.cuda.Event()
+            fork.record(main)
+            for s in self.side[:ns]:
+                s.wait_event(fork)
+        # forward chain on the calling stream
+        done = []
         for i, p in enumerate(self.proj):
             ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], self.plan, r, seg_ids=self.ids,
                     seg_scale=self.scale, independent=self.overlap and i > 0)
+            if ns:
+                ev = torch.cuda.Event()
+                ev.record(main)
+                done.append(ev)
         if self.tl:
-            for p in self.proj:
-                ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], self.pplan, r, part_ids=self.part_ids,
-                           part_scale=self.scale, independent=self.overlap)
+            # The backward launches are small (2048 rows) and a stream keeps at most two kernels in
+            # flight, so the projections are dealt over a few side streams that run next to the
+            # forward chain.  dV/dX of a projection needs nothing from its forward; the weight
+            # gradients need v (forward) and dV, so they wait for that projection's forward.
             for i, p in enumerate(self.proj):
-                # one workspace per projection, so that consecutive launches may overlap
-                ws = ops.wgrad_workspace(self.dev, self.tl, self.npart, r, p["h_out"], p["h_in"], slot=i)
-                ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], self.part, self.pplan, r,
-                               part_ids=self.part_ids, part_scale=self.scale, n_table=self.spec["n_adapters"],
-                               accumulate=self.accumulate_grads, workspace=ws,
-                               independent=self.overlap and i > 0)
-
+                s = self.side[i % ns] if ns else main
+                with torch.cuda.stream(s):
+                    ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], self.pplan, r, part_ids=self.part_ids,
+                               part_scale=self.scale, independent=self.overlap and ns > 0 and i >= ns)
+                    if ns:
+                        s.wait_event(done[i])
+                    # one workspace per projection: launches of different streams run side by side
+                    ws = ops.wgrad_workspace(self.dev, self.tl, self.npart, r, p["h_out"], p["h_in"], slot=i)
+                    ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], self.part, self.pplan, r,
+                                   part_ids=self.part_ids, part_scale=self.scale,
+                                   n_table=self.spec["n_adapters"], accumulate=self.accumulate_grads,
+                                   workspace=ws)
+            for s in self.side[:ns]:
+                main.wait_stream(s)
 
 # ---------------------------------------------------------------------------
 # timing helpers
 # ---------------------------------------------------------------------------
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
-    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs; only samples
+    whose timestamp falls between mark_start() and mark_end() are used."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index):
         self.index = index
         self.proc = None
+        self.t0 = self.t1 = None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
         return self
 
+    def mark_start(self):
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
+
     def __exit__(self, *a):
+        import datetime
         self.result = dict(sm_mhz=None, sm_max_mhz=None, reasons=[])
         if self.proc is None:
             return
-        time.sleep(0.15)
+        time.sleep(0.1)
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
@@ -241,13 +277,16 @@ class ClockSampler:
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.strip().splitlines():
             f = [v.strip() for v in line.split(",")]
-            if len(f) < 7:
+            if len(f) < 8:
                 continue
             try:
-                sm.append(float(f[0])); mx.append(float(f[1]))
+                ts = datetime.datetime.strptime(f[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                if self.t0 is not None and self.t1 is not None and not (self.t0 - 0.02 <= ts <= self.t1 + 0.02):
+                    continue
+                sm.append(float(f[1])); mx.append(float(f[2]))
             except ValueError:
                 continue
-            for nm, v in zip(names, f[3:7]):
+            for nm, v in zip(names, f[4:8]):
                 if v.lower().startswith("active"):
                     reasons.add(nm)
         if sm:
@@ -255,7 +294,7 @@ class ClockSampler:
                                samples=len(sm))
 
 
-def timed(fn, steps, warmup, torch, dist=None):
+def timed(fn, steps, warmup, torch, dist=None, clk=None):
     """W untimed + K timed iterations bracketed by barrier + synchronize; device
     time from CUDA events on the current stream; max over ranks."""
     for _ in range(warmup):
@@ -265,11 +304,15 @@ def timed(fn, steps, warmup, torch, dist=None):
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if clk is not None:
+        clk.mark_start()
     e0.record()
     for _ in range(steps):
         fn()
     e1.record()
     torch.cuda.synchronize()
+    if clk is not None:
+        clk.mark_end()
     if dist is not None:
         dist.barrier()
     ms = e0.elapsed_time(e1)
@@ -458,7 +501,7 @@ def run_cpu(spec, torch, budget_s=12.0, max_reps=5):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
@@ -466,6 +509,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="do not mark launches independent of each other")
+    ap.add_argument("--streams", type=int, default=3, help="streams the backward launches are dealt over")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-kernel-class timing pass")
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
@@ -521,6 +565,7 @@ def main():
 
     wl = Workload(spec, dev)
     wl.overlap = not a.no_overlap
+    wl.n_streams = a.streams
     bucket = None
     if a.workload == "c5":
         # data-parallel fine-tuning: dA/dB of all adapters live in one flat bucket that the backward
@@ -562,7 +607,8 @@ def main():
         step_fn = eager_step
 
     with ClockSampler(local) as clk:
-        ms = timed(step_fn, a.steps, a.warmup, torch, dist)
+        time.sleep(0.3)  # let the sampler come up so that its samples fall inside the timed region
+        ms = timed(step_fn, a.steps, a.warmup, torch, dist, clk)
     tokens_all = T * world
     value = tokens_all / (ms * 1e-3)
 
