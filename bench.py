@@ -40,6 +40,11 @@ if ROOT not in sys.path:
 
 SCALE = 2.0  # alpha / r of the reference's fine-tune configuration (16 / 8)
 
+# DRAM bytes (read + written during the launch) per algorithmic byte of the forward fused launch, from
+# the ncu capture summarised in profiles/fused_kernel_c3_q_proj.md: (70.82 + 9.56) MB / 138.7 MB.  Part of
+# the freshly written output is still dirty in L2 when the launch ends, hence a ratio below one.
+TRAFFIC_PER_ALGORITHMIC_BYTE = 0.58
+
 
 # ---------------------------------------------------------------------------
 # workloads
@@ -632,7 +637,8 @@ def main():
         t_ms, nbytes, nl = kb[top]
         ach = nbytes / (t_ms * 1e-3) / 1e9
         line["roofline"] = dict(bound="hbm", kernel=top, achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
-                                peak_source=which, traffic=None, launches_per_step=nl,
+                                peak_source=which, traffic=(ach and nbytes / nl * TRAFFIC_PER_ALGORITHMIC_BYTE) if top.startswith('fused_kernel(fwd') else None,
+                                launches_per_step=nl,
                                 avg_launch_us=t_ms * 1e3 / nl, algorithmic_bytes_per_launch=nbytes / nl)
         line["kernels"] = {k: dict(ms_per_step=v[0], gbs=v[1] / (v[0] * 1e-3) / 1e9, frac=v[1] / (v[0] * 1e-3) / 1e9 / peak,
                                    share=v[0] / sum(x[0] for x in kb.values())) for k, v in kb.items()}
