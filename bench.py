@@ -64,7 +64,7 @@ def zipf_lengths(seed, total, a=1.2, lo=1, hi=2048):
 def workload_spec(name, rank=0, world=1):
     """Returns dict(projections=[(name, h_in, h_out)], lens, ft (bool per segment),
     ids, n_adapters, rank, dtype).  Row order: fine-tune segments, then the rest."""
-    k = {"c2": 2, "c3": 3, "c4": 4, "c5": 5}[name]
+    k = {"c2": 2, "c3": 3, "c4": 4, "c4s": 4, "c5": 5}[name]
     seed = 1000 * k + rank
     rng = np.random.default_rng(seed)
     if name == "c2":
@@ -90,7 +90,7 @@ def workload_spec(name, rank=0, world=1):
         n_ad, r, dt = 128, 16, "bf16"
         proj = [("q_proj", 4096, 4096), ("k_proj", 4096, 1024), ("v_proj", 4096, 1024), ("o_proj", 4096, 4096),
                 ("gate_proj", 4096, 14336), ("up_proj", 4096, 14336), ("down_proj", 14336, 4096)]
-    elif name == "c4":
+    elif name in ("c4", "c4s"):
         lens = [1] * 1024
         ft = [False] * 1024
         n_ad, r, dt = 256, 32, "bf16"
@@ -106,6 +106,18 @@ def workload_spec(name, rank=0, world=1):
         # a rank only receives segments of the adapters it owns: a mod world == rank
         owned = np.arange(rank, n_ad, world)
         ids = [int(v) for v in owned[rng.integers(0, len(owned), size=len(lens))]]
+    if name == "c4s":
+        # the same decode tokens in the order the reference's batch assembler produces: decode requests
+        # sorted by adapter, equal neighbours merged into one segment (model_generation.py:186, 267-273)
+        ids = sorted(ids)
+        merged_ids, merged_lens = [], []
+        for a_ in ids:
+            if merged_ids and merged_ids[-1] == a_:
+                merged_lens[-1] += 1
+            else:
+                merged_ids.append(a_)
+                merged_lens.append(1)
+        ids, lens, ft = merged_ids, merged_lens, [False] * len(merged_ids)
     return dict(name=name, projections=proj, lens=lens, ft=ft, ids=ids, n_adapters=n_ad, rank=r, dtype=dt,
                 seed=seed)
 
@@ -508,7 +520,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -538,6 +550,8 @@ def main():
         "c3": "Llama-3-8B 7 LoRA projections of one layer, bf16, rank 16, 128 adapters, 8192 tokens, "
               "Zipf(1.2) segment lengths in [1,2048], 25% fine-tune tokens (fwd+bwd), rest forward only",
         "c4": "decode sweep, bf16, 1024 one-token segments, 256 adapters, rank 32, 4096->11008 and 11008->4096",
+        "c4s": "decode sweep as c4 with the tokens sorted by adapter and merged into segments, as the "
+               "reference's batch assembler orders decode requests",
         "c5": "fine-tune heavy, bf16, rank 64, 64 adapters, 16x2048 FT tokens per GPU, 4096<->14336, "
               "dA/dB all-reduced over NCCL"}[a.workload],
         tokens_per_gpu=T, segments=len(spec["lens"]), finetune_tokens=sum(l for l, f in zip(spec["lens"], spec["ft"]) if f),

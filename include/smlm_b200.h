@@ -58,6 +58,16 @@ const char* smlm_b200_status_string(int status);
  * writes into that buffer. */
 size_t smlm_b200_tmp_size(int num_problems);
 
+/* Segment bookkeeping on the device: the run-length merge of the ordered requests of a step into
+ * segments, bit-identical to the reference's host loop (src/loquetier_src/model_generation.py:267-283:
+ * neighbours with the same adapter become one segment; `segment` = cumsum of the lengths with a
+ * leading 0, int32).  req_ids / req_len: adapter id and token count per request in batch row order,
+ * n entries.  Outputs have n (seg_ids, seg_len) and n + 1 (seg_indptr) entries; entries past the
+ * number of segments are empty segments, so (seg_indptr, nseg = n) can be handed to smlm_b200_plan
+ * without reading nseg_out[0] back.  Stream-ordered; can be captured in a CUDA graph. */
+int smlm_b200_merge_segments(const int32_t* req_ids, const int32_t* req_len, int n, int32_t* seg_ids,
+                             int32_t* seg_len, int32_t* seg_indptr, int32_t* nseg_out, void* stream);
+
 /* Rows per piece the plan uses for a batch of T token rows (64 at most; a multiple of 8). */
 int smlm_b200_piece_rows(int T);
 

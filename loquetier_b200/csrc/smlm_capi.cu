@@ -8,6 +8,7 @@
 
 #include "../../include/smlm_b200.h"
 #include "smlm_fused.cuh"
+#include "smlm_merge.cuh"
 #include "smlm_plan.cuh"
 #include "smlm_wgrad.cuh"
 
@@ -358,6 +359,18 @@ int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int
   if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
   plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T));
+  if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
+  return SMLM_OK;
+}
+
+int smlm_b200_merge_segments(const int32_t* req_ids, const int32_t* req_len, int n, int32_t* seg_ids,
+                             int32_t* seg_len, int32_t* seg_indptr, int32_t* nseg_out, void* stream) {
+  if (n < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (seg_indptr == nullptr || nseg_out == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  if (n > 0 && (req_ids == nullptr || req_len == nullptr || seg_ids == nullptr || seg_len == nullptr))
+    return SMLM_ERR_INVALID_ARGUMENT;
+  merge_segments_kernel<<<1, kMergeThreads, 0, static_cast<cudaStream_t>(stream)>>>(req_ids, req_len, n, seg_ids,
+                                                                                  seg_len, seg_indptr, nseg_out);
   if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
   return SMLM_OK;
 }

@@ -66,3 +66,23 @@ def build_segment_batch(ordered: Sequence[SegmentRequest], device) -> SegmentBat
     segment = torch.tensor(seg_host, dtype=torch.int32, device=device)
     train_idx = [r.lora_id for r in ordered if r.status == InferStatus.Train]
     return SegmentBatch(ids, lora_len, segment, train_idx, int(seg_host[-1]))
+
+
+def merge_segments_device(req_ids: torch.Tensor, req_len: torch.Tensor):
+    """The run-length merge on the GPU: ``req_ids`` / ``req_len`` are int32 device tensors with one
+    entry per request in batch row order.  Returns (seg_ids, seg_len, segment, nseg) as device
+    tensors of n, n, n + 1 and 1 entries; entries past ``nseg`` describe empty segments, so the
+    padded arrays can be used as they are (no read-back, graph-capturable)."""
+    from .cabi import check, lib
+    assert req_ids.is_cuda and req_ids.dtype == torch.int32 and req_len.dtype == torch.int32
+    n = int(req_ids.numel())
+    dev = req_ids.device
+    seg_ids = torch.empty(n, dtype=torch.int32, device=dev)
+    seg_len = torch.empty(n, dtype=torch.int32, device=dev)
+    segment = torch.empty(n + 1, dtype=torch.int32, device=dev)
+    nseg = torch.empty(1, dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        check(lib.smlm_b200_merge_segments(req_ids.data_ptr(), req_len.data_ptr(), n, seg_ids.data_ptr(),
+                                           seg_len.data_ptr(), segment.data_ptr(), nseg.data_ptr(),
+                                           torch.cuda.current_stream(dev).cuda_stream), "smlm_b200_merge_segments")
+    return seg_ids, seg_len, segment, nseg

@@ -145,3 +145,30 @@ def test_add_lora_signature_and_return_structure():
     y2 = add_lora.apply((T, h_out), x2, wa_ptr, wb_ptr, s, r, 0, [])
     y2.sum().backward()
     assert x2.grad is None or (x2.grad == 0).all()
+
+
+def test_linear_forward_replays_inside_a_cuda_graph():
+    """The inference path allocates through torch and launches stream-ordered kernels only, so the
+    whole LoRA linear can be captured once and replayed on new inputs."""
+    z = load_npz("linear_ragged_bf16")
+    lin, _ = _build_linear(z, None, z["dtype"])
+    x_static = z["x"].to(DEV).clone()
+    with torch.no_grad():
+        lin(x_static)                                    # builds the per-step device state
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            lin(x_static)
+        torch.cuda.current_stream().wait_stream(side)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            y_static = lin(x_static)
+        g.replay()
+        torch.cuda.synchronize()
+        assert_close(y_static, z["y"], what="replay 1")
+        x2 = (z["x"].float() * 0.5).to(z["dtype"])
+        x_static.copy_(x2.to(DEV))
+        g.replay()
+        torch.cuda.synchronize()
+        want = lin(x2.to(DEV))
+        assert torch.equal(y_static, want)

@@ -310,3 +310,39 @@ def test_independent_launches_match_serial_ones():
     for a, b in zip(outs[False], outs[True]):
         assert torch.equal(a, b)
     assert float(outs[True][0].abs().max()) > 0
+
+
+def test_device_segment_merge_is_bit_exact():
+    """Integer bookkeeping on the device against the oracle's merge (and through it the reference's)."""
+    from loquetier_b200.segments import merge_segments_device
+    rng = np.random.default_rng(5)
+    for n in (1, 2, 37, 1024, 1025, 3000):
+        ids = rng.integers(0, 6, size=n)
+        if n > 40:
+            ids = np.sort(ids) if n % 2 else ids       # long runs and short runs
+        lens = rng.integers(1, 50, size=n)
+        want_ids, want_lens, want_seg = O.merge_segments(list(zip(ids.tolist(), lens.tolist())))
+        si, sl, sp, ns = merge_segments_device(torch.tensor(ids, dtype=torch.int32, device="cuda"),
+                                               torch.tensor(lens, dtype=torch.int32, device="cuda"))
+        k = int(ns.item())
+        assert k == len(want_ids)
+        assert si[:k].tolist() == want_ids and sl[:k].tolist() == want_lens and sp[:k + 1].tolist() == want_seg
+        # the padding is made of empty segments
+        assert (sl[k:] == 0).all() and (sp[k:] == want_seg[-1]).all()
+    # the padded arrays drive the kernels directly
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    c = _case(9, [5, 40, 3, 70], 3, 256, 384, 16, torch.bfloat16, ids=[1, 1, 0, 2])
+    d = to_dev(c)
+    si, sl, sp, ns = merge_segments_device(torch.tensor([1, 1, 0, 2], dtype=torch.int32, device="cuda"),
+                                           torch.tensor([5, 40, 3, 70], dtype=torch.int32, device="cuda"))
+    T = 118
+    plan = ops.Plan(sp, T)
+    y = torch.zeros((T, 384), dtype=torch.bfloat16, device=dev())
+    v = torch.zeros((T, 16), dtype=torch.bfloat16, device=dev())
+    ops.fwd(y, d["x"], v, ptr_table(d["wa_d"]), ptr_table(d["wb_d"]), plan, 16, seg_ids=si)
+    torch.cuda.synchronize()
+    plan.raise_if_failed()
+    from gpu_util import oracle_forward
+    y_ref, _ = oracle_forward(c)
+    assert_close(y, y_ref, what="y through device-merged segments")
