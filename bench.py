@@ -73,7 +73,9 @@ def workload_spec(name, rank=0, world=1):
         n_ad, r, dt = 32, 16, "fp16"
         proj = [("q_proj", 4096, 4096)]
     elif name == "c3":
-        raw = zipf_lengths(seed, 8192)
+        # the segment lengths are the same on every rank (weak scaling: per-GPU work is fixed);
+        # adapter ids and tensor values differ per rank
+        raw = zipf_lengths(1000 * k, 8192)
         # mark fine-tune segments in generation order until 2048 tokens, splitting the crossing one
         ft_lens, inf_lens, acc = [], [], 0
         for n in raw:

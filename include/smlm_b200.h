@@ -71,6 +71,14 @@ int smlm_b200_merge_segments(const int32_t* req_ids, const int32_t* req_len, int
 /* Rows per piece the plan uses for a batch of T token rows (64 at most; a multiple of 8). */
 int smlm_b200_piece_rows(int T);
 
+/* Kernel choice for ranks above 32 in smlm_b200_fwd / smlm_b200_bwd_dx / smlm_b200_bwd.  No
+ * reference counterpart (the reference has one CUTLASS grouped GEMM per product).  mode 0 (default):
+ * the tcgen05 kernel with 128-row tiles is used for batches of long segments, the mma.sync kernel
+ * with 64-row tiles otherwise; mode > 0: the tcgen05 kernel wherever it applies; mode < 0: never.
+ * Process-wide; returns the previous mode.  Both kernels compute the same function (fp32
+ * accumulation, V rounded to the storage type between the products). */
+int smlm_b200_set_tensor_core_mode(int mode);
+
 /* Bytes of the plan buffer for a batch of T token rows in nseg segments. */
 size_t smlm_b200_plan_bytes(int T, int nseg);
 

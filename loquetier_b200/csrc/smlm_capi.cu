@@ -4,10 +4,12 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/smlm_b200.h"
 #include "smlm_fused.cuh"
+#include "smlm_fused_tc.cuh"
 #include "smlm_merge.cuh"
 #include "smlm_plan.cuh"
 #include "smlm_wgrad.cuh"
@@ -68,6 +70,7 @@ inline int piece_rows_for(int T) {
 }
 
 inline int max_pieces_of(int T, int nseg) { return T / piece_rows_for(T) + nseg; }
+inline int max_tall_pieces_of(int T, int nseg) { return T / (2 * piece_rows_for(T)) + nseg; }
 
 inline int pow2_at_least(int v) {
   int p = 1;
@@ -134,6 +137,31 @@ int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cu
   return launch_fused<T, 8, RM>(a, tm, max_pieces, stream);
 }
 
+// ---- the tcgen05 variant for ranks above 32 ----------------------------------
+// 0: chosen by shape, 1: wherever the kernel applies, -1: never
+std::atomic<int> g_tensor_core_mode{0};
+
+template <typename T, int R16, bool RM>
+int launch_tc(const TcArgs& a, const TcMaps& tm, int max_tall, cudaStream_t stream) {
+  return launch(fused_tc_kernel<T, R16, RM>, dim3(max_tall, 1, 1), kTcThreads, 1, TcSmem<R16>::kTotal, stream, a, tm);
+}
+
+template <typename T, bool RM>
+int dispatch_tc(const TcArgs& a, const TcMaps& tm, int max_tall, cudaStream_t stream) {
+  if (a.R <= 64) return launch_tc<T, 4, RM>(a, tm, max_tall, stream);
+  return launch_tc<T, 8, RM>(a, tm, max_tall, stream);
+}
+
+// The 128-row MMA tile pays off when segments are long enough to fill it and the batch has
+// enough of them for every SM; short ragged segments stay on the 64-row mma.sync kernel.
+inline bool use_tensor_core_kernel(int T, int nseg, int R, int mode) {
+  if (mode != kFusedBoth || R <= 32) return false;
+  const int m = g_tensor_core_mode.load(std::memory_order_relaxed);
+  if (m < 0) return false;
+  if (m > 0) return true;
+  return T >= 128 * 96 && T / std::max(nseg, 1) >= 96;
+}
+
 // OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
 int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
               const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
@@ -145,6 +173,21 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   a.n_table = n_table; a.K1 = K1; a.R = R; a.N2 = N2; a.scale_mid = scale_mid; a.accumulate = accumulate;
   a.independent = independent;
   a.mode = mode;
+  if (use_tensor_core_kernel(T, nseg, R, mode)) {
+    TcArgs t;
+    t.out = out; t.mid = mid; t.w1_table = w1_table; t.w2_table = w2_table; t.ids = ids; t.scale = scale;
+    t.plan = static_cast<int*>(plan);
+    t.n_table = n_table; t.K1 = K1; t.R = R; t.N2 = N2; t.scale_mid = scale_mid; t.accumulate = accumulate;
+    t.independent = independent;
+    TcMaps m;
+    if (!make_map_2d(&m.in16, in, T, K1, 16, dtype) || !make_map_2d(&m.out16, out, T, N2, 16, dtype))
+      return SMLM_ERR_CUDA;
+    const int mt = max_tall_pieces_of(T, nseg);
+    if (dtype == SMLM_F16)
+      return row_major ? dispatch_tc<__half, true>(t, m, mt, stream) : dispatch_tc<__half, false>(t, m, mt, stream);
+    return row_major ? dispatch_tc<__nv_bfloat16, true>(t, m, mt, stream)
+                     : dispatch_tc<__nv_bfloat16, false>(t, m, mt, stream);
+  }
   const int mp = max_pieces_of(T, nseg);
   // One CTA per SM.  A piece can be split over the KS CTAs of a cluster; pick the KS that
   // minimises (waves of 148 CTAs) x (work per CTA + fixed cost of set-up and the cluster reduce).
@@ -350,7 +393,8 @@ size_t smlm_b200_tmp_size(int num_problems) {
 
 size_t smlm_b200_plan_bytes(int T, int nseg) {
   if (T < 0 || nseg < 0) return 0;
-  return sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_pieces_of(T, nseg) + 1);
+  return sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_pieces_of(T, nseg) + 1) +
+         sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_tall_pieces_of(T, nseg) + 1);
 }
 
 int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int nseg, int T, void* stream) {
@@ -358,7 +402,8 @@ int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int
   if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
   plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T));
+      static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T),
+      max_tall_pieces_of(T, nseg));
   if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
   return SMLM_OK;
 }
@@ -412,6 +457,11 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
   if (!small_dim_ok(d_in) || !large_dim_ok(d_out)) return SMLM_ERR_NO_KERNEL;
   return run_fused(y, const_cast<void*>(x), nullptr, nullptr, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, 64,
                    d_in, d_out, dtype, is_row_major, 0, accumulate, 0, kFusedExpandOnly, st);
+}
+
+int smlm_b200_set_tensor_core_mode(int mode) {
+  const int m = mode > 0 ? 1 : (mode < 0 ? -1 : 0);
+  return g_tensor_core_mode.exchange(m, std::memory_order_relaxed);
 }
 
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,

@@ -10,8 +10,11 @@
 // grouped-GEMM problem descriptors.
 //
 // Plan buffer layout: int header[4] = {count, error, max_pieces, bm}, then
-// Piece[max_pieces].  An indptr that is negative, decreasing or reaches past T
-// yields count = 0 and the kErrBadIndptr bit, so that no consumer touches memory.
+// Piece[max_pieces + 1]; after it a second list of the same form cut at twice the
+// height (its error word is unused: faults are always recorded in the first header).
+// The tall list feeds the tcgen05 kernel, whose MMA tile is 128 rows.  An indptr that
+// is negative, decreasing or reaches past T yields count = 0 in both lists and the
+// kErrBadIndptr bit, so that no consumer touches memory.
 #pragma once
 #include "smlm_common.cuh"
 
@@ -21,13 +24,13 @@ constexpr int kPlanThreads = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restrict__ plan,
                                                                    const int32_t* __restrict__ indptr, int nseg,
-                                                                   int T, int max_pieces, int bm) {
+                                                                   int T, int max_pieces, int bm, int max_pieces2) {
   __shared__ int s_off[kPlanThreads + 1];
   __shared__ int s_warp[32];
   __shared__ int s_base;
   __shared__ int s_bad;
   const int tid = threadIdx.x;
-  Piece* pieces = reinterpret_cast<Piece*>(plan + kPlanHeaderInts);
+  int* const plan0 = plan;
 
   if (tid == 0) {
     s_bad = 0;
@@ -48,9 +51,24 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
       plan[1] = kErrBadIndptr;
       plan[2] = max_pieces;
       plan[3] = bm;
+      int* second = plan + kPlanHeaderInts + 4 * (max_pieces + 1);
+      second[0] = 0;
+      second[1] = 0;
+      second[2] = max_pieces2;
+      second[3] = 2 * bm;
     }
     return;
   }
+
+  for (int list = 0; list < 2; ++list) {
+  if (list == 1) {
+    plan = plan0 + kPlanHeaderInts + 4 * (max_pieces + 1);
+    bm *= 2;
+    max_pieces = max_pieces2;
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+  }
+  Piece* pieces = reinterpret_cast<Piece*>(plan + kPlanHeaderInts);
 
   // pass 2: 1024 segments at a time: scan the piece counts, then let every
   // thread emit pieces of the chunk by position
@@ -115,10 +133,13 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
   if (tid == 0) {
     const int total = s_base;
     plan[0] = total <= max_pieces ? total : 0;
-    plan[1] = total <= max_pieces ? 0 : kErrBadIndptr;
+    if (list == 0) plan[1] = total <= max_pieces ? 0 : kErrBadIndptr;
+    else plan[1] = 0;
     plan[2] = max_pieces;
     plan[3] = bm;
   }
+  __syncthreads();
+  }  // list
 }
 
 }  // namespace smlm

@@ -70,6 +70,12 @@ class Plan:
         check(rc, "smlm plan")
 
 
+def set_tensor_core_mode(mode: int) -> int:
+    """Kernel choice for ranks above 32: 0 by shape (default), 1 the tcgen05 kernel wherever it
+    applies, -1 never.  Returns the previous mode."""
+    return int(lib.smlm_b200_set_tensor_core_mode(int(mode)))
+
+
 def gemm(y, x, w_table, plan: Plan, is_row_major=False, seg_ids=None, seg_scale=None, accumulate=False):
     """One segmented GEMM (one reference operator call)."""
     with torch.cuda.device(x.device):

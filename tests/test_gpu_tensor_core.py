@@ -1,0 +1,128 @@
+"""GPU parity of the tcgen05 kernel (ranks above 32, 128-row tiles) against the CPU oracle and
+against the mma.sync kernel, through the C ABI.  The kernel is forced on so that small and
+ragged batches reach it.  Tolerance as for the other kernels: rtol 1e-2, atol 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close
+from oracle import smlm_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+TALL_LENS = [0, 1, 127, 128, 129, 0, 300, 64, 15, 1, 256]
+
+
+@pytest.fixture(autouse=True)
+def forced_tensor_core_kernel():
+    from loquetier_b200 import ops
+    prev = ops.set_tensor_core_mode(1)
+    yield
+    ops.set_tensor_core_mode(prev)
+
+
+def _case(seed, lens, n_ad, h_in, h_out, rank, dtype, rm=False, ids=None):
+    rng = np.random.default_rng(seed)
+    ids = list(rng.integers(0, n_ad, size=len(lens))) if ids is None else ids
+    return O.make_case(seed, lens, [int(i) for i in ids], n_ad, h_in, h_out, rank, dtype, is_row_major=rm)
+
+
+def test_first_light_rank64():
+    from gpu_util import check_forward
+    check_forward(_case(1, [128], 1, 256, 128, 64, torch.bfloat16, False, ids=[0]))
+    check_forward(_case(2, [128, 40], 2, 512, 256, 64, torch.bfloat16, False))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rm", [False, True])
+@pytest.mark.parametrize("rank", [40, 64, 96, 128])
+def test_forward_edge_lengths(dtype, rm, rank):
+    from gpu_util import check_forward
+    check_forward(_case(400 + rank, TALL_LENS, 5, 200, 328, rank, dtype, rm))
+
+
+@pytest.mark.parametrize("h_in,h_out", [(4096, 1024), (1000, 264), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("rm", [False, True])
+def test_forward_shapes(h_in, h_out, rm):
+    from gpu_util import check_forward
+    c = _case(17, [200, 1, 3, 130, 128], 4, h_in, h_out, 64, torch.bfloat16, rm)
+    check_forward(c)
+    check_forward(c, indexed=True)
+
+
+def test_forward_scale_and_accumulate():
+    from gpu_util import check_forward
+    c = _case(18, [140, 1, 290, 17], 3, 512, 776, 64, torch.bfloat16)
+    g = torch.Generator().manual_seed(1)
+    y0 = torch.randn((sum(c["lens"]), 776), generator=g).to(torch.bfloat16)
+    check_forward(c, scale=[2.0, 0.5, 1.25])
+    check_forward(c, scale=[2.0, 0.5, 1.25], indexed=True, accumulate=True, y_init=y0)
+
+
+def test_rows_outside_segments_untouched_and_deterministic():
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    c = to_dev(_case(19, [133, 1, 164], 3, 256, 384, 64, torch.float16))
+    T = 310
+    x = torch.randn((T, 256), device=dev(), dtype=torch.float16)
+    seg = torch.tensor([4, 137, 138, 302], dtype=torch.int32, device=dev())
+    plan = ops.Plan(seg, T)
+    wa = ptr_table([c["wa_d"][i] for i in c["ids"]])
+    wb = ptr_table([c["wb_d"][i] for i in c["ids"]])
+    outs = []
+    for _ in range(2):
+        y = torch.full((T, 384), 7.0, dtype=torch.float16, device=dev())
+        v = torch.full((T, 64), 3.0, dtype=torch.float16, device=dev())
+        ops.fwd(y, x, v, wa, wb, plan, 64)
+        outs.append((y.clone(), v.clone()))
+    torch.cuda.synchronize()
+    plan.raise_if_failed()
+    y, v = outs[0]
+    assert (y[:4] == 7).all() and (y[302:] == 7).all() and (v[:4] == 3).all() and (v[302:] == 3).all()
+    assert not (y[4:302] == 7).all()
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_matches_the_mma_sync_kernel():
+    from gpu_util import run_forward
+    from loquetier_b200 import ops
+    c = _case(20, [300, 128, 77], 3, 1024, 640, 64, torch.bfloat16)
+    y_tc, v_tc = run_forward(c)
+    ops.set_tensor_core_mode(-1)
+    y_mma, v_mma = run_forward(c)
+    assert_close(v_tc, v_mma.to(torch.float32), rtol=1e-2, atol=1e-2, what="v")
+    assert_close(y_tc, y_mma.to(torch.float32), rtol=1e-2, atol=1e-2, what="y")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rm", [False, True])
+@pytest.mark.parametrize("rank", [64, 128])
+def test_backward_vs_oracle(dtype, rm, rank):
+    from test_gpu_parity import _grad_close, _oracle_bwd, _run_bwd
+    part = [0, 133, 133, 330, 331, 600]
+    c = _case(500 + rank, [610], 5, 264, 200, rank, dtype, rm, ids=[0])
+    dx, dA, dB = _run_bwd(c, part)
+    gx, gA, gB = _oracle_bwd(c, part)
+    _grad_close(dx[:600], gx[:600], "dX")
+    assert (dx[600:] == 0).all()
+    for p in range(5):
+        _grad_close(dA[p], gA[p], f"dA{p}")
+        _grad_close(dB[p], gB[p], f"dB{p}")
+
+
+def test_bad_adapter_pointer_is_reported_not_dereferenced():
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import cabi, ops
+    c = to_dev(_case(21, [150, 20], 2, 256, 256, 64, torch.bfloat16))
+    T = 170
+    plan = ops.Plan(c["seg_d"], T)
+    wa = ptr_table([c["wa_d"][i] for i in c["ids"]])
+    wb = ptr_table([c["wb_d"][i] for i in c["ids"]])
+    wb[1] = 0
+    y = torch.zeros((T, 256), dtype=torch.bfloat16, device=dev())
+    v = torch.zeros((T, 64), dtype=torch.bfloat16, device=dev())
+    ops.fwd(y, c["x"], v, wa, wb, plan, 64)
+    torch.cuda.synchronize()
+    with pytest.raises(cabi.SmlmError):
+        plan.raise_if_failed()
+    assert (y[150:] == 0).all()
