@@ -13,6 +13,7 @@
 #include "smlm_merge.cuh"
 #include "smlm_plan.cuh"
 #include "smlm_wgrad.cuh"
+#include "smlm_wgrad_tc.cuh"
 
 namespace {
 
@@ -264,15 +265,36 @@ struct WgradShape {
   size_t ticket_bytes, scratch_bytes;
 };
 
-WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1) {
+// The tcgen05 variant serves every rank above 32 unless it is switched off.
+inline bool wgrad_uses_tensor_cores(int R) {
+  return R > 32 && g_tensor_core_mode.load(std::memory_order_relaxed) >= 0;
+}
+
+WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1, bool tc) {
   WgradShape s;
   const int rt = wgrad_rt(R);
-  s.slab = 4 * wgrad_cols_per_warp(rt);
+  s.slab = tc ? wg_tc_slab(rt) : 4 * wgrad_cols_per_warp(rt);
   s.slabs_total = (h0 + s.slab - 1) / s.slab + (h1 > 0 ? (h1 + s.slab - 1) / s.slab : 0);
   const int mp = std::max(1, max_pieces_of(T, npart));
-  // one wave of two CTAs per SM, each with at most kWgMaxGroup pieces
-  long long g = (static_cast<long long>(mp) * s.slabs_total + 2 * kNumSMs - 1) / (2 * kNumSMs);
-  g = std::max(1LL, std::min<long long>(g, kWgMaxGroup));
+  long long g;
+  if (tc) {
+    // one CTA per SM: the group size that minimises (waves of 148 CTAs) x (pieces per CTA + a
+    // fixed cost of about two pieces for set-up and closing runs)
+    long long best = -1;
+    g = 1;
+    for (int c = 1; c <= kWgMaxGroup; ++c) {
+      const long long ctas = static_cast<long long>((mp + c - 1) / c) * s.slabs_total;
+      const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (c + 2);
+      if (best < 0 || cost < best) {
+        best = cost;
+        g = c;
+      }
+    }
+  } else {
+    // one wave of two CTAs per SM, each with at most kWgMaxGroup pieces
+    g = (static_cast<long long>(mp) * s.slabs_total + 2 * kNumSMs - 1) / (2 * kNumSMs);
+    g = std::max(1LL, std::min<long long>(g, kWgMaxGroup));
+  }
   s.group = static_cast<int>(g);
   s.groups = (mp + s.group - 1) / s.group;
   s.ticket_bytes = (static_cast<size_t>(npart) * s.slabs_total * 4 * sizeof(int) + 255) / 256 * 256;
@@ -287,17 +309,21 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   WgradArgs a;
   WgradMaps tm;
   const int rt = wgrad_rt(R);
-  const WgradShape sh = wgrad_shape(T, npart, R, job0->H, job1 ? job1->H : 0);
+  const bool tc = wgrad_uses_tensor_cores(R);
+  const WgradShape sh = wgrad_shape(T, npart, R, job0->H, job1 ? job1->H : 0, tc);
   if (workspace == nullptr || workspace_bytes < sh.ticket_bytes + sh.scratch_bytes) return SMLM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return SMLM_ERR_MISALIGNED;
   const WgradJobDesc* jobs[2] = {job0, job1};
+  WgradTcMaps tcm = {};
   for (int j = 0; j < 2; ++j) {
     WgradJob& w = a.job[j];
     if (jobs[j] == nullptr) {
       w.g_table = nullptr; w.p = nullptr; w.H = 0; w.transposed = 0; w.use_scale = 0; w.slabs = 0;
       tm.q[j] = tm.q[0];
+      tcm.p[j] = tcm.p[0];
       continue;
     }
+    if (tc && !make_map_2d(&tcm.p[j], jobs[j]->p, T, R, 16, dtype)) return SMLM_ERR_CUDA;
     w.g_table = jobs[j]->g_table; w.p = jobs[j]->p; w.H = jobs[j]->H; w.transposed = jobs[j]->transposed;
     w.use_scale = jobs[j]->use_scale; w.slabs = (jobs[j]->H + sh.slab - 1) / sh.slab;
     if (!make_map_2d(&tm.q[j], jobs[j]->q, T, jobs[j]->H, 16, dtype)) return SMLM_ERR_CUDA;
@@ -308,6 +334,18 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   a.scratch = reinterpret_cast<float*>(static_cast<char*>(workspace) + sh.ticket_bytes);
   a.npart = npart; a.T = T; a.R = R; a.group = sh.group; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
   a.independent = independent;
+  if (tc) {
+    tcm.q[0] = tm.q[0];
+    tcm.q[1] = tm.q[1];
+    const dim3 grid(sh.groups, a.job[0].slabs + a.job[1].slabs, 1);
+    if (dtype == SMLM_F16)
+      return rt <= 4 ? launch(wgrad_tc_kernel<__half, 4>, grid, kWgTcThreads, 1, WgradTcSmem<4>::kTotal, stream, a, tcm)
+                     : launch(wgrad_tc_kernel<__half, 8>, grid, kWgTcThreads, 1, WgradTcSmem<8>::kTotal, stream, a, tcm);
+    return rt <= 4 ? launch(wgrad_tc_kernel<__nv_bfloat16, 4>, grid, kWgTcThreads, 1, WgradTcSmem<4>::kTotal, stream,
+                            a, tcm)
+                   : launch(wgrad_tc_kernel<__nv_bfloat16, 8>, grid, kWgTcThreads, 1, WgradTcSmem<8>::kTotal, stream,
+                            a, tcm);
+  }
   if (dtype == SMLM_F16) {
     if (rt == 1) return launch_wgrad<__half, 1>(a, tm, sh.groups, stream);
     if (rt == 2) return launch_wgrad<__half, 2>(a, tm, sh.groups, stream);
@@ -483,8 +521,14 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
 
 size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1) {
   if (T < 0 || npart < 0 || rank <= 0 || h0 <= 0 || h1 < 0) return 0;
-  const WgradShape sh = wgrad_shape(T, npart, rank, h0, h1);
-  return sh.ticket_bytes + sh.scratch_bytes;
+  // enough for either kernel, so that a buffer sized before a change of the tensor-core mode stays valid
+  const WgradShape sh = wgrad_shape(T, npart, rank, h0, h1, false);
+  size_t need = sh.ticket_bytes + sh.scratch_bytes;
+  if (rank > 32) {
+    const WgradShape st = wgrad_shape(T, npart, rank, h0, h1, true);
+    need = std::max(need, st.ticket_bytes + st.scratch_bytes);
+  }
+  return need;
 }
 
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
@@ -512,7 +556,7 @@ int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, c
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
-  const WgradShape sh = wgrad_shape(T, npart, rank, h, 0);
+  const WgradShape sh = wgrad_shape(T, npart, rank, h, 0, wgrad_uses_tensor_cores(rank));
   if (sh.ticket_bytes + sh.scratch_bytes > kStaticWgradBytes) return SMLM_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
   const int rc = static_scratch_of_current_device(&scratch);

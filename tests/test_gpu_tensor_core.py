@@ -96,7 +96,7 @@ def test_matches_the_mma_sync_kernel():
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("rm", [False, True])
-@pytest.mark.parametrize("rank", [64, 128])
+@pytest.mark.parametrize("rank", [40, 64, 128])
 def test_backward_vs_oracle(dtype, rm, rank):
     from test_gpu_parity import _grad_close, _oracle_bwd, _run_bwd
     part = [0, 133, 133, 330, 331, 600]
@@ -108,6 +108,39 @@ def test_backward_vs_oracle(dtype, rm, rank):
     for p in range(5):
         _grad_close(dA[p], gA[p], f"dA{p}")
         _grad_close(dB[p], gB[p], f"dB{p}")
+
+
+def test_backward_scale_fp32_accumulate():
+    from test_gpu_parity import _grad_close, _oracle_bwd, _run_bwd
+    part = [0, 100, 457]
+    c = _case(600, [457], 2, 512, 320, 64, torch.bfloat16, False, ids=[0])
+    dx, dA, dB = _run_bwd(c, part, scale=[2.0, 0.5], grad_fp32=True, accumulate=True)
+    gx, gA, gB = _oracle_bwd(c, part, scale=[2.0, 0.5])
+    _grad_close(dx, gx, "dX")
+    for p in range(2):
+        assert dA[p].dtype == torch.float32
+        _grad_close(dA[p] - 1.0, gA[p], f"dA{p}")
+        _grad_close(dB[p] - 1.0, gB[p], f"dB{p}")
+
+
+@pytest.mark.parametrize("rm", [False, True])
+def test_backward_many_partitions_per_group(rm):
+    """Enough pieces that a CTA of the weight-gradient kernel owns several of them: runs that end
+    inside a CTA, runs that straddle CTAs, and more than two runs per CTA."""
+    from test_gpu_parity import _grad_close, _oracle_bwd, _run_bwd
+    rng = np.random.default_rng(5)
+    lens = [int(v) for v in rng.integers(0, 200, size=100)]
+    part = [0] + [int(v) for v in np.cumsum(lens)]
+    c = _case(601, [part[-1] + 7], 100, 512, 1024, 64, torch.bfloat16, rm, ids=[0])
+    dx, dA, dB = _run_bwd(c, part)
+    gx, gA, gB = _oracle_bwd(c, part)
+    _grad_close(dx[:part[-1]], gx[:part[-1]], "dX")
+    for p in range(100):
+        _grad_close(dA[p], gA[p], f"dA{p}")
+        _grad_close(dB[p], gB[p], f"dB{p}")
+    # the ticketed sum runs in a fixed order: a second launch gives the same bits
+    dx2, dA2, dB2 = _run_bwd(c, part)
+    assert all(torch.equal(a, b) for a, b in zip(dA, dA2)) and all(torch.equal(a, b) for a, b in zip(dB, dB2))
 
 
 def test_bad_adapter_pointer_is_reported_not_dereferenced():
