@@ -71,7 +71,16 @@ inline int piece_rows_for(int T) {
 }
 
 inline int max_pieces_of(int T, int nseg) { return T / piece_rows_for(T) + nseg; }
-inline int max_tall_pieces_of(int T, int nseg) { return T / (2 * piece_rows_for(T)) + nseg; }
+// Rows per piece of the tall list (the tcgen05 kernel's tiles).  Always the full 128: cutting a
+// batch that needs a little more than a whole number of waves of 148 CTAs at 120 rows instead made
+// the launch 1.5x slower (measured), because every piece then ends in rows that leave the kernel's
+// 16-row tensor stores for plain stores, and a short tail piece costs as much as a full one.
+inline int tall_rows_for(int T, int nseg) {
+  (void)T;
+  (void)nseg;
+  return 2 * kBM;
+}
+inline int max_tall_pieces_of(int T, int nseg) { return T / tall_rows_for(T, nseg) + nseg; }
 
 inline int pow2_at_least(int v) {
   int p = 1;
@@ -441,7 +450,7 @@ int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int
   if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
   plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T),
-      max_tall_pieces_of(T, nseg));
+      max_tall_pieces_of(T, nseg), tall_rows_for(T, nseg));
   if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
   return SMLM_OK;
 }

@@ -10,10 +10,10 @@
 // operands read from shared memory through matrix descriptors and fp32 accumulators in tensor
 // memory (TMEM): acc1 [128 x KP] for the shrink, two [128 x 128] buffers for the expand.
 //
-// Warp roles (6 warps):
+// Warp roles (8 warps):
 //   warp 0   TMA producer of IN: tiled tensor copies of [16 rows x 64 columns] boxes with the
 //            128-byte swizzle, which is exactly the K-major SWIZZLE_128B operand layout;
-//            in phase 3 it loads the W2 slabs.
+//            in phase 3 it loads the W2 slabs together with warps 6 and 7.
 //   warp 1   allocates TMEM, issues every MMA, signals completion with tcgen05.commit.
 //   warps 2-5 load the W1 panel slices (16-byte cp.async into the swizzled operand layout,
 //            completion counted on the stage's mbarrier) and run both epilogues: TMEM ->
@@ -28,9 +28,11 @@
 
 namespace smlm {
 
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 256;
 constexpr int kTcRows = 128;   // rows of a tall piece = M of the MMA
 constexpr int kTcNG = 128;     // OUT columns per MMA group of phase 3
+constexpr int kTcW2Bufs = 4;   // W2 slabs in flight
+constexpr int kTcOutBufs = 4;  // staging blocks per epilogue warp: tensor stores in flight
 
 constexpr int tc_chunks(int r16) { return r16 >= 8 ? 2 : 4; }  // 64-column chunks of IN per stage
 
@@ -45,17 +47,17 @@ struct TcSmem {
   static constexpr int kStage = kXBytes + kW1Bytes;
   static constexpr int kStages = 2;
   static constexpr int kRing = kStages * kStage;
-  // phase 3 lives in the space of the ring: two W2 slabs [kTcNG x KP], then per epilogue warp two
-  // staging blocks of [32 rows][128 B]
+  // phase 3 lives in the space of the ring: kTcW2Bufs W2 slabs [kTcNG x KP], then per epilogue warp
+  // kTcOutBufs staging blocks of [32 rows][128 B]
   static constexpr int kW2Slab = kTcNG * KP * 2;
-  static constexpr int kOutOff = 2 * kW2Slab;
-  static constexpr int kStageOut = 4 * 2 * 4096;
+  static constexpr int kOutOff = kTcW2Bufs * kW2Slab;
+  static constexpr int kStageOut = 4 * kTcOutBufs * 4096;
   static constexpr int kPhase3 = kOutOff + kStageOut;
   static constexpr int kUnion = kRing > kPhase3 ? kRing : kPhase3;
   static constexpr int kMidOff = kUnion;                      // MID operand: NB blocks of [128 rows][128 B]
   static constexpr int kMid = NB * kTcRows * 128;
   static constexpr int kBarOff = kMidOff + kMid;
-  static constexpr int kNumBars = 2 * kStages + 2 + 8;
+  static constexpr int kNumBars = 2 * kStages + 2 + 2 * kTcW2Bufs + 4;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16 + 1024;
   static constexpr int kTmemCols = 512;                       // acc1 (KP) + 2 x 128, rounded up to a power of two
   static_assert(kTotal <= 227 * 1024, "shared memory budget");
@@ -180,8 +182,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
   const uint32_t bar0 = base + SM::kBarOff;
   const uint32_t full0 = bar0, empty0 = bar0 + S * 8;
   const uint32_t acc1_full = bar0 + 2 * S * 8, mid_full = acc1_full + 8;
-  const uint32_t w2_full0 = mid_full + 8, w2_empty0 = w2_full0 + 16;
-  const uint32_t acc2_full0 = w2_empty0 + 16, acc2_empty0 = acc2_full0 + 16;
+  const uint32_t w2_full0 = mid_full + 8, w2_empty0 = w2_full0 + 8 * kTcW2Bufs;
+  const uint32_t acc2_full0 = w2_empty0 + 8 * kTcW2Bufs, acc2_empty0 = acc2_full0 + 16;
   const uint32_t tmem_slot = acc2_empty0 + 16;
   volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - raw));
 
@@ -192,9 +194,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
     }
     mbar_init(acc1_full, 1);
     mbar_init(mid_full, 128);
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(w2_full0 + b * 8, 32);
+    for (int b = 0; b < kTcW2Bufs; ++b) {
+      mbar_init(w2_full0 + b * 8, 96);
       mbar_init(w2_empty0 + b * 8, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
       mbar_init(acc2_full0 + b * 8, 1);
       mbar_init(acc2_empty0 + b * 8, 128);
     }
@@ -233,18 +237,21 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
         tma_load_2d(xs + c * (kTcRows * 128) + b * 2048, &tm.in16, k0 + c * 64, pc.row0 + b * 16, fb);
       }
     }
-    // ============ phase 3: loader of the W2 slabs ============
+  }
+  if (warp == 0 || warp >= 6) {
+    // ============ phase 3: three warps load the W2 slabs ============
+    const int lt = (warp == 0 ? 0 : warp - 5) * 32 + lane;   // 0..95
     mbar_wait(acc1_full, 0, err, dead);  // the ring is no longer read once the shrink has completed
     for (int g = 0; g < ngroups; ++g) {
-      const int buf = g & 1;
-      if (g >= 2) mbar_wait(w2_empty0 + buf * 8, ((g >> 1) - 1) & 1, err, dead);
+      const int buf = g % kTcW2Bufs;
+      if (g >= kTcW2Bufs) mbar_wait(w2_empty0 + buf * 8, ((g / kTcW2Bufs) - 1) & 1, err, dead);
       if (dead) break;
       const int n0 = g * kTcNG;
       const int ncols = min(kTcNG, N2 - n0);
       const uint32_t ws = base + buf * SM::kW2Slab;
       if constexpr (!RM) {
         // W2 stored [N2][R] (K-major): per 64-wide rank block, [128 n-rows][128 B] swizzled
-        for (int i = lane; i < kTcNG * NB * 8; i += 32) {
+        for (int i = lt; i < kTcNG * NB * 8; i += 96) {
           const int c = i & 7, n = (i >> 3) % kTcNG, blk = i / (8 * kTcNG);
           const int kcol = blk * 64 + c * 8;
           const bool ok = (n < ncols) && (kcol < R);
@@ -253,7 +260,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
         }
       } else {
         // W2 stored [R][N2] (MN-major): per 64-column block, [KP k-rows][128 B] swizzled
-        for (int i = lane; i < KP * (kTcNG / 64) * 8; i += 32) {
+        for (int i = lt; i < KP * (kTcNG / 64) * 8; i += 96) {
           const int c = i & 7, k = (i >> 3) % KP, blk = i / (8 * KP);
           const int col = blk * 64 + c * 8;
           const bool ok = (k < R) && (col < ncols);
@@ -295,9 +302,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
       const uint32_t idesc2 = tc_idesc<T>(kTcNG, RM);
       const uint32_t mids = base + SM::kMidOff;
       for (int g = 0; g < ngroups; ++g) {
-        const int buf = g & 1;
-        const uint32_t ws = base + buf * SM::kW2Slab;
-        mbar_wait(w2_full0 + buf * 8, (g >> 1) & 1, err, dead);
+        const int buf = g & 1;              // accumulator buffer
+        const int wbuf = g % kTcW2Bufs;     // W2 slab
+        const uint32_t ws = base + wbuf * SM::kW2Slab;
+        mbar_wait(w2_full0 + wbuf * 8, (g / kTcW2Bufs) & 1, err, dead);
         if (g >= 2) mbar_wait(acc2_empty0 + buf * 8, ((g >> 1) - 1) & 1, err, dead);
         fence_proxy_async();
         tc_fence_after();
@@ -310,7 +318,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
             tc_mma(acc2 + buf * kTcNG, ad, bd, idesc2, j > 0 ? 1u : 0u);
           }
         }
-        tc_commit(w2_empty0 + buf * 8);
+        tc_commit(w2_empty0 + wbuf * 8);
         tc_commit(acc2_full0 + buf * 8);
       }
     }
@@ -389,7 +397,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
     mbar_arrive(mid_full);
 
     // ---- epilogue 2: acc2[buf] -> OUT ----
-    const uint32_t ostage = base + SM::kOutOff + (warp - 2) * 8192;
+    const uint32_t ostage = base + SM::kOutOff + (warp - 2) * (kTcOutBufs * 4096);
     T* orow = static_cast<T*>(a.out) + static_cast<size_t>(pc.row0 + row) * N2;
     const int rows_here = min(32, nrows - sub * 32);   // rows of this warp that exist (may be <= 0)
     int obuf = 0;
@@ -402,7 +410,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {   // 64 columns at a time: one [32 rows][128 B] staging block
-        if (lane == 0) bulk_wait_read<1>();
+        if (lane == 0) bulk_wait_read<kTcOutBufs - 1>();
         __syncwarp();
         const uint32_t os = ostage + obuf * 4096;
 #pragma unroll
@@ -465,7 +473,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
             }
           }
           __syncwarp();
-          obuf ^= 1;
+          obuf = (obuf + 1) % kTcOutBufs;
         }
       }
     }

@@ -10,8 +10,8 @@
 // grouped-GEMM problem descriptors.
 //
 // Plan buffer layout: int header[4] = {count, error, max_pieces, bm}, then
-// Piece[max_pieces + 1]; after it a second list of the same form cut at twice the
-// height (its error word is unused: faults are always recorded in the first header).
+// Piece[max_pieces + 1]; after it a second list of the same form cut at `bm2` rows, 128
+// at most (its error word is unused: faults are always recorded in the first header).
 // The tall list feeds the tcgen05 kernel, whose MMA tile is 128 rows.  An indptr that
 // is negative, decreasing or reaches past T yields count = 0 in both lists and the
 // kErrBadIndptr bit, so that no consumer touches memory.
@@ -24,7 +24,8 @@ constexpr int kPlanThreads = 1024;
 
 __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restrict__ plan,
                                                                    const int32_t* __restrict__ indptr, int nseg,
-                                                                   int T, int max_pieces, int bm, int max_pieces2) {
+                                                                   int T, int max_pieces, int bm, int max_pieces2,
+                                                                   int bm2) {
   __shared__ int s_off[kPlanThreads + 1];
   __shared__ int s_warp[32];
   __shared__ int s_base;
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
       second[0] = 0;
       second[1] = 0;
       second[2] = max_pieces2;
-      second[3] = 2 * bm;
+      second[3] = bm2;
     }
     return;
   }
@@ -63,7 +64,7 @@ __global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restri
   for (int list = 0; list < 2; ++list) {
   if (list == 1) {
     plan = plan0 + kPlanHeaderInts + 4 * (max_pieces + 1);
-    bm *= 2;
+    bm = bm2;
     max_pieces = max_pieces2;
     if (tid == 0) s_base = 0;
     __syncthreads();

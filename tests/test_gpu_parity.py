@@ -48,15 +48,17 @@ def test_plan_pieces_bit_exact():
         assert n == len(want)
         got = plan.buf[4:4 + 4 * n].cpu().view(-1, 4).tolist()
         assert [tuple(g) for g in got] == want
-        # the second list: the same segments cut at twice the height
+        # the second list: the same segments cut at the height its header records (96..128 rows)
         off = 4 + 4 * (T // bm + nseg + 1)
         hdr = plan.buf[off:off + 4].tolist()
+        bm2 = hdr[3]
+        assert 96 <= bm2 <= 128 and bm2 % 8 == 0
         want2 = []
         for i in range(nseg):
             a, b = int(seg[i]), int(seg[i + 1])
-            for r0 in range(a, b, 2 * bm):
-                want2.append((r0, min(2 * bm, b - r0), i, 0))
-        assert hdr[0] == len(want2) and hdr[3] == 2 * bm
+            for r0 in range(a, b, bm2):
+                want2.append((r0, min(bm2, b - r0), i, 0))
+        assert hdr[0] == len(want2) and hdr[0] <= hdr[2]
         got2 = plan.buf[off + 4:off + 4 + 4 * hdr[0]].cpu().view(-1, 4).tolist()
         assert [tuple(g) for g in got2] == want2
 

@@ -30,7 +30,7 @@ def test_library_loads_and_exports_every_declared_symbol():
     bm = cabi.lib.smlm_b200_piece_rows(8192)
     assert 16 <= bm <= 64 and bm % 8 == 0
     assert cabi.lib.smlm_b200_plan_bytes(8192, 100) == (16 + 16 * (8192 // bm + 100 + 1)
-                                                        + 16 + 16 * (8192 // (2 * bm) + 100 + 1))
+                                                        + 16 + 16 * (8192 // 128 + 100 + 1))
     assert cabi.lib.smlm_b200_status_string(3) == b"No suitable kernel."
 
 
