@@ -11,8 +11,9 @@ and the backward (dV, dB, dA, dX) over the fine-tune rows.  Default workload (c3
 Llama-3-8B projection set, bf16, rank 16, 128 adapters, 8192 tokens in segments of
 Zipf(1.2) lengths clipped to [1, 2048], 25 % of the tokens in fine-tune segments.
 Under torchrun every rank holds its own batch (weak scaling) whose segments use
-the adapters that rank owns; the path has no collective for c2/c3/c4, and one
-NCCL all-reduce of the dA/dB bucket per step for c5.
+the adapters that rank owns; the path has no collective for c2/c3/c4; for c5 the dA/dB
+slice of each projection is all-reduced over NCCL, started right behind that projection's
+weight-gradient kernel so that it runs under the next projection's backward.
 
 Rank 0 prints ONE JSON line.  `value` is tokens/s with inputs resident in HBM;
 `e2e` is the same metric with the step's inputs copied from pinned host memory and
@@ -186,6 +187,7 @@ class Workload:
         self.pplan = None
         self.ops = ops
         self.accumulate_grads = False
+        self.after_wgrad = None  # callable(projection index), called on the stream of its weight gradients
         self.overlap = True
         self.n_streams = 3
         self.side = []
@@ -246,6 +248,8 @@ class Workload:
                                    part_ids=self.part_ids, part_scale=self.scale,
                                    n_table=self.spec["n_adapters"], accumulate=self.accumulate_grads,
                                    workspace=ws)
+                    if self.after_wgrad is not None:
+                        self.after_wgrad(i)
             for s in self.side[:ns]:
                 main.wait_stream(s)
 
@@ -560,7 +564,7 @@ def main():
         l2="one step touches %.0f MB of distinct operands (> 126 MB L2); nothing is reused between steps"
            % ((fwd_b + bwd_b) / 1e6),
         sharding="segments partitioned by adapter owner (adapter mod N), no collective" if a.workload != "c5"
-                 else "data parallel, one all-reduce of the dA/dB bucket per step")
+                 else "data parallel, one all-reduce per projection of its dA/dB slice, started behind its weight-gradient kernel")
 
     if a.impl == "reference":
         if rank != 0:
@@ -598,13 +602,16 @@ def main():
             p["dA"], p["dB"] = bucket.dA[i], bucket.dB[i]
         wl.accumulate_grads = True
         cfg["allreduce_bytes_per_step"] = bucket.nbytes
+        # the exchange of a projection starts right behind its weight-gradient kernel and runs under
+        # the backward of the next projection
+        wl.after_wgrad = bucket.reduce_projection
 
     def eager_step():
         if bucket is not None:
             bucket.zero()
         wl.step()
         if bucket is not None:
-            bucket.reduce()
+            bucket.finish()
 
     eager_step()
     torch.cuda.synchronize()

@@ -12,9 +12,11 @@ src/loquetier_src/trainer_utils.py:28-29), so there is no behaviour to match bey
 * Data-parallel fine-tuning of adapters shared by several ranks has one exchange
   step: the sum of dA/dB.  ``GradBucket`` is one flat, contiguous buffer that holds
   the gradients of every (projection, adapter); the backward kernels write into
-  it directly through per-partition pointer tables (no repack pass), and
-  ``reduce()`` is a single all-reduce of the flat buffer (NCCL over NVLink on GPUs,
-  gloo in the CPU tests)."""
+  it directly through per-partition pointer tables (no repack pass).  ``reduce()`` is
+  a single all-reduce of the flat buffer; ``reduce_projection(p)`` starts the
+  all-reduce of one projection's slice as soon as its weight-gradient kernel has been
+  issued, so that the exchange of projection p runs under the backward of projection
+  p+1, and ``finish()`` joins them (NCCL over NVLink on GPUs, gloo in the CPU tests)."""
 from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -62,8 +64,11 @@ class GradBucket:
         self.dA: List[torch.Tensor] = []
         self.dB: List[torch.Tensor] = []
         self._ptrs: List[Tuple[torch.Tensor, torch.Tensor]] = []
+        self._slices: List[torch.Tensor] = []
+        self._pending: list = []
         off = 0
         for (h_in, h_out) in shapes:
+            self._slices.append(self.flat[off:off + n_adapters * rank * (h_in + h_out)])
             a = self.flat[off:off + n_adapters * rank * h_in].view(n_adapters, rank, h_in)
             off += a.numel()
             b = self.flat[off:off + n_adapters * h_out * rank].view(n_adapters, h_out, rank)
@@ -90,6 +95,23 @@ class GradBucket:
         if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(self.group) == 1:
             return None
         return dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=self.group, async_op=async_op)
+
+    def reduce_projection(self, proj: int):
+        """Starts the sum over ranks of one projection's dA/dB (a contiguous slice of the flat
+        buffer).  The collective is ordered after the work already issued on the current stream
+        and runs next to whatever is issued afterwards; ``finish()`` joins it."""
+        import torch.distributed as dist
+        if not dist.is_available() or not dist.is_initialized() or dist.get_world_size(self.group) == 1:
+            return None
+        w = dist.all_reduce(self._slices[proj], op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        self._pending.append(w)
+        return w
+
+    def finish(self):
+        """Makes the current stream (or the host, on CPU) wait for every started reduction."""
+        for w in self._pending:
+            w.wait()
+        self._pending = []
 
     @property
     def nbytes(self) -> int:

@@ -55,6 +55,12 @@ def _worker(rank, world, port, out):
         dist.all_gather(gathered, local)
         want = sum(gathered)
         ok = torch.allclose(b.flat, want)
+        # the per-projection reductions together give the same sums as the single one
+        b.flat.copy_(local)
+        for p in range(len(shapes)):
+            b.reduce_projection(p)
+        b.finish()
+        ok = ok and torch.allclose(b.flat, want)
         # untouched adapter 2 stays zero everywhere
         ok = ok and all(float(b.dA[p][2].abs().max()) == 0.0 for p in range(len(shapes)))
         out[rank] = bool(ok)
