@@ -536,6 +536,8 @@ def main():
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-kernel-class timing pass")
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
+    ap.add_argument("--seg-len", type=int, default=0, help="c5 only: tokens per segment instead of 2048 "
+                                                          "(a smaller footprint for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
 
@@ -545,6 +547,9 @@ def main():
     import torch
 
     spec = workload_spec(a.workload, rank, world)
+    if a.seg_len > 0:
+        assert a.workload == "c5", "--seg-len applies to c5"
+        spec["lens"] = [a.seg_len] * len(spec["lens"])
     if a.only:
         keep = set(a.only.split(","))
         spec["projections"] = [p for p in spec["projections"] if p[0] in keep]
