@@ -159,3 +159,73 @@ def test_bad_adapter_pointer_is_reported_not_dereferenced():
     with pytest.raises(cabi.SmlmError):
         plan.raise_if_failed()
     assert (y[150:] == 0).all()
+
+
+def test_c5_full_size_both_kernels_and_oracle_slices():
+    """The fine-tune-heavy configuration at full size (16 x 2048 tokens, rank 64, 4096 -> 14336): the
+    kernel choice left to the library (long segments: tcgen05), against the mma.sync kernels on the
+    same tensors, and against the CPU oracle on slices of rows (rows are independent of each other)."""
+    from gpu_util import dev, ptr_table
+    from loquetier_b200 import ops
+    ops.set_tensor_core_mode(0)
+    T, nseg, h_in, h_out, r = 32768, 16, 4096, 14336, 64
+    g = torch.Generator(device=dev()).manual_seed(55)
+    dt = torch.bfloat16
+    x = torch.randn((T, h_in), generator=g, device=dev(), dtype=torch.float32).to(dt)
+    go = torch.randn((T, h_out), generator=g, device=dev(), dtype=torch.float32).to(dt)
+    wa = [(torch.randn((r, h_in), generator=g, device=dev()) / h_in ** 0.5).to(dt) for _ in range(nseg)]
+    wb = [(torch.randn((h_out, r), generator=g, device=dev()) * 0.02).to(dt) for _ in range(nseg)]
+    seg = torch.arange(0, T + 1, T // nseg, dtype=torch.int32, device=dev())
+    wa_t, wb_t = ptr_table(wa), ptr_table(wb)
+
+    def run():
+        plan = ops.Plan(seg, T)
+        y = torch.zeros((T, h_out), dtype=dt, device=dev())
+        v = torch.zeros((T, r), dtype=dt, device=dev())
+        ops.fwd(y, x, v, wa_t, wb_t, plan, r)
+        dx = torch.zeros((T, h_in), dtype=dt, device=dev())
+        dv = torch.zeros((T, r), dtype=dt, device=dev())
+        dA = [torch.zeros_like(w) for w in wa]
+        dB = [torch.zeros_like(w) for w in wb]
+        ops.bwd(dx, ptr_table(dA), ptr_table(dB), dv, go, x, v, wa_t, wb_t, plan, r)
+        torch.cuda.synchronize()
+        plan.raise_if_failed()
+        return y, v, dx, dA, dB
+
+    y, v, dx, dA, dB = run()
+    ops.set_tensor_core_mode(-1)
+    y2, v2, dx2, dA2, dB2 = run()
+
+    def close(a, b, what):
+        a32, b32 = a.float(), b.float()
+        tol = 1e-2 * max(1.0, float(b32.abs().max()))
+        bad = (a32 - b32).abs() > tol + 1e-2 * b32.abs()
+        assert not bool(bad.any()), f"{what}: {int(bad.sum())} elements differ"
+
+    close(v, v2, "v")
+    close(y, y2, "y")
+    close(dx, dx2, "dX")
+    for p in (0, 7, 15):
+        close(dA[p], dA2[p], f"dA{p}")
+        close(dB[p], dB2[p], f"dB{p}")
+    # oracle on row slices: fp32 on the host from the same 16-bit inputs
+    for s, off, n in ((0, 0, 40), (5, 1000, 64), (15, 2047, 1)):
+        a, b = s * 2048 + off, s * 2048 + off + n
+        xs = x[a:b].cpu().float()
+        vs = (xs @ wa[s].cpu().float().T).to(dt).float()
+        ys = vs @ wb[s].cpu().float().T
+        assert_close(v[a:b].cpu(), vs, what=f"v rows of segment {s}")
+        assert_close(y[a:b].cpu(), ys, what=f"y rows of segment {s}")
+        gs = go[a:b].cpu().float()
+        dvs = gs @ wb[s].cpu().float()
+        dxs = dvs @ wa[s].cpu().float()
+        assert_close(dx[a:b].cpu(), dxs, rtol=2e-2, atol=2e-2, what=f"dX rows of segment {s}")
+    # one adapter's gradients against the oracle formulas (dB = gO^T v, dA = dV^T x), fp32 on the device
+    s = 9
+    a, b = s * 2048, (s + 1) * 2048
+    vs = (x[a:b].float() @ wa[s].float().T).to(dt).float()
+    dB_ref = go[a:b].float().T @ vs
+    dvs = (go[a:b].float() @ wb[s].float())
+    dA_ref = dvs.T @ x[a:b].float()
+    close(dB[s], dB_ref, "dB vs fp32")
+    close(dA[s], dA_ref, "dA vs fp32")
