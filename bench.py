@@ -526,7 +526,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=1000)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5"])
+    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
@@ -546,6 +546,8 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", "0"))
     import torch
 
+    if a.workload == "rmsnorm":
+        return run_rmsnorm(a, rank, world, local, torch)
     spec = workload_spec(a.workload, rank, world)
     if a.seg_len > 0:
         assert a.workload == "c5", "--seg-len applies to c5"
@@ -681,6 +683,151 @@ def main():
     if rank == 0 and world == 1 and not a.no_cpu:
         base, _ = run_cpu(spec, torch)
         line["cpu_baseline"] = base
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank == 0:
+        print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# RMSNorm, the caller on either side of the projections (--workload rmsnorm)
+# ---------------------------------------------------------------------------
+
+def run_rmsnorm(a, rank, world, local, torch):
+    """Forward + backward of the Llama-3-8B RMSNorm over 32768 token rows of 4096 columns, bf16.
+    Rows shard over ranks with no collective (every rank holds the same weight; its dW would join the
+    gradient all-reduce of the model, which is not part of this operator)."""
+    from oracle import smlm_oracle as O
+    rows, cols, eps = 32768, 4096, 1e-5
+    e = 2
+    fwd_b = e * (2 * rows * cols + cols) + 4 * rows
+    bwd_b = e * (3 * rows * cols + 2 * cols) + 4 * rows
+    cfg = dict(workload="rmsnorm: Llama-3-8B RMSNorm forward + backward, bf16, 32768 token rows x 4096 columns",
+               tokens_per_gpu=rows, l2="one step touches %.0f MB of distinct operands (> 126 MB L2)" % ((fwd_b + bwd_b) / 1e6),
+               sharding="rows partitioned over ranks, no collective")
+    g = torch.Generator().manual_seed(7000 + rank)
+
+    def cpu_data(n):
+        x = (torch.randn((n, cols), generator=g) * 1.5).to(torch.bfloat16)
+        w = (1.0 + 0.1 * torch.randn((cols,), generator=g)).to(torch.bfloat16)
+        go = torch.randn((n, cols), generator=g).to(torch.bfloat16)
+        return x, w, go
+
+    def cpu_leg(budget_s, max_reps):
+        cores = os.cpu_count() or 1
+        torch.set_num_threads(cores)
+        x, w, go = cpu_data(rows)
+
+        def fn():
+            o, m = O.rms_norm_forward(x, w, eps)
+            O.rms_norm_backward(go, x, w, m)
+        fn()
+        times, t_all = [], time.perf_counter()
+        while len(times) < max_reps and (time.perf_counter() - t_all) < budget_s:
+            t0 = time.perf_counter()
+            fn()
+            times.append(time.perf_counter() - t0)
+        sec = float(np.median(times))
+        return dict(value=rows / sec, unit="tokens/s", cores=cores, kind="port",
+                    sample=f"{len(times)} full steps ({rows} rows x {cols}, fwd+bwd) of the fp32 restatement with "
+                           f"torch.set_num_threads({cores}); median {sec * 1e3:.1f} ms/step"), sec
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        base, sec = cpu_leg(max(10.0, 0.5 * a.steps), max(1, a.steps))
+        print(json.dumps(dict(metric="RMSNorm fwd+bwd tokens/s", value=base["value"], unit="tokens/s", n_gpus=a.gpus,
+                              steps=a.steps, warmup=a.warmup, ms_per_step=sec * 1e3, higher_is_better=True,
+                              scaling="weak", vs_baseline=None, dtype="fp32 on CPU (16-bit inputs upcast)",
+                              data="synthetic", config=cfg, impl="reference", cpu_baseline=base, gpu_launches=0,
+                              e2e=dict(value=base["value"], unit="tokens/s", h2d_bytes_per_step=0,
+                                       d2h_bytes_per_step=0))))
+        return
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    from loquetier_b200 import ops
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist_mod.init_process_group("nccl", device_id=dev)
+        dist = dist_mod
+    gd = torch.Generator(device=dev).manual_seed(7000 + rank)
+    x = (torch.randn((rows, cols), generator=gd, device=dev) * 1.5).to(torch.bfloat16)
+    w = (1.0 + 0.1 * torch.randn((cols,), generator=gd, device=dev)).to(torch.bfloat16)
+    go = torch.randn((rows, cols), generator=gd, device=dev).to(torch.bfloat16)
+    o, dx = torch.empty_like(x), torch.empty_like(x)
+    m = torch.empty((rows, 1), dtype=torch.float32, device=dev)
+    dw = torch.empty((cols,), dtype=torch.bfloat16, device=dev)
+    ws = torch.empty(max(16, int(ops.lib.smlm_b200_rms_norm_bwd_workspace_bytes(rows, cols))), dtype=torch.uint8,
+                     device=dev)
+
+    def step():
+        ops.rms_norm(o, m, x, w, eps)
+        ops.rms_norm_bwd(dx, dw, go, x, w, m, workspace=ws)
+
+    step()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    with torch.cuda.graph(graph):
+        step()
+    with ClockSampler(local) as clk:
+        time.sleep(0.3)
+        ms = timed(graph.replay, a.steps, a.warmup, torch, dist, clk)
+    line = dict(metric="RMSNorm fwd+bwd tokens/s", value=rows * world / (ms * 1e-3), unit="tokens/s", n_gpus=world,
+                steps=a.steps, warmup=a.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak",
+                vs_baseline=None, dtype="bf16", data="synthetic", config=cfg, clocks=clk.result,
+                gpu_launches=3 * a.steps, launch_mode="cuda graph replay")
+    if rank == 0:
+        try:
+            peak, which = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+        except Exception:
+            peak, which = 6650.0, "fallback"
+        line["step_hbm"] = dict(algorithmic_bytes=fwd_b + bwd_b, achieved_gbs=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9,
+                                frac=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9 / peak, peak_gbs=peak, peak_source=which)
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        kern = {}
+        for name, fn, nb in (("rms_norm_fwd_kernel", lambda: ops.rms_norm(o, m, x, w, eps), fwd_b),
+                             ("rms_norm_bwd_kernel + rms_norm_dw_kernel",
+                              lambda: ops.rms_norm_bwd(dx, dw, go, x, w, m, workspace=ws), bwd_b)):
+            tot = 0.0
+            for it in range(6):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(); fn(); e1.record()
+                torch.cuda.synchronize()
+                if it:
+                    tot += e0.elapsed_time(e1)
+            t = tot / 5
+            kern[name] = dict(ms_per_step=t, gbs=nb / (t * 1e-3) / 1e9, frac=nb / (t * 1e-3) / 1e9 / peak)
+        top = max(kern, key=lambda k: kern[k]["ms_per_step"])
+        line["kernels"] = kern
+        line["roofline"] = dict(bound="hbm", kernel=top, achieved=kern[top]["gbs"], peak=peak, unit="GB/s",
+                                frac=kern[top]["frac"], peak_source=which, traffic=None)
+    if not a.no_e2e:
+        hx, hg = x.cpu().pin_memory(), go.cpu().pin_memory()
+        ho, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+        hdw = torch.empty((cols,), dtype=torch.bfloat16).pin_memory()
+
+        def e2e_step():
+            x.copy_(hx, non_blocking=True)
+            go.copy_(hg, non_blocking=True)
+            step()
+            ho.copy_(o, non_blocking=True)
+            hdx.copy_(dx, non_blocking=True)
+            hdw.copy_(dw, non_blocking=True)
+        e_ms = timed(e2e_step, max(3, min(a.steps, 10)), 3, torch, dist)
+        line["e2e"] = dict(value=rows * world / (e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=2 * rows * cols * e,
+                           d2h_bytes_per_step=2 * rows * cols * e + cols * e, ms_per_step=e_ms)
+    if rank == 0 and world == 1 and not a.no_cpu:
+        line["cpu_baseline"], _ = cpu_leg(12.0, 5)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()

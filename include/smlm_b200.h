@@ -205,6 +205,31 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
                   void* workspace, size_t workspace_bytes, int n_table, int T, int npart, int h_in, int h_out,
                   int rank, int dtype, int is_row_major, int accumulate_grads, int grad_fp32, void* stream);
 
+/* ---- RMSNorm: the caller on either side of the q/k/v and gate/up projections ----------------- */
+
+/* Replaces dispatch_rms_norm / rms_norm<T> (kernel_src/csrc/loquetier_ops.cc:326-358,
+ * kernel_src/csrc/rms_norm/rms_norm_cutlass.cu:158-186) behind `loquetier.ops._kernels.rms_norm`:
+ *   rms_out[row] = rsqrt(mean(x[row]^2) + eps)   (fp32, the reference's [rows, 1] tensor)
+ *   out[row]     = T(float(x[row]) * rms_out[row] * float(w))
+ * x, out [rows, cols] and w [cols] in the 16-bit `dtype`, 16-byte aligned; cols a multiple of 8
+ * (otherwise SMLM_ERR_NO_KERNEL, the reference's "No suitable kernel.").  Runs on `stream` and does
+ * not synchronise (the reference launches on the default stream and then synchronises `stream`). */
+int smlm_b200_rms_norm(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,
+                       int dtype, void* stream);
+
+/* Bytes of the workspace of smlm_b200_rms_norm_bwd (fp32 partial sums of dW, one row per CTA). */
+size_t smlm_b200_rms_norm_bwd_workspace_bytes(int rows, int cols);
+
+/* Backward of the above; replaces the torch expressions of rms_norm.backward
+ * (src/loquetier_src/kernel_utils.py:166-176), which the reference runs as separate passes:
+ *   dW = sum_rows(x * rms * gO)      dX = (gO * w - x * dot * rms^2 / cols) * rms,  dot = sum_cols(gO * w * x)
+ * go, x, dx [rows, cols] and w in `dtype`; rms [rows] fp32 as written by the forward; dw [cols] in
+ * `dtype`, or fp32 when dw_fp32 is set.  Sums are formed in fp32 in a fixed order.  The workspace needs
+ * no initialisation.  rows must be positive. */
+int smlm_b200_rms_norm_bwd(void* dx, void* dw, const void* go, const void* x, const void* w, const float* rms,
+                           void* workspace, size_t workspace_bytes, int rows, int cols, int dtype, int dw_fp32,
+                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_size_t, c_void_p
+from ctypes import c_char_p, c_float, c_int, c_size_t, c_void_p
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsmlm_b200.so")
@@ -41,6 +41,9 @@ SIGNATURES = {
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 11 + [c_void_p]),
     "smlm_b200_bwd": (c_int, [c_void_p] * 14 + [c_size_t] + [c_int] * 10 + [c_void_p]),
+    "smlm_b200_rms_norm": (c_int, [c_void_p] * 4 + [c_int, c_int, c_float, c_int, c_void_p]),
+    "smlm_b200_rms_norm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "smlm_b200_rms_norm_bwd": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 4 + [c_void_p]),
 }
 
 

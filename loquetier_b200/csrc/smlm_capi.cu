@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "../../include/smlm_b200.h"
+#include "rms_norm.cuh"
 #include "smlm_fused.cuh"
 #include "smlm_fused_tc.cuh"
 #include "smlm_merge.cuh"
@@ -402,6 +403,68 @@ int static_scratch_of_current_device(void** out) {
   return SMLM_OK;
 }
 
+// ---- RMSNorm ---------------------------------------------------------------------
+// Kernel variant for rows of n8 16-byte chunks: threads per CTA and chunks per thread (0: two-pass).
+struct RmsShape { int threads, vpt; };
+inline RmsShape rms_shape(int n8) {
+  if (n8 <= 256) return {256, 1};
+  if (n8 <= 512) return {256, 2};
+  if (n8 <= 1024) return {512, 2};
+  if (n8 <= 2048) return {1024, 2};
+  return {1024, 0};
+}
+// persistent CTAs: about 2048 threads per SM in the forward, 512 in the backward (which holds two rows
+// of x, two of gO and its share of dW in registers)
+inline int rms_fwd_grid(int rows, int cols) {
+  return std::max(1, std::min(rows, kNumSMs * (2048 / rms_shape(cols / 8).threads)));
+}
+inline int rms_bwd_grid(int rows, int cols) {
+  return std::max(1, std::min(rows, kNumSMs * std::max(1, 512 / rms_shape(cols / 8).threads)));
+}
+
+template <typename T, int VPT, int NT>
+int launch_rms_fwd_v(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,
+                     cudaStream_t stream) {
+  return launch(rms_norm_fwd_kernel<T, VPT, NT>, dim3(rms_fwd_grid(rows, cols), 1, 1), NT, 1, 0, stream,
+                static_cast<uint4*>(out), rms_out, static_cast<const uint4*>(x), static_cast<const uint4*>(w), rows,
+                cols / 8, 1.0f / static_cast<float>(cols), eps);
+}
+
+template <typename T>
+int launch_rms_fwd(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,
+                   cudaStream_t stream) {
+  const RmsShape sh = rms_shape(cols / 8);
+  if (sh.vpt == 0) return launch_rms_fwd_v<T, 0, 1024>(out, rms_out, x, w, rows, cols, eps, stream);
+  if (sh.threads == 1024) return launch_rms_fwd_v<T, 2, 1024>(out, rms_out, x, w, rows, cols, eps, stream);
+  if (sh.threads == 512) return launch_rms_fwd_v<T, 2, 512>(out, rms_out, x, w, rows, cols, eps, stream);
+  if (sh.vpt == 2) return launch_rms_fwd_v<T, 2, 256>(out, rms_out, x, w, rows, cols, eps, stream);
+  return launch_rms_fwd_v<T, 1, 256>(out, rms_out, x, w, rows, cols, eps, stream);
+}
+
+template <typename T, int VPT, int NT>
+int launch_rms_bwd_v(void* dx, const void* go, const void* x, const void* w, const float* rms, float* partial,
+                     int rows, int cols, int grid, cudaStream_t stream) {
+  return launch(rms_norm_bwd_kernel<T, VPT, NT>, dim3(grid, 1, 1), NT, 1, 0, stream, static_cast<uint4*>(dx),
+                partial, static_cast<const uint4*>(go), static_cast<const uint4*>(x), static_cast<const uint4*>(w),
+                rms, rows, cols / 8, 1.0f / static_cast<float>(cols));
+}
+
+template <typename T>
+int launch_rms_bwd(void* dx, void* dw, const void* go, const void* x, const void* w, const float* rms,
+                   float* partial, int rows, int cols, int dw_fp32, cudaStream_t stream) {
+  const RmsShape sh = rms_shape(cols / 8);
+  const int g = rms_bwd_grid(rows, cols);
+  int rc;
+  if (sh.vpt == 0) rc = launch_rms_bwd_v<T, 0, 1024>(dx, go, x, w, rms, partial, rows, cols, g, stream);
+  else if (sh.threads == 1024) rc = launch_rms_bwd_v<T, 2, 1024>(dx, go, x, w, rms, partial, rows, cols, g, stream);
+  else if (sh.threads == 512) rc = launch_rms_bwd_v<T, 2, 512>(dx, go, x, w, rms, partial, rows, cols, g, stream);
+  else if (sh.vpt == 2) rc = launch_rms_bwd_v<T, 2, 256>(dx, go, x, w, rms, partial, rows, cols, g, stream);
+  else rc = launch_rms_bwd_v<T, 1, 256>(dx, go, x, w, rms, partial, rows, cols, g, stream);
+  if (rc != SMLM_OK) return rc;
+  return launch(rms_norm_dw_kernel<T>, dim3((cols + 31) / 32, 1, 1), kRmsThreads, 1, 0, stream, dw,
+                static_cast<const float*>(partial), g, cols, dw_fp32);
+}
+
 inline bool small_dim_ok(int v) { return v >= 8 && v <= 128 && (v % 8) == 0; }
 inline bool large_dim_ok(int v) { return v >= 8 && (v % 8) == 0; }
 
@@ -636,6 +699,45 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   return smlm_b200_wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, part_ids, part_scale, plan, workspace,
                               workspace_bytes, n_table, npart, T, h_in, h_out, rank, dtype, is_row_major,
                               accumulate_grads, grad_fp32, 0, stream);
+}
+
+int smlm_b200_rms_norm(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,
+                       int dtype, void* stream) {
+  if (rows < 0 || cols <= 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (cols % 8 != 0) return SMLM_ERR_NO_KERNEL;  // the reference's only refusal (rms_norm_cutlass.cu:163-165)
+  if (rows == 0) return SMLM_OK;
+  if (out == nullptr || rms_out == nullptr || x == nullptr || w == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(out) || !aligned16(x) || !aligned16(w) || (reinterpret_cast<uintptr_t>(rms_out) & 3) != 0)
+    return SMLM_ERR_MISALIGNED;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == SMLM_F16 ? launch_rms_fwd<__half>(out, rms_out, x, w, rows, cols, eps, st)
+                           : launch_rms_fwd<__nv_bfloat16>(out, rms_out, x, w, rows, cols, eps, st);
+}
+
+size_t smlm_b200_rms_norm_bwd_workspace_bytes(int rows, int cols) {
+  if (rows <= 0 || cols <= 0 || cols % 8 != 0) return 0;
+  return static_cast<size_t>(rms_bwd_grid(rows, cols)) * cols * sizeof(float);
+}
+
+int smlm_b200_rms_norm_bwd(void* dx, void* dw, const void* go, const void* x, const void* w, const float* rms,
+                           void* workspace, size_t workspace_bytes, int rows, int cols, int dtype, int dw_fp32,
+                           void* stream) {
+  if (rows < 0 || cols <= 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (cols % 8 != 0) return SMLM_ERR_NO_KERNEL;
+  if (dx == nullptr || dw == nullptr || go == nullptr || x == nullptr || w == nullptr || rms == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(dx) || !aligned16(go) || !aligned16(x) || !aligned16(w) || !aligned16(workspace))
+    return SMLM_ERR_MISALIGNED;
+  if (rows == 0) return SMLM_ERR_INVALID_ARGUMENT;  // a sum over no rows: the caller zeroes dW itself
+  if (workspace == nullptr || workspace_bytes < smlm_b200_rms_norm_bwd_workspace_bytes(rows, cols))
+    return SMLM_ERR_WORKSPACE;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* partial = static_cast<float*>(workspace);
+  return dtype == SMLM_F16
+             ? launch_rms_bwd<__half>(dx, dw, go, x, w, rms, partial, rows, cols, dw_fp32, st)
+             : launch_rms_bwd<__nv_bfloat16>(dx, dw, go, x, w, rms, partial, rows, cols, dw_fp32, st);
 }
 
 }  // extern "C"

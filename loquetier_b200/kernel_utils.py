@@ -124,3 +124,46 @@ class add_lora(Function):
                 is_row_major=False)
         grads += [None] * (len(weight_list) - 2 * npart)
         return None, grad_x, None, None, None, None, None, None, *grads
+
+
+class rms_norm(Function):
+    """RMSNorm with the call signature of the reference's autograd function
+    (src/loquetier_src/kernel_utils.py:149-176): ``rms_norm.apply(x, w, eps)`` on a 2-D ``x``.
+    The backward is one native pass instead of the reference's torch expressions; dW is summed in
+    fp32 and returned in the weight's dtype (autograd casts the reference's fp32 sum the same way)."""
+
+    @staticmethod
+    def forward(ctx: FunctionCtx, x: torch.Tensor, w: torch.Tensor, eps: float = 1e-6):
+        from . import kernels
+        m = torch.empty((x.size(0), 1), dtype=torch.float32, device=x.device)
+        o = torch.empty_like(x)
+        kernels.rms_norm(o, m, x, w, eps)
+        ctx.save_for_backward(x, w, m)
+        return o
+
+    @staticmethod
+    def backward(ctx: FunctionCtx, grad_output: torch.Tensor):
+        x, w, rms_1 = ctx.saved_tensors
+        go = grad_output.contiguous()
+        dx = torch.empty_like(x)
+        dw = torch.empty_like(w)
+        if x.size(0) == 0:
+            return dx, dw.zero_(), None
+        ops.rms_norm_bwd(dx, dw, go, x, w, rms_1)
+        return dx, dw, None
+
+
+class MixedLlamaRMSNorm(torch.nn.Module):
+    """The module of src/loquetier_src/models/mixed_llama.py:53-66: same constructor, parameter name
+    and forward (cast to the module dtype, normalise, cast back)."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6, dtype: torch.dtype = torch.bfloat16):
+        super().__init__()
+        self.dtype = dtype
+        self.weight = torch.nn.Parameter(torch.ones(hidden_size, dtype=self.dtype))
+        self.variance_epsilon = eps
+
+    def forward(self, hidden_states: torch.Tensor) -> torch.Tensor:
+        input_dtype = hidden_states.dtype
+        hidden_states = hidden_states.to(self.dtype)
+        return rms_norm.apply(hidden_states, self.weight, self.variance_epsilon).to(input_dtype)

@@ -1,6 +1,6 @@
 """Drop-in for the reference's native module ``loquetier.ops._kernels`` on the SMLM
-path: the same two names with the same arguments and error behaviour
-(pybind registrations at kernel_src/csrc/loquetier_ops.cc:371-372).
+path and for the RMSNorm next to it: the same names with the same arguments and error
+behaviour (pybind registrations at kernel_src/csrc/loquetier_ops.cc:371-373).
 
 ``install_as_loquetier_kernels()`` registers this module under that import name so
 that the reference's ``from loquetier.ops import _kernels as kernel``
@@ -51,9 +51,35 @@ def smlm_forward_cutlass(y: torch.Tensor, x: torch.Tensor, w_ptr: torch.Tensor, 
     ops.gemm(y, x, w_ptr, plan, is_row_major=bool(is_row_major))
 
 
+def rms_norm(output: torch.Tensor, rms_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor,
+             epsilon: float) -> None:
+    """output = input * rsqrt(mean(input^2) + epsilon) * weight per row; rms_output [rows, 1] fp32
+    receives the rsqrt.  Same checks as dispatch_rms_norm (loquetier_ops.cc:326-358).  Runs on the
+    current stream and does not synchronise (the reference launches on the default stream and then
+    synchronises the current one, rms_norm_cutlass.cu:170-173)."""
+    for t, name, dim in ((output, "output", 2), (rms_output, "rms_output", 2), (input, "input", 2),
+                         (weight, "weight", 1)):
+        ops._chk_cuda_contig(t, name, dim)
+    if output.shape != input.shape:
+        raise RuntimeError("CHECK_SHAPE(output, input) failed")
+    if rms_output.size(0) != input.size(0) or rms_output.size(1) != 1:
+        raise RuntimeError("CHECK_EQ(input.size(0), rms_output.size(0)) / CHECK_EQ(1, rms_output.size(1)) failed")
+    if weight.size(0) != input.size(1):
+        raise RuntimeError("CHECK_EQ(input.size(input.dim() - 1), weight.size(0)) failed")
+    if weight.dtype != input.dtype or output.dtype != input.dtype:
+        raise RuntimeError("CHECK_EQ(input.scalar_type(), weight.scalar_type()) failed")
+    if rms_output.dtype != torch.float32:
+        raise RuntimeError("rms_output must be float32")
+    if input.dtype not in (torch.float16, torch.bfloat16) or input.size(1) % 8 != 0:
+        raise RuntimeError(f"No suitable kernel. dtype={input.dtype} columns={input.size(1)}")
+    if input.size(0) == 0:
+        return
+    ops.rms_norm(output, rms_output, input, weight, epsilon)
+
+
 def install_as_loquetier_kernels() -> types.ModuleType:
-    """Make ``import loquetier.ops._kernels`` resolve to this module (only names of
-    the SMLM path exist on it)."""
+    """Make ``import loquetier.ops._kernels`` resolve to this module (only the names of
+    the SMLM path and ``rms_norm`` exist on it)."""
     me = sys.modules[__name__]
     pkg = sys.modules.get("loquetier")
     if pkg is None:

@@ -170,3 +170,28 @@ def bwd(dx, dA_table, dB_table, dv, go, x, v, wa_table, wb_table, plan: Plan, ra
                                 plan.nseg, int(x.size(1)), int(go.size(1)), int(rank), _dtype_code(go),
                                 int(bool(is_row_major)), int(bool(accumulate_grads)), int(bool(grad_fp32)),
                                 _stream(go)), "smlm_b200_bwd")
+
+
+# ---------------------------------------------------------------------------
+# RMSNorm (the caller on either side of the projections)
+# ---------------------------------------------------------------------------
+
+def rms_norm(out: torch.Tensor, rms_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float):
+    """out = x * rsqrt(mean(x^2) + eps) * w per row, rms_out [rows, 1] fp32 gets the rsqrt."""
+    with torch.cuda.device(x.device):
+        check(lib.smlm_b200_rms_norm(out.data_ptr(), rms_out.data_ptr(), x.data_ptr(), w.data_ptr(), int(x.size(0)),
+                                     int(x.size(1)), float(eps), _dtype_code(x), _stream(x)), "smlm_b200_rms_norm")
+    return out
+
+
+def rms_norm_bwd(dx: torch.Tensor, dw: torch.Tensor, go: torch.Tensor, x: torch.Tensor, w: torch.Tensor,
+                 rms: torch.Tensor, workspace: Optional[torch.Tensor] = None):
+    """dX and dW of ``rms_norm``; ``dw`` in the storage type or fp32."""
+    rows, cols = int(x.size(0)), int(x.size(1))
+    need = int(lib.smlm_b200_rms_norm_bwd_workspace_bytes(rows, cols))
+    ws = workspace if workspace is not None else torch.empty(max(need, 16), dtype=torch.uint8, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib.smlm_b200_rms_norm_bwd(dx.data_ptr(), dw.data_ptr(), go.data_ptr(), x.data_ptr(), w.data_ptr(),
+                                         rms.data_ptr(), ws.data_ptr(), ws.numel(), rows, cols, _dtype_code(x),
+                                         int(dw.dtype == torch.float32), _stream(x)), "smlm_b200_rms_norm_bwd")
+    return dx, dw

@@ -60,6 +60,14 @@ def _install_stubs(ref_root: str):
             wm = w32.reshape(d_in, d_out) if is_row_major else w32.reshape(d_out, d_in).t()
             y[a:b] = (x[a:b].to(torch.float32) @ wm).to(y.dtype)
 
+    def rms_norm(o, m, x, w, eps):
+        # the CUDA kernel cannot run here: its arithmetic restated from rms_norm_cutlass.cu:100-155
+        x32 = x.to(torch.float32)
+        s = torch.rsqrt((x32 * x32).sum(dim=1, keepdim=True) / x.size(1) + eps)
+        m.copy_(s)
+        o.copy_((x32 * s * w.to(torch.float32)).to(o.dtype))
+
+    kern.rms_norm = rms_norm
     kern.smlm_forward_cutlass = smlm_forward_cutlass
     kern.smlm_forward_cutlass_tmp_size = smlm_forward_cutlass_tmp_size
     loq = types.ModuleType("loquetier"); loq.__path__ = []
@@ -190,6 +198,23 @@ def golden_add_lora_bwd(ku, name, seed, dtype, part, h_in, h_out, r, T):
         out[f"wa{p}"] = _bits(wa[p]); out[f"wb{p}"] = _bits(wb[p])
         out[f"dA{p}"] = _bits(res[8 + 2 * p]); out[f"dB{p}"] = _bits(res[9 + 2 * p])
     return name, out
+
+
+def golden_rms_norm(ku, name, seed, dtype, rows, cols, eps):
+    """rms_norm.forward / backward of the reference (kernel_utils.py:149-176) run on the CPU: the forward
+    through the stubbed native op, the backward is the reference's own torch code."""
+    g = torch.Generator().manual_seed(seed)
+    x = (torch.randn((rows, cols), generator=g) * 1.5).to(dtype)
+    w = (1.0 + 0.1 * torch.randn((cols,), generator=g)).to(dtype)
+    go = torch.randn((rows, cols), generator=g).to(dtype)
+    ctx = types.SimpleNamespace()
+    ctx.save_for_backward = lambda *t: setattr(ctx, "saved_tensors", t)
+    o = ku.rms_norm.forward(ctx, x, w, eps)
+    dx, dw, none = ku.rms_norm.backward(ctx, go)
+    assert none is None
+    return name, dict(x=_bits(x), w=_bits(w), go=_bits(go), o=_bits(o), rms=ctx.saved_tensors[2].numpy(),
+                      dx=dx.to(torch.float32).numpy(), dw=dw.to(torch.float32).numpy(),
+                      meta=np.asarray([rows, cols, eps], dtype=np.float64), dtype=str(dtype))
 
 
 def golden_batch_len_info(ku):
@@ -323,6 +348,8 @@ def main():
         golden_add_lora_bwd(ku, "bwd_math_fp32", 1006, torch.float32, [0, 24, 24, 61], 96, 80, 8, 70),
         golden_add_lora_bwd(ku, "bwd_math_bf16", 1007, torch.bfloat16, [0, 33, 97], 128, 192, 16, 100),
         golden_add_lora_bwd(ku, "bwd_math_fp16", 1008, torch.float16, [0, 70], 64, 64, 8, 70),
+        golden_rms_norm(ku, "rmsnorm_bf16", 1009, torch.bfloat16, 37, 256, 1e-6),
+        golden_rms_norm(ku, "rmsnorm_fp16", 1010, torch.float16, 5, 520, 1e-5),
     ]
     for name, arrs in cases:
         np.savez_compressed(os.path.join(a.out, name + ".npz"), **arrs)

@@ -244,6 +244,32 @@ def smlm_tmp_size(num_problems: int) -> int:
 
 
 # ----------------------------------------------------------------------------
+# RMSNorm (the caller on either side of the projections)
+# ----------------------------------------------------------------------------
+
+def rms_norm_forward(x: torch.Tensor, w: torch.Tensor, eps: float):
+    """Restates rmsnorm_twoPassAlgo_e8 (kernel_src/csrc/rms_norm/rms_norm_cutlass.cu:80-156): the sum
+    of squares and ``s = rsqrt(sum / n + eps)`` in fp32 (:100-117), then every element as
+    ``T(float(x) * s * float(w))`` (:141-155).  Returns (out in x's dtype, s as fp32 [rows, 1])."""
+    x32 = x.to(torch.float32)
+    s = torch.rsqrt((x32 * x32).sum(dim=1, keepdim=True) / x.size(1) + eps)
+    out = (x32 * s * w.to(torch.float32)).to(x.dtype)
+    return out, s
+
+
+def rms_norm_backward(go: torch.Tensor, x: torch.Tensor, w: torch.Tensor, rms_1: torch.Tensor):
+    """The formulas of rms_norm.backward (src/loquetier_src/kernel_utils.py:166-176) evaluated in fp32
+    from the stored 16-bit operands: dW = sum_rows(x * rms * gO); dX = (gO * w - x * dot * rms^2 / n) * rms
+    with dot = sum_cols(gO * w * x).  Returns (dx, dw) in fp32."""
+    g32, x32, w32 = go.to(torch.float32), x.to(torch.float32), w.to(torch.float32)
+    dw = (x32 * rms_1 * g32).sum(dim=0)
+    dxh = g32 * w32
+    dot = (dxh * x32).sum(dim=1, keepdim=True)
+    dx = (dxh - (x32 * dot * rms_1 ** 2) / x.size(1)) * rms_1
+    return dx, dw
+
+
+# ----------------------------------------------------------------------------
 # seeded synthetic workloads shared by tests and the benchmark's CPU leg
 # ----------------------------------------------------------------------------
 
