@@ -187,6 +187,7 @@ class Workload:
         self.pplan = None
         self.ops = ops
         self.accumulate_grads = False
+        self.grouped = True
         self.after_wgrad = None  # callable(projection index), called on the stream of its weight gradients
         self.overlap = True
         self.n_streams = 3
@@ -194,7 +195,10 @@ class Workload:
         self.torch = torch
 
     def build_plans(self):
-        self.plan = self.ops.Plan(self.seg, self.T)
+        # grouped where it changes anything: decode tokens are gathered by adapter for the forward launches
+        from loquetier_b200.segments import wants_grouped_plan
+        g = self.grouped and wants_grouped_plan(self.spec["lens"], self.spec["ids"])
+        self.plan = self.ops.Plan(self.seg, self.T, seg_ids=self.ids if g else None, n_table=self.spec["n_adapters"])
         if self.tl:
             self.pplan = self.ops.Plan(self.part, self.tl)
 
@@ -536,6 +540,7 @@ def main():
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-kernel-class timing pass")
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
+    ap.add_argument("--no-group", action="store_true", help="plan without grouping short segments by adapter")
     ap.add_argument("--seg-len", type=int, default=0, help="c5 only: tokens per segment instead of 2048 "
                                                           "(a smaller footprint for profiler captures)")
     a = ap.parse_args()
@@ -597,6 +602,7 @@ def main():
 
     wl = Workload(spec, dev)
     wl.overlap = not a.no_overlap
+    wl.grouped = not a.no_group
     wl.n_streams = a.streams
     bucket = None
     if a.workload == "c5":

@@ -43,7 +43,8 @@ enum {
   SMLM_ERR_BAD_POINTER = 8,      /* reported by smlm_b200_plan_status */
   SMLM_ERR_BAD_INDEX = 9,        /* reported by smlm_b200_plan_status */
   SMLM_ERR_TIMEOUT = 10,         /* reported by smlm_b200_plan_status: a bounded wait in a kernel gave up */
-  SMLM_ERR_STATIC_LIMIT = 11     /* smlm_b200_wgrad_static: the problem needs more than the built-in scratch */
+  SMLM_ERR_STATIC_LIMIT = 11,    /* smlm_b200_wgrad_static: the problem needs more than the built-in scratch */
+  SMLM_ERR_GROUPED_PLAN = 12     /* reported by smlm_b200_plan_status: a grouped plan reached a launch that cannot use it */
 };
 
 enum { SMLM_F16 = 0, SMLM_BF16 = 1 };
@@ -89,6 +90,20 @@ size_t smlm_b200_plan_bytes(int T, int nseg);
  * projection of a model step).  `plan` must be 16-byte aligned. */
 int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int nseg, int T, void* stream);
 
+/* The same, for the forward entry points when they are called with an adapter table and seg_ids:
+ * segments of at most 8 rows (decode tokens) are not given pieces of their own; their rows are grouped
+ * by adapter, wherever they sit in the batch, so that the kernels fetch an adapter's panels once for all
+ * of its decode tokens.  The reference gets this effect only when its batch assembler has sorted the
+ * decode requests by adapter (src/loquetier_src/model_generation.py:186, 267-273); here the order of the
+ * batch does not matter.  seg_ids[nseg] is the per-segment adapter index the compute call will also be
+ * given, n_table the table size (tables above 4096 entries, or seg_ids == NULL, give the ordinary plan).
+ * A grouped plan serves smlm_b200_gemm / smlm_b200_fwd / smlm_b200_bwd_dx with that seg_ids and table and
+ * `grouped = 1`; the weight-gradient entry points need an ordinary plan (they record SMLM_ERR_GROUPED_PLAN
+ * otherwise).  The tcgen05 kernels read the plan's list of 128-row pieces, which is never grouped.
+ * Same buffer size as smlm_b200_plan. */
+int smlm_b200_plan_grouped(void* plan, size_t plan_bytes, const int32_t* seg_indptr, const int32_t* seg_ids,
+                           int nseg, int n_table, int T, void* stream);
+
 /* Synchronises the stream and reports what the device recorded in a plan: number
  * of pieces and SMLM_OK or one of the SMLM_ERR_BAD_* codes.  For tests and
  * debugging; the compute entry points never synchronise. */
@@ -100,10 +115,12 @@ int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream);
  * smlm_forward, smlm_forward_cutlass.cuh:61-175): d_in >= d_out runs the shrink
  * kernel, d_in < d_out the expand kernel.  With seg_scale == NULL and
  * accumulate == 0 the result is the reference's (alpha 1, beta 0: rows inside
- * segments overwritten, other rows untouched). */
+ * segments overwritten, other rows untouched).  `grouped` must be 1 when `plan` comes from
+ * smlm_b200_plan_grouped (the launch then runs the kernel variant that knows gather pieces) and 0
+ * otherwise; a grouped plan passed with 0 is refused piece by piece (SMLM_ERR_GROUPED_PLAN). */
 int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int32_t* seg_ids,
                    const float* seg_scale, void* plan, int n_table, int T, int nseg, int d_in, int d_out,
-                   int dtype, int is_row_major, int accumulate, void* stream);
+                   int dtype, int is_row_major, int accumulate, int grouped, void* stream);
 
 /* Fused LoRA forward  v = x . A^T ;  y (+)= scale * v . B^T  for every segment:
  * the two operator calls of add_lora.forward (kernel_utils.py:114-120) and, with
@@ -117,11 +134,11 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
  * that kernel is still running - its read phase overlaps the predecessor's write
  * phase, which is how both directions of HBM are kept busy - and it still completes
  * after it, so stream order holds for everything enqueued later.  With 0 the launch
- * waits for its predecessor like any kernel. */
+ * waits for its predecessor like any kernel.  `grouped` as in smlm_b200_gemm. */
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
                   int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, int independent,
-                  void* stream);
+                  int grouped, void* stream);
 
 /* Bytes of the workspace the weight-gradient kernels need for a batch of T token
  * rows in npart partitions and one (h1 == 0) or two column counts.  The workspace
@@ -182,11 +199,12 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
 
 /* First half of the backward: dV = scale * gO . B (written to dv [T, rank]) and
  * dX = dV . A for the rows of every train partition (kernel_utils.py:142-143), one
- * launch.  `plan` is built on the partition index pointer; `independent` as in
+ * launch.  `plan` is built on the partition index pointer; `independent` and `grouped` as in
  * smlm_b200_fwd. */
 int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
                      const int32_t* part_ids, const float* part_scale, void* plan, int n_table, int T, int npart,
-                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, void* stream);
+                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, int grouped,
+                     void* stream);
 
 /* Fine-tuning backward of the fused forward over the train partitions
  * part_indptr[npart + 1] (add_lora.backward, kernel_utils.py:129-147):

@@ -19,6 +19,7 @@ STATUS_NAMES = {
     0: "SMLM_OK", 1: "SMLM_ERR_INVALID_ARGUMENT", 2: "SMLM_ERR_DTYPE", 3: "SMLM_ERR_NO_KERNEL",
     4: "SMLM_ERR_MISALIGNED", 5: "SMLM_ERR_WORKSPACE", 6: "SMLM_ERR_CUDA", 7: "SMLM_ERR_BAD_INDPTR",
     8: "SMLM_ERR_BAD_POINTER", 9: "SMLM_ERR_BAD_INDEX", 10: "SMLM_ERR_TIMEOUT", 11: "SMLM_ERR_STATIC_LIMIT",
+    12: "SMLM_ERR_GROUPED_PLAN",
 }
 
 # name -> (restype, argtypes); mirrors include/smlm_b200.h one to one
@@ -31,11 +32,12 @@ SIGNATURES = {
     "smlm_b200_set_tensor_core_mode": (c_int, [c_int]),
     "smlm_b200_plan_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_plan": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p]),
+    "smlm_b200_plan_grouped": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "smlm_b200_plan_status": (c_int, [c_void_p, ctypes.POINTER(c_int), c_void_p]),
     "smlm_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "smlm_b200_fwd": (c_int, [c_void_p] * 8 + [c_int] * 10 + [c_void_p]),
-    "smlm_b200_bwd_dx": (c_int, [c_void_p] * 8 + [c_int] * 9 + [c_void_p]),
+                               c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_fwd": (c_int, [c_void_p] * 8 + [c_int] * 11 + [c_void_p]),
+    "smlm_b200_bwd_dx": (c_int, [c_void_p] * 8 + [c_int] * 10 + [c_void_p]),
     "smlm_b200_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),

@@ -134,18 +134,21 @@ int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cud
 // ---- fused shrink + expand ----------------------------------------------------
 
 template <typename T, int R16, bool RM>
-int launch_fused(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cudaStream_t stream) {
-  return launch(fused_kernel<T, R16, RM>, dim3(max_pieces * a.ksplit, 1, 1), kFusedThreads, a.ksplit,
-                FusedSmem<R16, RM>::kTotal, stream, a, tm);
+int launch_fused(const FusedArgs& a, const FusedMaps& tm, int max_pieces, bool grouped, cudaStream_t stream) {
+  const dim3 grid(max_pieces * a.ksplit, 1, 1);
+  return grouped ? launch(fused_kernel<T, R16, RM, true>, grid, kFusedThreads, a.ksplit, FusedSmem<R16, RM>::kTotal,
+                          stream, a, tm)
+                 : launch(fused_kernel<T, R16, RM, false>, grid, kFusedThreads, a.ksplit,
+                          FusedSmem<R16, RM>::kTotal, stream, a, tm);
 }
 
 template <typename T, bool RM>
-int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, cudaStream_t stream) {
+int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, bool grouped, cudaStream_t stream) {
   const int r16 = (a.R + 15) / 16;
-  if (r16 <= 1) return launch_fused<T, 1, RM>(a, tm, max_pieces, stream);
-  if (r16 <= 2) return launch_fused<T, 2, RM>(a, tm, max_pieces, stream);
-  if (r16 <= 4) return launch_fused<T, 4, RM>(a, tm, max_pieces, stream);
-  return launch_fused<T, 8, RM>(a, tm, max_pieces, stream);
+  if (r16 <= 1) return launch_fused<T, 1, RM>(a, tm, max_pieces, grouped, stream);
+  if (r16 <= 2) return launch_fused<T, 2, RM>(a, tm, max_pieces, grouped, stream);
+  if (r16 <= 4) return launch_fused<T, 4, RM>(a, tm, max_pieces, grouped, stream);
+  return launch_fused<T, 8, RM>(a, tm, max_pieces, grouped, stream);
 }
 
 // ---- the tcgen05 variant for ranks above 32 ----------------------------------
@@ -177,7 +180,7 @@ inline bool use_tensor_core_kernel(int T, int nseg, int R, int mode) {
 int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
               const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
               int N2, int dtype, int row_major, int scale_mid, int accumulate, int independent, int mode,
-              cudaStream_t stream) {
+              int grouped, cudaStream_t stream) {
   FusedArgs a;
   a.out = out; a.mid = mid; a.w1_table = w1_table; a.w2_table = w2_table; a.ids = ids; a.scale = scale;
   a.plan = static_cast<int*>(plan);
@@ -237,14 +240,16 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   const int in_cols = mode == kFusedExpandOnly ? N2 : K1;
   void* out_t = mode == kFusedShrinkOnly ? const_cast<void*>(in) : out;
   const int out_cols = mode == kFusedShrinkOnly ? K1 : N2;
+  a.in = in_t;
   if (!make_map_2d(&tm.in8, in_t, T, in_cols, 8, dtype) || !make_map_2d(&tm.in16, in_t, T, in_cols, 16, dtype) ||
       !make_map_2d(&tm.out, out_t, T, out_cols, 16, dtype) || !make_map_2d(&tm.out8, out_t, T, out_cols, 8, dtype))
     return SMLM_ERR_CUDA;
+  const bool g = grouped != 0;
   if (dtype == SMLM_F16)
-    return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, stream)
-                     : dispatch_fused_r<__half, false>(a, tm, mp, stream);
-  return row_major ? dispatch_fused_r<__nv_bfloat16, true>(a, tm, mp, stream)
-                   : dispatch_fused_r<__nv_bfloat16, false>(a, tm, mp, stream);
+    return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, g, stream)
+                     : dispatch_fused_r<__half, false>(a, tm, mp, g, stream);
+  return row_major ? dispatch_fused_r<__nv_bfloat16, true>(a, tm, mp, g, stream)
+                   : dispatch_fused_r<__nv_bfloat16, false>(a, tm, mp, g, stream);
 }
 
 // ---- wgrad ------------------------------------------------------------------
@@ -489,6 +494,8 @@ const char* smlm_b200_status_string(int status) {
     case SMLM_ERR_BAD_POINTER: return "adapter pointer is null or not 16-byte aligned";
     case SMLM_ERR_BAD_INDEX: return "adapter index outside the table";
     case SMLM_ERR_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    case SMLM_ERR_GROUPED_PLAN:
+      return "a weight-gradient call was handed a grouped plan; build an ordinary plan for it";
     case SMLM_ERR_STATIC_LIMIT:
       return "problem too large for the library's built-in 16 MiB scratch; use the entry point that takes a "
              "workspace";
@@ -503,17 +510,29 @@ size_t smlm_b200_tmp_size(int num_problems) {
 
 size_t smlm_b200_plan_bytes(int T, int nseg) {
   if (T < 0 || nseg < 0) return 0;
+  // two piece lists, then the row index array of a grouped plan (one int per token row)
   return sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_pieces_of(T, nseg) + 1) +
-         sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_tall_pieces_of(T, nseg) + 1);
+         sizeof(int) * kPlanHeaderInts + sizeof(Piece) * static_cast<size_t>(max_tall_pieces_of(T, nseg) + 1) +
+         sizeof(int) * (static_cast<size_t>(T) + 4);
 }
 
 int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int nseg, int T, void* stream) {
-  if (plan == nullptr || seg_indptr == nullptr || nseg < 0 || T < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  return smlm_b200_plan_grouped(plan, plan_bytes, seg_indptr, nullptr, nseg, 0, T, stream);
+}
+
+int smlm_b200_plan_grouped(void* plan, size_t plan_bytes, const int32_t* seg_indptr, const int32_t* seg_ids,
+                           int nseg, int n_table, int T, void* stream) {
+  if (plan == nullptr || seg_indptr == nullptr || nseg < 0 || T < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (plan_bytes < smlm_b200_plan_bytes(T, nseg)) return SMLM_ERR_WORKSPACE;
+  // tables beyond what the builder can count in shared memory get an ordinary plan
+  if (seg_ids == nullptr || n_table == 0 || n_table > kGatherMaxTable) {
+    seg_ids = nullptr;
+    n_table = 0;
+  }
   plan_pieces_kernel<<<1, kPlanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<int*>(plan), seg_indptr, nseg, T, max_pieces_of(T, nseg), piece_rows_for(T),
-      max_tall_pieces_of(T, nseg), tall_rows_for(T, nseg));
+      max_tall_pieces_of(T, nseg), tall_rows_for(T, nseg), seg_ids, n_table);
   if (cudaGetLastError() != cudaSuccess) return SMLM_ERR_CUDA;
   return SMLM_OK;
 }
@@ -544,12 +563,13 @@ int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream) {
   if (hdr[1] & kErrBadIndex) return SMLM_ERR_BAD_INDEX;
   if (hdr[1] & kErrBadPointer) return SMLM_ERR_BAD_POINTER;
   if (hdr[1] & kErrTimeout) return SMLM_ERR_TIMEOUT;
+  if (hdr[1] & kErrGrouped) return SMLM_ERR_GROUPED_PLAN;
   return SMLM_OK;
 }
 
 int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int32_t* seg_ids,
                    const float* seg_scale, void* plan, int n_table, int T, int nseg, int d_in, int d_out,
-                   int dtype, int is_row_major, int accumulate, void* stream) {
+                   int dtype, int is_row_major, int accumulate, int grouped, void* stream) {
   if (T < 0 || nseg < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (T == 0 || nseg == 0) return SMLM_OK;
@@ -561,12 +581,12 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
     if (!small_dim_ok(d_out) || !large_dim_ok(d_in)) return SMLM_ERR_NO_KERNEL;
     if (accumulate) return SMLM_ERR_NO_KERNEL;
     return run_fused(nullptr, y, x, w_table, nullptr, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, 64,
-                     dtype, is_row_major, 1, 0, 0, kFusedShrinkOnly, st);
+                     dtype, is_row_major, 1, 0, 0, kFusedShrinkOnly, grouped, st);
   }
   // expand: the small dimension is the input width; x plays the part of MID
   if (!small_dim_ok(d_in) || !large_dim_ok(d_out)) return SMLM_ERR_NO_KERNEL;
   return run_fused(y, const_cast<void*>(x), nullptr, nullptr, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, 64,
-                   d_in, d_out, dtype, is_row_major, 0, accumulate, 0, kFusedExpandOnly, st);
+                   d_in, d_out, dtype, is_row_major, 0, accumulate, 0, kFusedExpandOnly, grouped, st);
 }
 
 int smlm_b200_set_tensor_core_mode(int mode) {
@@ -577,7 +597,7 @@ int smlm_b200_set_tensor_core_mode(int mode) {
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
                   int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, int independent,
-                  void* stream) {
+                  int grouped, void* stream) {
   if (T < 0 || nseg < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (T == 0 || nseg == 0) return SMLM_OK;
@@ -587,7 +607,7 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
   if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
   return run_fused(y, v, x, wa_table, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, h_in, rank, h_out,
-                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0, kFusedBoth,
+                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0, kFusedBoth, grouped,
                    static_cast<cudaStream_t>(stream));
 }
 
@@ -666,7 +686,8 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
 
 int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
                      const int32_t* part_ids, const float* part_scale, void* plan, int n_table, int T, int npart,
-                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, void* stream) {
+                     int h_in, int h_out, int rank, int dtype, int is_row_major, int independent, int grouped,
+                     void* stream) {
   if (T < 0 || npart < 0 || n_table < 0) return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (T == 0 || npart == 0) return SMLM_OK;
@@ -679,7 +700,7 @@ int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_t
   // [K = h_out][N = r] operand; the math layout B [r, h_out] is the column-major one.  The layout
   // flag therefore flips for both products of this launch (dX = dV . A likewise).
   return run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
-                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0, kFusedBoth,
+                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0, kFusedBoth, grouped,
                    static_cast<cudaStream_t>(stream));
 }
 
@@ -692,7 +713,7 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   if (dA_table == nullptr || dB_table == nullptr || x == nullptr || v == nullptr || part_indptr == nullptr)
     return SMLM_ERR_INVALID_ARGUMENT;
   const int rc = smlm_b200_bwd_dx(dx, dv, go, wa_table, wb_table, part_ids, part_scale, plan, n_table, T, npart,
-                                  h_in, h_out, rank, dtype, is_row_major, 0, stream);
+                                  h_in, h_out, rank, dtype, is_row_major, 0, 0, stream);
   if (rc != SMLM_OK) return rc;
   // dB = scale * gO^T . V ([h_out, r] in the PEFT layout: transposed store) and
   // dA = dV^T . X ([r, h_in] in the PEFT layout; dV already carries the scale), in one launch

@@ -21,13 +21,25 @@ constexpr int kErrBadIndptr = 1;    // indptr not monotone, negative or beyond T
 constexpr int kErrBadPointer = 2;   // an adapter pointer is null or not 16-byte aligned
 constexpr int kErrBadIndex = 4;     // an adapter index outside the table
 constexpr int kErrTimeout = 8;      // a bounded wait on a shared-memory barrier ran out
+constexpr int kErrGrouped = 16;     // a kernel that needs contiguous pieces was handed a grouped plan
+
+constexpr int kGatherMaxLen = 8;    // segments of at most this many rows are grouped by adapter
+constexpr int kGatherRows = 48;     // rows of a gather piece at most (its rows sit padded in a ring stage)
+constexpr int kGatherMaxTable = 4096;  // largest adapter table a grouped plan is built for
 
 struct __align__(16) Piece {
-  int row0;   // first token row
+  int row0;   // first token row; gather piece: first entry of its rows in the plan's row index array
   int nrows;  // 1..kBM
-  int seg;    // segment (or train partition) the rows belong to
-  int pad;
+  int seg;    // segment (or train partition) the rows belong to; gather piece: the adapter index itself
+  int pad;    // 0: nrows consecutive rows of one segment; 1: gather piece, rows of short segments of one adapter
 };
+
+// Where the row index array of a grouped plan starts (ints from the start of the plan buffer): behind the
+// two piece lists, whose capacities are recorded in their headers.
+__device__ __forceinline__ const int* plan_row_index(const int* plan) {
+  const int* tall = plan + kPlanHeaderInts + 4 * (plan[2] + 1);
+  return tall + kPlanHeaderInts + 4 * (tall[2] + 1);
+}
 
 // ---------------------------------------------------------------------------
 // shared-memory addressing

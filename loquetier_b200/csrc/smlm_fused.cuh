@@ -8,6 +8,12 @@
 //             scale and add of MixedLoraLinear.forward, models/mixed_lora.py:214-217)
 //   backward: IN = gO, W1 = B, W2 = A, MID = dV, OUT = dX  (kernel_utils.py:142-143)
 //
+// A gather piece (Piece::pad = 1, from a grouped plan) holds rows of short segments that share an
+// adapter but not a place in the batch: each row's slice of a ring stage arrives as one untiled bulk copy
+// (1 KB; one tensor copy per row and 64-column chunk moved 128 bytes at a time and ran at a fraction of
+// the speed) into rows padded by 16 bytes, which keeps ldmatrix free of bank conflicts without a
+// swizzle; MID and OUT rows go out through the row index; everything between is the same.  This is the decode (BGMV-style) case with the adapter's panels streamed once.
+//
 // The same kernel also runs either half alone (FusedArgs::mode), which is one call of the
 // reference operator smlm_forward_cutlass: shrink only (MID is the result) or expand only
 // (MID is the input).
@@ -35,6 +41,8 @@
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda.h>
+
+#include <type_traits>
 
 #include "smlm_common.cuh"
 
@@ -71,6 +79,8 @@ struct FusedSmem {
   static constexpr int CH = fused_chunks(R16);
   static constexpr int KC = 64 * CH;            // K1 columns per ring stage
   static constexpr int WPad = KC * 2 + 16;      // bytes between W1 rows in shared memory ([R][K1] layout)
+  static constexpr int XPad = KC * 2 + 16;      // bytes between the rows of a gather piece in a ring stage
+  static_assert(kGatherRows * XPad <= kBM * KC * 2, "a gather piece must fit the stage's IN region");
   static constexpr int kStages = fused_stages(R16);
   static constexpr int kXBytes = kBM * KC * 2;  // 4 row blocks x CH column chunks of [16][64]
   static constexpr int kW1Raw = RM ? KC * KP * 2 : KP * WPad;
@@ -95,6 +105,7 @@ struct FusedSmem {
 };
 
 struct FusedArgs {
+  const void* in;               // [T, K1] (gather pieces read it through this pointer, the others through TMA)
   void* out;                    // [T, N2]
   void* mid;                    // [T, R]
   const void* const* w1_table;  // shrink panels
@@ -127,7 +138,7 @@ __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
 }
 
-template <typename T, int R16, bool RM>
+template <typename T, int R16, bool RM, bool GATHER>
 __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_kernel(const FusedArgs a,
                                                                 const __grid_constant__ FusedMaps tm) {
   extern __shared__ unsigned char smem_raw[];
@@ -162,16 +173,33 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const int nrows = pc.nrows;
   const int K1 = a.K1, R = a.R, N2 = a.N2;
   int* err = a.plan + 1;
+  // GATHER is a compile-time switch because the extra paths cost the ordinary launch about 3 %: only
+  // launches whose caller announces a grouped plan run the instantiation that knows gather pieces
+  const bool gather = GATHER && pc.pad != 0;
+  if (!GATHER && pc.pad != 0) {  // a grouped plan handed to a launch that was not told so: refuse the piece
+    if (tid == 0) atomicOr(a.plan + 1, kErrGrouped);
+    if (a.independent) pdl_wait();
+    return;
+  }
+  // rows of a gather piece; its adapter index sits in the piece itself
+  const int* rowidx = gather ? plan_row_index(a.plan) + pc.row0 : nullptr;
+  if (gather && a.ids == nullptr && tid == 0) atomicOr(err, kErrBadIndex);  // grouped plans need the adapter table
 
   const int mode = a.mode;
-  const T* w1 = mode == kFusedExpandOnly
-                    ? nullptr
-                    : static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
-  const T* w2 = mode == kFusedShrinkOnly
-                    ? nullptr
-                    : static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
-  const bool w_ok = (w1 != nullptr || mode == kFusedExpandOnly) && (w2 != nullptr || mode == kFusedShrinkOnly);
-  const float sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
+  const T* w1 = nullptr;
+  const T* w2 = nullptr;
+  float sc = 1.0f;
+  if (!gather) {
+    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
+    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
+    sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
+  } else if (a.ids != nullptr && pc.seg >= 0 && pc.seg < a.n_table) {
+    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(a.w1_table, nullptr, a.n_table, pc.seg, err));
+    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(a.w2_table, nullptr, a.n_table, pc.seg, err));
+    sc = a.scale != nullptr ? a.scale[pc.seg] : 1.0f;
+  }
+  const bool w_ok = (w1 != nullptr || mode == kFusedExpandOnly) && (w2 != nullptr || mode == kFusedShrinkOnly) &&
+                    !(gather && a.ids == nullptr);
   const float sc_mid = (a.scale_mid || mode == kFusedShrinkOnly) ? sc : 1.0f;
   const float sc_out = (a.scale_mid || mode == kFusedShrinkOnly) ? 1.0f : sc;
 
@@ -196,6 +224,14 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       mbar_init(empty0 + s * 8, NW);
     }
     fence_mbar_init();
+  }
+  if (gather && (K1 & 15) != 0 && tid < nrows) {
+    // the last 16-column step of a row reaches 8 columns past K1, which a bulk copy does not fill:
+    // clear them in every stage (W1 holds zeros there, but zero times a non-finite leftover is not zero)
+    const int tail = (K1 % KC) * 2;
+    for (int s = 0; s < S; ++s)
+      *reinterpret_cast<uint4*>(smem + s * SM::kStage + tid * SM::XPad + tail) = make_uint4(0, 0, 0, 0);
+    fence_proxy_async();
   }
   if ((K1 % 64) != 0) {
     // the last 64-column chunk is only partly overwritten by the panel copies: start from zeros so
@@ -237,7 +273,8 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       const int kcols = min(KC, K1 - k0);
       const int nch = (kcols + 63) >> 6;
       const uint32_t wbytes = static_cast<uint32_t>(kcols) * R * 2;
-      if (lane == 0) mbar_expect_tx(fb, rowbytes * nch + wbytes);
+      if (lane == 0)
+        mbar_expect_tx(fb, (gather ? static_cast<uint32_t>(nrows) * kcols * 2 : rowbytes * nch) + wbytes);
       __syncwarp();
       if constexpr (!RM) {
         for (int n = lane; n < R; n += 32)
@@ -245,50 +282,64 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       } else {
         if (lane == 0) bulk_load(ws, w1 + static_cast<size_t>(k0) * R, wbytes, fb);
       }
-      for (int i = lane; i < nblk * nch; i += 32) {
-        const int b = i / nch, c = i - b * nch;
-        tma_load_2d(xs + (b * CH + c) * 2048, (last8 && b == nblk - 1) ? &tm.in8 : &tm.in16, k0 + c * 64,
-                    pc.row0 + b * 16, fb);
+      if (!gather) {
+        for (int i = lane; i < nblk * nch; i += 32) {
+          const int b = i / nch, c = i - b * nch;
+          tma_load_2d(xs + (b * CH + c) * 2048, (last8 && b == nblk - 1) ? &tm.in8 : &tm.in16, k0 + c * 64,
+                      pc.row0 + b * 16, fb);
+        }
+      } else {
+        // one bulk copy per row: its kcols columns of this K step, into rows XPad bytes apart
+        const T* in = static_cast<const T*>(a.in);
+        for (int r = lane; r < nrows; r += 32)
+          bulk_load(xs + r * SM::XPad, in + static_cast<size_t>(rowidx[r]) * K1 + k0, kcols * 2, fb);
       }
     }
   } else {
     const bool active = (wm * 16 < nrows);
-    for (int it = 0; it < nk; ++it) {
-      const int slot = it % S;
-      const uint32_t xs = base + slot * SM::kStage;
-      const uint32_t ws = xs + SM::kXBytes;
-      mbar_wait(full0 + slot * 8, (it / S) & 1, err, dead);
-      if (active) {
-        const int kstep = kbeg + (it + krot < nk ? it + krot : it + krot - nk);
-        const int kmax = (min(KC, K1 - kstep * KC) + 15) >> 4;
-        for (int kk = wk; kk < kmax; kk += WK) {
-          uint32_t af[4];
-          {
-            const int m = lane >> 3;
-            const int r = (m & 1) * 8 + (lane & 7);
-            const int c = (kk & 3) * 2 + (m >> 1);
-            ldsm_x4(af, xs + (wm * CH + (kk >> 2)) * 2048 + r * 128 + ((c ^ (r & 7)) << 4));
-          }
-#pragma unroll
-          for (int j = 0; j < NT; j += 2) {
-            uint32_t bf[4];
-            const int m = lane >> 3;
-            if constexpr (!RM) {
-              const int n = (j + (m >> 1)) * 8 + (lane & 7);
-              ldsm_x4(bf, ws + n * WPad + ((kk * 2 + (m & 1)) << 4));
-            } else {
-              // panel stored [K1][R] with rows of R elements, exactly as in global memory
-              const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
-              ldsm_x4_t(bf, ws + k * (R * 2) + ((j + (m >> 1)) << 4));
+    // the loop exists twice, once per stage layout, so that the common one carries no test per step
+    auto consume = [&](auto gathered) {
+      constexpr bool G = decltype(gathered)::value;
+      for (int it = 0; it < nk; ++it) {
+        const int slot = it % S;
+        const uint32_t xs = base + slot * SM::kStage;
+        const uint32_t ws = xs + SM::kXBytes;
+        mbar_wait(full0 + slot * 8, (it / S) & 1, err, dead);
+        if (active) {
+          const int kstep = kbeg + (it + krot < nk ? it + krot : it + krot - nk);
+          const int kmax = (min(KC, K1 - kstep * KC) + 15) >> 4;
+          for (int kk = wk; kk < kmax; kk += WK) {
+            uint32_t af[4];
+            {
+              const int m = lane >> 3;
+              const int r = (m & 1) * 8 + (lane & 7);
+              const int c = (kk & 3) * 2 + (m >> 1);
+              if constexpr (!G) ldsm_x4(af, xs + (wm * CH + (kk >> 2)) * 2048 + r * 128 + ((c ^ (r & 7)) << 4));
+              else ldsm_x4(af, xs + (wm * 16 + r) * SM::XPad + kk * 32 + (m >> 1) * 16);
             }
-            mma16816<T>(acc[j], af, bf[0], bf[1]);
-            mma16816<T>(acc[j + 1], af, bf[2], bf[3]);
+#pragma unroll
+            for (int j = 0; j < NT; j += 2) {
+              uint32_t bf[4];
+              const int m = lane >> 3;
+              if constexpr (!RM) {
+                const int n = (j + (m >> 1)) * 8 + (lane & 7);
+                ldsm_x4(bf, ws + n * WPad + ((kk * 2 + (m & 1)) << 4));
+              } else {
+                // panel stored [K1][R] with rows of R elements, exactly as in global memory
+                const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
+                ldsm_x4_t(bf, ws + k * (R * 2) + ((j + (m >> 1)) << 4));
+              }
+              mma16816<T>(acc[j], af, bf[0], bf[1]);
+              mma16816<T>(acc[j + 1], af, bf[2], bf[3]);
+            }
           }
         }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + slot * 8);
       }
-      __syncwarp();
-      if (lane == 0) mbar_arrive(empty0 + slot * 8);
-    }
+    };
+    if (gather) consume(std::true_type{});
+    else consume(std::false_type{});
   }
 
   // ======================= phase 2: reduce the K1 slices, build MID =======================
@@ -314,16 +365,17 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const uint32_t mids = base + SM::kMidOff;  // MID tile [64][KP] in the storage type, swizzled rows
   {
     const int load_rows = min(kBM, ((nrows + 15) >> 4) << 4);
-    T* mrow = static_cast<T*>(a.mid) + static_cast<size_t>(pc.row0) * R;
+    T* const mbase = static_cast<T*>(a.mid);
     constexpr int HP = KP / 2;
     for (int e = tid; e < load_rows * HP; e += kFusedThreads) {
       const int r = e / HP;
       const int n = (e - r * HP) * 2;
       const int fm = r >> 4, r16 = r & 15;
       const bool inside = r < nrows && n < R && w_ok;
+      T* mrow = inside ? mbase + static_cast<size_t>(gather ? rowidx[r] : pc.row0 + r) * R + n : mbase;
       uint32_t packed = 0;
       if (mode == kFusedExpandOnly) {
-        if (inside) packed = *reinterpret_cast<const uint32_t*>(mrow + static_cast<size_t>(r) * R + n);
+        if (inside) packed = *reinterpret_cast<const uint32_t*>(mrow);
       } else {
         float2 s = make_float2(0.f, 0.f);
         if (inside) {
@@ -337,7 +389,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
           }
         }
         packed = pack2<T>(s.x * sc_mid, s.y * sc_mid);
-        if (z == 0 && inside) *reinterpret_cast<uint32_t*>(mrow + static_cast<size_t>(r) * R + n) = packed;
+        if (z == 0 && inside) *reinterpret_cast<uint32_t*>(mrow) = packed;
       }
       const int c = n >> 3;
       asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(mids + r * (XC * 16) + (swz<XC>(r, c) << 4) + (n & 7) * 2),
@@ -406,10 +458,20 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       }
     }
     const int rows_here = min(16, nrows - wm * 16);
-    const bool full_block = (rows_here == 16) || (rows_here == 8);
+    const bool full_block = !gather && ((rows_here == 16) || (rows_here == 8));
     const CUtensorMap* omap = rows_here == 8 ? &tm.out8 : &tm.out;
     const uint32_t ostage = base + SM::kOutOff + warp * 8192;
-    T* dbase = static_cast<T*>(a.out) + static_cast<size_t>(pc.row0 + wm * 16) * N2;
+    // rows a lane writes in the plain-store path (row q * 4 + lane / 8 of the warp's block), as element
+    // offsets into OUT; a gather piece looks its rows up once, here
+    size_t orow_off[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int r = q * 4 + (lane >> 3);
+      int orow = pc.row0 + wm * 16 + r;
+      if (gather && r < rows_here) orow = rowidx[wm * 16 + r];
+      orow_off[q] = static_cast<size_t>(orow) * N2;
+    }
+    T* const obase = static_cast<T*>(a.out);
     int obuf = 0;
 
     for (int si = 0; si < ns; ++si) {
@@ -493,7 +555,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
                   asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
                                : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                                : "r"(os + gi * 2048 + r * 128 + ((c ^ (r & 7)) << 4)));
-                  uint4* dst = reinterpret_cast<uint4*>(dbase + static_cast<size_t>(r) * N2 + n0 + col);
+                  uint4* dst = reinterpret_cast<uint4*>(obase + orow_off[q] + n0 + col);
                   if (a.accumulate) {
                     const uint4 old = *dst;
                     const uint32_t* ov = reinterpret_cast<const uint32_t*>(&old);

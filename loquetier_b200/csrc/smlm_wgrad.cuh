@@ -157,7 +157,11 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
   }
 
   if (tid < np) {
-    const Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[pbeg + tid];
+    Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[pbeg + tid];
+    if (pc.pad != 0) {  // a gather piece of a grouped plan: not a row range of one partition
+      atomicOr(err, kErrGrouped);
+      pc.row0 = 0; pc.nrows = 0; pc.seg = 0;
+    }
     pcs[tid] = pc;
     bounds[tid] = make_int2(a.part_indptr[pc.seg], a.part_indptr[pc.seg + 1]);
     gouts[tid] = g_table[pc.seg];

@@ -19,6 +19,7 @@ from torch.autograd.function import Function
 
 from . import ops
 from .kernel_utils import BatchLenInfo, _ptr_table, add_lora
+from .segments import wants_grouped_plan
 
 
 class MixedLoraContext:
@@ -56,8 +57,15 @@ class MixedLoraContext:
         st = self._dev.get(key)
         if st is None:
             seg = self._segment.to(device=device, dtype=torch.int32).contiguous()
-            st = dict(segment=seg, plan=ops.Plan(seg, T),
-                      seg_ids=torch.tensor(list(self._lora_ids), dtype=torch.int32, device=device))
+            seg_ids = torch.tensor(list(self._lora_ids), dtype=torch.int32, device=device)
+            # grouped plan when it helps: decode tokens of one adapter then share its panels wherever they
+            # sit in the batch
+            lens = [int(b) - int(a) for a, b in zip(self._segment[:-1], self._segment[1:])]
+            if wants_grouped_plan(lens, list(self._lora_ids)):
+                plan = ops.Plan(seg, T, seg_ids=seg_ids, n_table=max(self._lora_ids) + 1)
+            else:
+                plan = ops.Plan(seg, T)
+            st = dict(segment=seg, plan=plan, seg_ids=seg_ids)
             tl = int(self._blen.tlen) if self._blen is not None else 0
             if tl > 0:
                 tp = [int(v) for v in self._blen.train_partition]

@@ -42,20 +42,29 @@ class Plan:
     """Work list of one batch: built on the device from the segment index pointer,
     shared by every SMLM call of the batch (all projections, shrink and expand)."""
 
-    __slots__ = ("buf", "indptr", "nseg", "T")
+    __slots__ = ("buf", "indptr", "nseg", "T", "seg_ids", "n_table")
 
-    def __init__(self, indptr: torch.Tensor, T: int):
+    def __init__(self, indptr: torch.Tensor, T: int, seg_ids: Optional[torch.Tensor] = None, n_table: int = 0):
+        """``seg_ids`` (int32 per segment) and ``n_table`` make it a grouped plan: short segments
+        (decode tokens) are grouped by adapter for the forward calls that pass the same ``seg_ids``
+        and an adapter table of ``n_table`` entries.  Weight gradients need a plan without them."""
         _chk_cuda_contig(indptr, "s", 1)
         if indptr.dtype != torch.int32:
             raise RuntimeError("s must be int32")
         self.indptr = indptr
         self.nseg = int(indptr.numel()) - 1
         self.T = int(T)
+        self.seg_ids = seg_ids
+        self.n_table = int(n_table) if seg_ids is not None else 0
+        if seg_ids is not None:
+            _chk_cuda_contig(seg_ids, "seg_ids", 1)
+            if seg_ids.dtype != torch.int32 or seg_ids.numel() < self.nseg:
+                raise RuntimeError("seg_ids must hold one int32 adapter index per segment")
         nbytes = lib.smlm_b200_plan_bytes(self.T, max(self.nseg, 0))
         self.buf = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=indptr.device)
         with torch.cuda.device(indptr.device):
-            check(lib.smlm_b200_plan(self.buf.data_ptr(), nbytes, indptr.data_ptr(), self.nseg, self.T,
-                                     _stream(indptr)), "smlm_b200_plan")
+            check(lib.smlm_b200_plan_grouped(self.buf.data_ptr(), nbytes, indptr.data_ptr(), _p(seg_ids), self.nseg,
+                                             self.n_table, self.T, _stream(indptr)), "smlm_b200_plan")
 
     def status(self):
         """Synchronises.  Returns (n_pieces, status code)."""
@@ -82,7 +91,7 @@ def gemm(y, x, w_table, plan: Plan, is_row_major=False, seg_ids=None, seg_scale=
         check(lib.smlm_b200_gemm(y.data_ptr(), x.data_ptr(), w_table.data_ptr(), _p(seg_ids), _p(seg_scale),
                                  plan.buf.data_ptr(), int(w_table.numel()), int(x.size(0)), plan.nseg,
                                  int(x.size(1)), int(y.size(1)), _dtype_code(x), int(bool(is_row_major)),
-                                 int(bool(accumulate)), _stream(x)), "smlm_b200_gemm")
+                                 int(bool(accumulate)), int(plan.n_table > 0), _stream(x)), "smlm_b200_gemm")
     return y
 
 
@@ -97,7 +106,8 @@ def fwd(y, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, 
                                 wb_table.data_ptr(), _p(seg_ids), _p(seg_scale), plan.buf.data_ptr(),
                                 int(wa_table.numel()), int(x.size(0)), plan.nseg, int(x.size(1)),
                                 int(y.size(1)), int(rank), _dtype_code(x), int(bool(is_row_major)),
-                                int(bool(accumulate)), int(bool(independent)), _stream(x)), "smlm_b200_fwd")
+                                int(bool(accumulate)), int(bool(independent)), int(plan.n_table > 0), _stream(x)),
+              "smlm_b200_fwd")
     return y
 
 
@@ -109,7 +119,7 @@ def bwd_dx(dx, dv, go, wa_table, wb_table, plan: Plan, rank: int, is_row_major=F
                                    wb_table.data_ptr(), _p(part_ids), _p(part_scale), plan.buf.data_ptr(),
                                    int(wa_table.numel()), plan.T, plan.nseg, int(dx.size(1)), int(go.size(1)),
                                    int(rank), _dtype_code(go), int(bool(is_row_major)), int(bool(independent)),
-                                   _stream(go)), "smlm_b200_bwd_dx")
+                                   int(plan.n_table > 0), _stream(go)), "smlm_b200_bwd_dx")
     return dx
 
 

@@ -86,3 +86,20 @@ def merge_segments_device(req_ids: torch.Tensor, req_len: torch.Tensor):
                                            seg_len.data_ptr(), segment.data_ptr(), nseg.data_ptr(),
                                            torch.cuda.current_stream(dev).cuda_stream), "smlm_b200_merge_segments")
     return seg_ids, seg_len, segment, nseg
+
+
+GATHER_MAX_LEN = 8  # rows of a "short" segment at most (the plan builder's rule)
+
+
+def wants_grouped_plan(seg_lens, seg_ids) -> bool:
+    """True when a grouped plan changes anything: some adapter has at least two segments of at most
+    ``GATHER_MAX_LEN`` rows (decode tokens that are not neighbours in the batch).  Known on the host
+    from the same lists the segment index pointer is built from, so no device round trip is needed;
+    batches without such segments keep the ordinary plan and the kernels built for it."""
+    seen = set()
+    for n, a in zip(seg_lens, seg_ids):
+        if 0 < int(n) <= GATHER_MAX_LEN:
+            if a in seen:
+                return True
+            seen.add(a)
+    return False

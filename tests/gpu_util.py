@@ -25,12 +25,18 @@ def to_dev(case):
     return d
 
 
-def run_forward(case, indexed=False, scale=None, accumulate=False, y_init=None):
-    """Returns (y, v) computed on the GPU by the fused forward."""
+def run_forward(case, indexed=False, scale=None, accumulate=False, y_init=None, grouped=None):
+    """Returns (y, v) computed on the GPU by the fused forward.  ``indexed`` passes an adapter table plus
+    per-segment indices (and then, unless ``grouped`` is False, a plan that groups short segments by
+    adapter); otherwise one pointer per segment."""
     from loquetier_b200 import ops
     c = to_dev(case)
     T = c["x"].shape[0]
-    plan = ops.Plan(c["seg_d"], T)
+    if grouped is None:
+        grouped = indexed
+    assert indexed or not grouped
+    plan = (ops.Plan(c["seg_d"], T, seg_ids=c["ids_d"], n_table=len(c["wa_d"])) if grouped
+            else ops.Plan(c["seg_d"], T))
     y = (torch.zeros((T, c["h_out"]), dtype=c["dtype"], device=dev()) if y_init is None
          else y_init.to(dev()).clone())
     v = torch.zeros((T, c["rank"]), dtype=c["dtype"], device=dev())

@@ -30,7 +30,8 @@ def test_library_loads_and_exports_every_declared_symbol():
     bm = cabi.lib.smlm_b200_piece_rows(8192)
     assert 16 <= bm <= 64 and bm % 8 == 0
     assert cabi.lib.smlm_b200_plan_bytes(8192, 100) == (16 + 16 * (8192 // bm + 100 + 1)
-                                                        + 16 + 16 * (8192 // 128 + 100 + 1))
+                                                        + 16 + 16 * (8192 // 128 + 100 + 1)
+                                                        + 4 * (8192 + 4))
     assert cabi.lib.smlm_b200_status_string(3) == b"No suitable kernel."
 
 
@@ -38,14 +39,14 @@ def test_argument_validation_needs_no_gpu():
     from loquetier_b200 import cabi
     L = cabi.lib
     # dtype, shapes and alignment are rejected before any CUDA call
-    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 5, 0, 0, None) == 2
-    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 256, 256, 1, 0, 0, None) == 3
-    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 12, 1, 0, 0, None) == 3
-    assert L.smlm_b200_gemm(16, 24, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, None) == 4
-    assert L.smlm_b200_gemm(None, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, None) == 1
-    assert L.smlm_b200_gemm(None, None, None, None, None, None, 0, 0, 0, 64, 16, 1, 0, 0, None) == 0
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 5, 0, 0, 0, None) == 2
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 256, 256, 1, 0, 0, 0, None) == 3
+    assert L.smlm_b200_gemm(16, 16, 16, None, None, 16, 1, 8, 1, 64, 12, 1, 0, 0, 0, None) == 3
+    assert L.smlm_b200_gemm(16, 24, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, 0, None) == 4
+    assert L.smlm_b200_gemm(None, 16, 16, None, None, 16, 1, 8, 1, 64, 16, 1, 0, 0, 0, None) == 1
+    assert L.smlm_b200_gemm(None, None, None, None, None, None, 0, 0, 0, 64, 16, 1, 0, 0, 0, None) == 0
     assert L.smlm_b200_plan(16, 8, 16, 4, 100, None) == 5
-    assert L.smlm_b200_fwd(16, 16, 16, 16, 16, None, None, 16, 1, 8, 1, 64, 64, 130, 1, 0, 0, 0, None) == 3
+    assert L.smlm_b200_fwd(16, 16, 16, 16, 16, None, None, 16, 1, 8, 1, 64, 64, 130, 1, 0, 0, 0, 0, None) == 3
     with pytest.raises(cabi.SmlmError, match="No suitable kernel"):
         cabi.check(3, "x")
 
@@ -121,3 +122,12 @@ def test_prepare_weight_pads_rank_and_bakes_scale():
     assert q.shape == (4, 8) and q.dtype == torch.bfloat16 and (q[:, 3:] == 0).all()
     same = prepare_weight(w, 3, torch.float16, "cpu")
     assert same.shape == (3, 4) and same.is_contiguous()
+
+
+def test_grouped_plan_is_requested_only_when_it_changes_something():
+    from loquetier_b200.segments import wants_grouped_plan
+    assert not wants_grouped_plan([], [])
+    assert not wants_grouped_plan([100, 1, 1, 9], [0, 1, 2, 1])      # no adapter has two short segments
+    assert wants_grouped_plan([100, 1, 50, 8], [0, 1, 2, 1])        # adapter 1: rows 100 and 151..158
+    assert not wants_grouped_plan([0, 0, 4], [3, 3, 3])             # empty segments do not count
+    assert wants_grouped_plan([1] * 4, [7, 2, 5, 7])
