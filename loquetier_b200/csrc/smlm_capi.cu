@@ -213,13 +213,16 @@ int run_fused(void* out, void* mid, const void* in, const void* const* w1_table,
   // timelines on B200): set-up, a read phase that is bound either by the latency of its ring
   // stages or by what one SM can ingest, the reduce across the cluster, and a write phase
   // bound the same way.
+  // pieces the plan is expected to hold: its capacity, except that a grouped plan turns the short
+  // segments of an adapter into one gather piece, so no more than one piece per adapter comes from them
+  const int est_pieces = grouped ? std::min(mp, T / piece_rows_for(T) + std::min(nseg, n_table)) : mp;
   int ks = 1;
   double best = 1e30;
   const double stage_kb = 64.0 * kc * 2 / 1024.0 * 1.28, slab_kb = 64.0 * fused_slab(r16) * 2 / 1024.0;
   for (int k = 1; k <= 4; ++k) {
     if (k > 1 && ((mode != kFusedExpandOnly && ksteps < k) || (mode != kFusedShrinkOnly && nslabs < k))) break;
     const int slots = kNumSMs * fused_ctas_per_sm(r16);
-    const int ctas = std::max(mp, 1) * k;
+    const int ctas = std::max(est_pieces, 1) * k;
     const int waves = (ctas + slots - 1) / slots;
     const double load = std::max(1.0, std::min<double>(ctas, slots) / kNumSMs);  // CTAs sharing one SM
     const int nk = (ksteps + k - 1) / k, ns = (nslabs + k - 1) / k;
