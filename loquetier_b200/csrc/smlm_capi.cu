@@ -22,7 +22,6 @@ using namespace smlm;
 
 constexpr int kNumSMs = 148;
 
-constexpr int kTargetCtas = 148 * 2;  // aim for at least two resident CTAs on each of the 148 SMs
 
 // ---- tensor maps ------------------------------------------------------------
 // cuTensorMapEncodeTiled is a host-only driver routine; it is looked up through the
@@ -82,21 +81,6 @@ inline int tall_rows_for(int T, int nseg) {
   return 2 * kBM;
 }
 inline int max_tall_pieces_of(int T, int nseg) { return T / tall_rows_for(T, nseg) + nseg; }
-
-inline int pow2_at_least(int v) {
-  int p = 1;
-  while (p < v) p <<= 1;
-  return p;
-}
-
-// How many ways to cut the long dimension so that the grid fills the machine while
-// every CTA still streams at least four pipeline stages.
-inline int pick_split(int work_items, int stages_total) {
-  int ks = pow2_at_least((kTargetCtas + std::max(work_items, 1) - 1) / std::max(work_items, 1));
-  ks = std::min(ks, 8);
-  while (ks > 1 && stages_total / ks < 4) ks >>= 1;
-  return std::max(ks, 1);
-}
 
 template <typename Kern, typename... Args>
 int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cudaStream_t stream,
