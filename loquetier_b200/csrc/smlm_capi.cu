@@ -267,14 +267,16 @@ struct WgradShape {
   size_t ticket_bytes, scratch_bytes;
 };
 
-// The tcgen05 variant serves every rank above 32 unless it is switched off.
+// The tcgen05 variant serves every rank above 32 unless it is switched off, and the lower ranks
+// (padded to 32) when it is forced on.
 inline bool wgrad_uses_tensor_cores(int R) {
-  return R > 32 && g_tensor_core_mode.load(std::memory_order_relaxed) >= 0;
+  const int m = g_tensor_core_mode.load(std::memory_order_relaxed);
+  return R > 32 ? m >= 0 : m > 0;
 }
 
 WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1, bool tc) {
   WgradShape s;
-  const int rt = wgrad_rt(R);
+  const int rt = tc ? std::max(2, wgrad_rt(R)) : wgrad_rt(R);  // the tcgen05 kernel pads ranks below 32
   s.slab = tc ? wg_tc_slab(rt) : 4 * wgrad_cols_per_warp(rt);
   s.slabs_total = (h0 + s.slab - 1) / s.slab + (h1 > 0 ? (h1 + s.slab - 1) / s.slab : 0);
   const int mp = std::max(1, max_pieces_of(T, npart));
@@ -310,8 +312,8 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
               int R, int dtype, int accumulate, int grad_fp32, int independent, cudaStream_t stream) {
   WgradArgs a;
   WgradMaps tm;
-  const int rt = wgrad_rt(R);
   const bool tc = wgrad_uses_tensor_cores(R);
+  const int rt = tc ? std::max(2, wgrad_rt(R)) : wgrad_rt(R);
   const WgradShape sh = wgrad_shape(T, npart, R, job0->H, job1 ? job1->H : 0, tc);
   if (workspace == nullptr || workspace_bytes < sh.ticket_bytes + sh.scratch_bytes) return SMLM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return SMLM_ERR_MISALIGNED;
@@ -340,9 +342,13 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
     tcm.q[0] = tm.q[0];
     tcm.q[1] = tm.q[1];
     const dim3 grid(sh.groups, a.job[0].slabs + a.job[1].slabs, 1);
-    if (dtype == SMLM_F16)
+    if (dtype == SMLM_F16) {
+      if (rt <= 2) return launch(wgrad_tc_kernel<__half, 2>, grid, kWgTcThreads, 1, WgradTcSmem<2>::kTotal, stream, a, tcm);
       return rt <= 4 ? launch(wgrad_tc_kernel<__half, 4>, grid, kWgTcThreads, 1, WgradTcSmem<4>::kTotal, stream, a, tcm)
                      : launch(wgrad_tc_kernel<__half, 8>, grid, kWgTcThreads, 1, WgradTcSmem<8>::kTotal, stream, a, tcm);
+    }
+    if (rt <= 2)
+      return launch(wgrad_tc_kernel<__nv_bfloat16, 2>, grid, kWgTcThreads, 1, WgradTcSmem<2>::kTotal, stream, a, tcm);
     return rt <= 4 ? launch(wgrad_tc_kernel<__nv_bfloat16, 4>, grid, kWgTcThreads, 1, WgradTcSmem<4>::kTotal, stream,
                             a, tcm)
                    : launch(wgrad_tc_kernel<__nv_bfloat16, 8>, grid, kWgTcThreads, 1, WgradTcSmem<8>::kTotal, stream,
@@ -603,7 +609,7 @@ size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h
   // enough for either kernel, so that a buffer sized before a change of the tensor-core mode stays valid
   const WgradShape sh = wgrad_shape(T, npart, rank, h0, h1, false);
   size_t need = sh.ticket_bytes + sh.scratch_bytes;
-  if (rank > 32) {
+  {
     const WgradShape st = wgrad_shape(T, npart, rank, h0, h1, true);
     need = std::max(need, st.ticket_bytes + st.scratch_bytes);
   }

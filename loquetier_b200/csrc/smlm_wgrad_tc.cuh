@@ -29,8 +29,8 @@ constexpr int wg_tc_stages(int rt) { return rt <= 4 ? 3 : 4; }
 
 template <int RT>
 struct WgradTcSmem {
-  static constexpr int KP = RT * 16;                 // 64 or 128
-  static constexpr int NB = KP / 64;                 // 64-rank blocks of P
+  static constexpr int KP = RT * 16;                 // 32, 64 or 128
+  static constexpr int NB = KP > 64 ? KP / 64 : 1;   // 64-rank blocks of P (a narrower P is zero-filled by TMA)
   static constexpr int SLAB = wg_tc_slab(RT);
   static constexpr int NT = SLAB / 128;              // MMA tiles (128 columns each)
   static constexpr int NCH = SLAB / 64;              // 64-column blocks of Q
@@ -45,7 +45,7 @@ struct WgradTcSmem {
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16 + 1024;
   static constexpr int kTmemCols = 2 * NT * KP;      // two accumulator sets
   static constexpr int kPartialFloats = KP * SLAB;   // one CTA's partial sums for one run
-  static_assert(kTmemCols == 512, "tensor memory budget");
+  static_assert(kTmemCols == 512 || kTmemCols == 256, "tensor memory budget: a power of two, 512 columns at most");
   static_assert(kTotal <= 227 * 1024, "shared memory budget");
 };
 
