@@ -172,3 +172,41 @@ def test_linear_forward_replays_inside_a_cuda_graph():
         torch.cuda.synchronize()
         want = lin(x2.to(DEV))
         assert torch.equal(y_static, want)
+
+
+def test_linear_with_unsorted_decode_tokens_uses_a_grouped_plan():
+    """A batch whose decode tokens of one adapter are scattered: the module asks for a grouped plan, and its
+    result equals the reference's operator sequence (per-segment pointers, ordinary plan) and the oracle."""
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    dt = torch.bfloat16
+    h_in, h_out, r, n_ad = 512, 384, 16, 5
+    g = torch.Generator().manual_seed(12)
+    rng = np.random.default_rng(12)
+    lens = [70] + [1] * 40 + [3, 1, 9]
+    ids = [4] + [int(v) for v in rng.integers(0, n_ad, size=40)] + [1, 2, 0]
+    T = sum(lens)
+    x = torch.randn((T, h_in), generator=g).to(dt)
+    wbase = (torch.randn((h_out, h_in), generator=g) * 0.02).to(dt)
+    was = [(torch.randn((r, h_in), generator=g) / 22).to(dt) for _ in range(n_ad)]
+    wbs = [(torch.randn((h_out, r), generator=g) * 0.02).to(dt) for _ in range(n_ad)]
+    scale = [2.0, 0.5, 1.0, 4.0, 1.5]
+    base = nn.Linear(h_in, h_out, bias=False, dtype=dt, device=DEV)
+    with torch.no_grad():
+        base.weight.copy_(wbase)
+    ads = [NamedLoraLayer(f"a{i}", was[i].to(DEV).contiguous(), wbs[i].to(DEV).contiguous(), nn.Identity(),
+                          scale[i]) for i in range(n_ad)]
+    ctx = MixedLoraContext()
+    lin = MixedLoraLinear(ctx, base, ads, r, dt)
+    seg = torch.cumsum(torch.tensor([0] + lens, dtype=torch.int32, device=DEV), 0, dtype=torch.int32)
+    ctx.update(BatchLenInfo([], [], 0, [], torch.device(DEV)), ids, torch.tensor(lens, dtype=torch.int32, device=DEV),
+               seg, [])
+    with torch.no_grad():
+        y = lin(x.to(DEV))
+        y_ops = lin.forward_reference_ops(x.to(DEV))
+    st = ctx.device_state(torch.device(DEV), T)
+    assert st["plan"].n_table == max(ids) + 1          # the grouped plan was requested
+    y_ref = O.lora_linear_forward(x, wbase, was, wbs, scale, ids, lens, r, dt)
+    assert_close(y, y_ref, what="fused, grouped plan")
+    assert_close(y_ops, y_ref, what="reference operator sequence")
+    assert_close(y, y_ops.float(), rtol=1e-2, atol=1e-2, what="fused vs operator sequence")
