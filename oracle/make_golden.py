@@ -322,7 +322,8 @@ def golden_segments(mg, en):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("LOQUETIER_REFERENCE"), required="LOQUETIER_REFERENCE" not in os.environ,
+                    help="path of a checkout of the reference (or set LOQUETIER_REFERENCE)")
     ap.add_argument("--out", default=os.path.join(os.path.dirname(__file__), "..", "tests", "golden"))
     a = ap.parse_args()
     ku, ml, mg, en = _install_stubs(a.reference)
