@@ -581,7 +581,7 @@ def main():
     if a.impl == "reference":
         if rank != 0:
             return
-        base, sec = run_cpu(spec, torch, budget_s=max(10.0, 0.5 * a.steps), max_reps=max(1, a.steps))
+        base, sec = run_cpu(spec, torch, budget_s=min(90.0, max(10.0, 0.5 * a.steps)), max_reps=max(1, a.steps))
         line = dict(metric="SMLM fwd+bwd tokens/s", value=base["value"], unit="tokens/s", n_gpus=a.gpus,
                     steps=a.steps, warmup=a.warmup, ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak",
                     vs_baseline=None, dtype="fp32 on CPU (16-bit inputs upcast)", data="synthetic", config=cfg,
@@ -742,7 +742,7 @@ def run_rmsnorm(a, rank, world, local, torch):
     if a.impl == "reference":
         if rank != 0:
             return
-        base, sec = cpu_leg(max(10.0, 0.5 * a.steps), max(1, a.steps))
+        base, sec = cpu_leg(min(90.0, max(10.0, 0.5 * a.steps)), max(1, a.steps))
         print(json.dumps(dict(metric="RMSNorm fwd+bwd tokens/s", value=base["value"], unit="tokens/s", n_gpus=a.gpus,
                               steps=a.steps, warmup=a.warmup, ms_per_step=sec * 1e3, higher_is_better=True,
                               scaling="weak", vs_baseline=None, dtype="fp32 on CPU (16-bit inputs upcast)",
