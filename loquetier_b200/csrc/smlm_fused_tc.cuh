@@ -10,7 +10,7 @@
 // operands read from shared memory through matrix descriptors and fp32 accumulators in tensor
 // memory (TMEM): acc1 [128 x KP] for the shrink, two [128 x 128] buffers for the expand.
 //
-// Warp roles (8 warps):
+// Warp roles (12 warps):
 //   warp 0   TMA producer of IN: tiled tensor copies of [16 rows x 64 columns] boxes with the
 //            128-byte swizzle, which is exactly the K-major SWIZZLE_128B operand layout;
 //            in phase 3 it loads the W2 slabs together with warps 6 and 7.
@@ -18,6 +18,9 @@
 //   warps 2-5 load the W1 panel slices (16-byte cp.async into the swizzled operand layout,
 //            completion counted on the stage's mbarrier) and run both epilogues: TMEM ->
 //            registers (tcgen05.ld) -> storage type -> shared -> global (TMA tensor stores).
+//   warps 8-11 share the second epilogue with them: of every 128-column group, warps 2-5 drain the
+//            first 64 columns and warps 8-11 the second (measured: the drain, not the stores, bounds
+//            the write phase - 0.8 us per group with four warps).
 //
 // Every wait is a bounded mbarrier wait; on a timeout the kernel records kErrTimeout, stops
 // issuing work, still frees its TMEM and returns.
@@ -28,11 +31,13 @@
 
 namespace smlm {
 
-constexpr int kTcThreads = 256;
+constexpr int kTcW2Warps = 3;   // warps that load W2 slabs: warp 0, 6, 7 and the last ones
+constexpr int kTcThreads = 384 + (kTcW2Warps - 3) * 32;
 constexpr int kTcRows = 128;   // rows of a tall piece = M of the MMA
 constexpr int kTcNG = 128;     // OUT columns per MMA group of phase 3
 constexpr int kTcW2Bufs = 4;   // W2 slabs in flight
-constexpr int kTcOutBufs = 4;  // staging blocks per epilogue warp: tensor stores in flight
+// staging blocks per epilogue warp = tensor stores it keeps in flight
+constexpr int tc_out_bufs(int r16) { return r16 >= 8 ? 2 : 4; }
 
 constexpr int tc_chunks(int r16) { return r16 >= 8 ? 2 : 4; }  // 64-column chunks of IN per stage
 
@@ -48,10 +53,11 @@ struct TcSmem {
   static constexpr int kStages = 2;
   static constexpr int kRing = kStages * kStage;
   // phase 3 lives in the space of the ring: kTcW2Bufs W2 slabs [kTcNG x KP], then per epilogue warp
-  // kTcOutBufs staging blocks of [32 rows][128 B]
+  // OB staging blocks of [32 rows][128 B]
   static constexpr int kW2Slab = kTcNG * KP * 2;
   static constexpr int kOutOff = kTcW2Bufs * kW2Slab;
-  static constexpr int kStageOut = 4 * kTcOutBufs * 4096;
+  static constexpr int OB = tc_out_bufs(R16);
+  static constexpr int kStageOut = 8 * OB * 4096;
   static constexpr int kPhase3 = kOutOff + kStageOut;
   static constexpr int kUnion = kRing > kPhase3 ? kRing : kPhase3;
   static constexpr int kMidOff = kUnion;                      // MID operand: NB blocks of [128 rows][128 B]
@@ -195,12 +201,12 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
     mbar_init(acc1_full, 1);
     mbar_init(mid_full, 128);
     for (int b = 0; b < kTcW2Bufs; ++b) {
-      mbar_init(w2_full0 + b * 8, 96);
+      mbar_init(w2_full0 + b * 8, kTcW2Warps * 32);
       mbar_init(w2_empty0 + b * 8, 1);
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc2_full0 + b * 8, 1);
-      mbar_init(acc2_empty0 + b * 8, 128);
+      mbar_init(acc2_empty0 + b * 8, 256);
     }
     fence_mbar_init();
   }
@@ -238,9 +244,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
       }
     }
   }
-  if (warp == 0 || warp >= 6) {
+  if (warp == 0 || warp == 6 || warp == 7 || warp >= 12) {
     // ============ phase 3: three warps load the W2 slabs ============
-    const int lt = (warp == 0 ? 0 : warp - 5) * 32 + lane;   // 0..95
+    const int lt = (warp == 0 ? 0 : (warp >= 12 ? warp - 9 : warp - 5)) * 32 + lane;   // 0 .. 32 * kTcW2Warps - 1
     mbar_wait(acc1_full, 0, err, dead);  // the ring is no longer read once the shrink has completed
     for (int g = 0; g < ngroups; ++g) {
       const int buf = g % kTcW2Bufs;
@@ -251,7 +257,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
       const uint32_t ws = base + buf * SM::kW2Slab;
       if constexpr (!RM) {
         // W2 stored [N2][R] (K-major): per 64-wide rank block, [128 n-rows][128 B] swizzled
-        for (int i = lt; i < kTcNG * NB * 8; i += 96) {
+        for (int i = lt; i < kTcNG * NB * 8; i += kTcW2Warps * 32) {
           const int c = i & 7, n = (i >> 3) % kTcNG, blk = i / (8 * kTcNG);
           const int kcol = blk * 64 + c * 8;
           const bool ok = (n < ncols) && (kcol < R);
@@ -260,7 +266,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
         }
       } else {
         // W2 stored [R][N2] (MN-major): per 64-column block, [KP k-rows][128 B] swizzled
-        for (int i = lt; i < KP * (kTcNG / 64) * 8; i += 96) {
+        for (int i = lt; i < KP * (kTcNG / 64) * 8; i += kTcW2Warps * 32) {
           const int c = i & 7, k = (i >> 3) % KP, blk = i / (8 * KP);
           const int col = blk * 64 + c * 8;
           const bool ok = (k < R) && (col < ncols);
@@ -324,12 +330,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
     }
     __syncwarp();
   } else {
-    // ============ W1 loaders, then the epilogues (warps 2..5, 128 threads) ============
-    const int lt = tid - 64;                    // 0..127
+    // ============ W1 loaders, then the epilogues (warps 2..5; warps 8..11 join for the second) ============
+    const bool second = warp >= 8;              // drains columns 64..127 of every group, nothing else
+    const int lt = tid - 64;                    // 0..127 for the W1 loaders
     const int sub = warp & 3;                   // TMEM subpartition this warp may read
     const int row = sub * 32 + lane;            // row of the piece held by this thread
     const uint32_t lane_base = static_cast<uint32_t>(sub * 32) << 16;
-    for (int it = 0; it < ksteps; ++it) {
+    for (int it = 0; !second && it < ksteps; ++it) {
       const int slot = it % S;
       const int k0 = it * KC;
       const uint32_t ws = base + slot * SM::kStage + SM::kXBytes;
@@ -358,9 +365,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
     }
 
     // ---- epilogue 1: acc1 -> MID (global, storage type) and the MID operand tile ----
-    mbar_wait(acc1_full, 0, err, dead);
-    tc_fence_after();
-    {
+    if (!second) {
+      mbar_wait(acc1_full, 0, err, dead);
+      tc_fence_after();
       const uint32_t mids = base + SM::kMidOff;
       T* mrow = static_cast<T*>(a.mid) + static_cast<size_t>(pc.row0 + row) * R;
 #pragma unroll
@@ -391,13 +398,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
           }
         }
       }
+      tc_fence_before();
+      fence_proxy_async();  // the MMA reads the MID tile through the async proxy
+      mbar_arrive(mid_full);
     }
-    tc_fence_before();
-    fence_proxy_async();  // the MMA reads the MID tile through the async proxy
-    mbar_arrive(mid_full);
 
-    // ---- epilogue 2: acc2[buf] -> OUT ----
-    const uint32_t ostage = base + SM::kOutOff + (warp - 2) * (kTcOutBufs * 4096);
+    // ---- epilogue 2: acc2[buf] -> OUT; this warp's 64 columns of every 128-column group ----
+    constexpr int OB = SM::OB;
+    const int half = second ? 1 : 0;
+    const uint32_t ostage = base + SM::kOutOff + ((second ? warp - 4 : warp - 2)) * (OB * 4096);
     T* orow = static_cast<T*>(a.out) + static_cast<size_t>(pc.row0 + row) * N2;
     const int rows_here = min(32, nrows - sub * 32);   // rows of this warp that exist (may be <= 0)
     int obuf = 0;
@@ -408,33 +417,32 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
       mbar_wait(acc2_full0 + buf * 8, (g >> 1) & 1, err, dead);
       dead = __any_sync(0xffffffffu, dead);  // the warp leaves the store path together
       tc_fence_after();
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {   // 64 columns at a time: one [32 rows][128 B] staging block
-        if (lane == 0) bulk_wait_read<kTcOutBufs - 1>();
+      {   // one [32 rows][128 B] staging block
+        if (lane == 0) bulk_wait_read<OB - 1>();
         __syncwarp();
         const uint32_t os = ostage + obuf * 4096;
+        // both 32-column loads of the half are in flight before the one wait
+        uint32_t v0[32], v1[32];
+        tc_ld32(acc2 + buf * kTcNG + lane_base + half * 64, v0);
+        tc_ld32(acc2 + buf * kTcNG + lane_base + half * 64 + 32, v1);
+        tc_wait_ld();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          uint32_t v[32];
-          tc_ld32(acc2 + buf * kTcNG + lane_base + half * 64 + h * 32, v);
-          tc_wait_ld();
+        for (int q = 0; q < 8; ++q) {
+          uint32_t p[4];
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t p[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e)
-              p[e] = pack2<T>(__uint_as_float(v[q * 8 + e * 2]) * sc_out, __uint_as_float(v[q * 8 + e * 2 + 1]) * sc_out);
-            const int c = h * 4 + q;
-            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(os + lane * 128 + ((c ^ (lane & 7)) << 4)),
-                         "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3])
-                         : "memory");
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t lo = q < 4 ? v0[q * 8 + e * 2] : v1[(q - 4) * 8 + e * 2];
+            const uint32_t hi = q < 4 ? v0[q * 8 + e * 2 + 1] : v1[(q - 4) * 8 + e * 2 + 1];
+            p[e] = pack2<T>(__uint_as_float(lo) * sc_out, __uint_as_float(hi) * sc_out);
           }
+          asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(os + lane * 128 + ((q ^ (lane & 7)) << 4)),
+                       "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3])
+                       : "memory");
         }
-        if (half == 1) {
-          // both halves are in registers/shared memory: the TMEM buffer may be overwritten
-          tc_fence_before();
-          mbar_arrive(acc2_empty0 + buf * 8);
-        }
+        // this warp's share is in registers / shared memory: the TMEM buffer may be overwritten once
+        // all eight warps have said so
+        tc_fence_before();
+        mbar_arrive(acc2_empty0 + buf * 8);
         const int col0 = n0 + half * 64;
         if (col0 < n0 + ncols && rows_here > 0 && !dead) {
           fence_proxy_async();
@@ -473,7 +481,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
             }
           }
           __syncwarp();
-          obuf = (obuf + 1) % kTcOutBufs;
+          obuf = (obuf + 1) % OB;
         }
       }
     }
