@@ -41,11 +41,6 @@ if ROOT not in sys.path:
 
 SCALE = 2.0  # alpha / r of the reference's fine-tune configuration (16 / 8)
 
-# DRAM bytes (read + written during the launch) per algorithmic byte of the forward fused launch, from
-# the ncu capture summarised in profiles/fused_kernel_c3_q_proj.md: (70.82 + 9.56) MB / 138.7 MB.  Part of
-# the freshly written output is still dirty in L2 when the launch ends, hence a ratio below one.
-TRAFFIC_PER_ALGORITHMIC_BYTE = 0.58
-
 
 # ---------------------------------------------------------------------------
 # workloads
@@ -104,7 +99,8 @@ def workload_spec(name, rank=0, world=1):
         n_ad, r, dt = 64, 64, "bf16"
         proj = [("up_4096_14336", 4096, 14336), ("down_14336_4096", 14336, 4096)]
     if name == "c5":
-        ids = [int(v) for v in rng.choice(n_ad, size=16, replace=False)]
+        # the train partitions of a rank are ordered by adapter, so that a range of adapters is a range of rows
+        ids = sorted(int(v) for v in rng.choice(n_ad, size=16, replace=False))
     else:
         # a rank only receives segments of the adapters it owns: a mod world == rank
         owned = np.arange(rank, n_ad, world)
@@ -185,6 +181,7 @@ class Workload:
             self.proj.append(p)
         self.plan = None
         self.pplan = None
+        self.iplan = None
         self.ops = ops
         self.accumulate_grads = False
         self.grouped = True
@@ -193,23 +190,97 @@ class Workload:
         self.n_streams = 3
         self.side = []
         self.torch = torch
+        # "multi": one launch per kernel class over all projections; "split": the same with the forward of
+        # the inference rows on a second stream; "single": one launch per projection and class
+        self.sched = "multi"
+        self.pset = ops.ProjSet([dict(x=p["x"], y=p["y"], v=p["v"], go=p.get("go"), dx=p.get("dx"), dv=p.get("dv"),
+                                      wa=p["wa"], wb=p["wb"], dA_t=p.get("dA_t"), dB_t=p.get("dB_t"),
+                                      h_in=p["h_in"], h_out=p["h_out"]) for p in self.proj]) \
+            if len(self.proj) <= 8 else None
+        if self.npart and self.npart < len(spec["lens"]):
+            self.iseg = self.seg[self.npart:].contiguous()
+            self.iids = self.ids[self.npart:].contiguous()
+        else:
+            self.iseg = self.iids = None
+
+    def rebuild_projset(self):
+        """After the gradient tables were re-pointed (the data-parallel bucket)."""
+        self.pset = self.ops.ProjSet([dict(x=p["x"], y=p["y"], v=p["v"], go=p.get("go"), dx=p.get("dx"),
+                                           dv=p.get("dv"), wa=p["wa"], wb=p["wb"], dA_t=p.get("dA_t"),
+                                           dB_t=p.get("dB_t"), h_in=p["h_in"], h_out=p["h_out"])
+                                      for p in self.proj])
 
     def build_plans(self):
         # grouped where it changes anything: decode tokens are gathered by adapter for the forward launches
         from loquetier_b200.segments import wants_grouped_plan
-        g = self.grouped and wants_grouped_plan(self.spec["lens"], self.spec["ids"])
-        self.plan = self.ops.Plan(self.seg, self.T, seg_ids=self.ids if g else None, n_table=self.spec["n_adapters"])
+        lens, ids = self.spec["lens"], self.spec["ids"]
+        if self.sched == "split" and self.iseg is not None:
+            # the train rows go through the partition plan, the other rows get a plan of their own
+            g = self.grouped and wants_grouped_plan(lens[self.npart:], ids[self.npart:])
+            self.iplan = self.ops.Plan(self.iseg, self.T, seg_ids=self.iids if g else None,
+                                       n_table=self.spec["n_adapters"])
+            self.plan = None
+        else:
+            g = self.grouped and wants_grouped_plan(lens, ids)
+            self.plan = self.ops.Plan(self.seg, self.T, seg_ids=self.ids if g else None,
+                                      n_table=self.spec["n_adapters"])
+            self.iplan = None
         if self.tl:
             self.pplan = self.ops.Plan(self.part, self.tl)
 
-    # one plan per index pointer, then 1 forward and 2 backward kernels per projection
-    launches_per_step = property(lambda self: 1 + (1 if self.tl else 0)
-                                 + len(self.proj) * (1 + (2 if self.tl else 0)))
+    def plans(self):
+        return [p for p in (self.plan, self.pplan, self.iplan) if p is not None]
+
+    @property
+    def launches_per_step(self):
+        """Kernels of this library launched per step: the plans, then per class one launch (multi / split)
+        or one per projection (single)."""
+        nplan = 1 + (1 if self.tl else 0)
+        if self.sched == "single" or self.pset is None:
+            return nplan + len(self.proj) * (1 + (2 if self.tl else 0))
+        if self.sched == "split" and self.iseg is not None and self.tl:
+            return nplan + 1 + 4
+        return nplan + 1 + (2 if self.tl else 0)
 
     def step(self):
-        """The hot path: plans once, then for every projection the fused forward, the fused
-        dV/dX backward and the weight gradients.  The projections are independent of each other,
-        so the launches of one kind are issued back to back and marked independent: the read
+        if self.sched == "single" or self.pset is None:
+            return self.step_single()
+        ops, r, torch = self.ops, self.spec["rank"], self.torch
+        self.build_plans()
+        n_ad = self.spec["n_adapters"]
+        if self.sched == "split" and self.iseg is not None and self.tl:
+            # The weight gradients need v and dV of the train rows only: the train rows' forward and dV/dX
+            # run first and the weight gradients right behind them, while the forward of the inference
+            # rows - most of the step - runs next to all three on a second stream.
+            main = torch.cuda.current_stream()
+            if not self.side:
+                self.side = [torch.cuda.Stream()]
+            fork = torch.cuda.Event()
+            fork.record(main)
+            self.side[0].wait_event(fork)
+            with torch.cuda.stream(self.side[0]):
+                ops.fwd_multi(self.pset, self.iplan, r, seg_ids=self.iids, seg_scale=self.scale)
+            ops.bwd_dx_multi(self.pset, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale)
+            ops.fwd_multi(self.pset, self.pplan, r, seg_ids=self.part_ids, seg_scale=self.scale,
+                          independent=self.overlap)
+            ops.wgrad_pair_multi(self.pset, self.part, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale,
+                                 n_table=n_ad, accumulate=self.accumulate_grads)
+            main.wait_stream(self.side[0])
+            return
+        # dV/dX of all projections, the forward of all projections (independent of it: it starts while
+        # dV/dX drains), then the weight gradients, which consume v and dV
+        if self.tl:
+            ops.bwd_dx_multi(self.pset, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale)
+        ops.fwd_multi(self.pset, self.plan, r, seg_ids=self.ids, seg_scale=self.scale,
+                      independent=self.overlap and self.tl > 0)
+        if self.tl:
+            ops.wgrad_pair_multi(self.pset, self.part, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale,
+                                 n_table=n_ad, accumulate=self.accumulate_grads)
+
+    def step_single(self):
+        """One launch per projection and kernel class: plans once, then for every projection the fused
+        forward, the fused dV/dX backward and the weight gradients.  The projections are independent of
+        each other, so the launches of one kind are issued back to back and marked independent: the read
         phase of one overlaps the write phase of the one before.  The weight gradients come last
         because they consume v and dV."""
         ops = self.ops
@@ -321,101 +392,215 @@ class ClockSampler:
                                samples=len(sm))
 
 
-def timed(fn, steps, warmup, torch, dist=None, clk=None):
-    """W untimed + K timed iterations bracketed by barrier + synchronize; device
-    time from CUDA events on the current stream; max over ranks."""
+def timed(fn, steps, warmup, torch, dist=None, clk=None, blocks=1):
+    """W untimed iterations, then `blocks` timed blocks of EXACTLY `steps` iterations, each bracketed
+    by barrier + synchronize on both sides; device time from CUDA events on the current stream; max
+    over ranks per block.  Returns (median ms per step over the blocks, [ms per step of every block])."""
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
-    if dist is not None:
-        dist.barrier()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    per_block = []
     if clk is not None:
         clk.mark_start()
-    e0.record()
-    for _ in range(steps):
-        fn()
-    e1.record()
-    torch.cuda.synchronize()
+    for _ in range(max(1, blocks)):
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if dist is not None:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        per_block.append(ms / steps)
     if clk is not None:
         clk.mark_end()
-    if dist is not None:
-        dist.barrier()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    return ms / steps
+    return float(np.median(per_block)), per_block
 
 
-def kernel_breakdown(wl, torch, reps=5):
-    """Device time of every kernel class over one step, measured by launching the
-    class back to back for all projections between two events (so that launch gaps
-    do not count), through the same C-ABI entry points the fused calls use.
-    Returns {class: (ms per step, algorithmic bytes per step, launches per step)}."""
-    ops, r, e = wl.ops, wl.spec["rank"], 2
+def class_bytes(wl):
+    """Algorithmic bytes of one step per kernel class (2-byte elements; every distinct adapter panel
+    once per class; the rank-r intermediate a class writes or reads is counted with it)."""
+    r, e = wl.spec["rank"], 2
     used = len(set(wl.spec["ids"]))
     used_ft = len(set(wl.spec["ids"][:wl.npart]))
     T, n = wl.T, wl.tl
+    fwd = sum(e * (T * p["h_in"] + T * p["h_out"] + T * r + used * r * (p["h_in"] + p["h_out"])) for p in wl.proj)
+    bdx = sum(e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"])) for p in wl.proj)
+    wg = sum(e * (n * (p["h_in"] + p["h_out"]) + 2 * n * r + used_ft * r * (p["h_in"] + p["h_out"])) for p in wl.proj)
+    return fwd, bdx, wg
+
+
+def kernel_breakdown(wl, torch, reps=5):
+    """Device time of every kernel class over one step, each class timed alone between two CUDA
+    events on the launching stream with L2 flushed before: with the multi schedules a class is ONE
+    launch over all projections, with the single schedule it is the class launched back to back for
+    every projection (so that launch gaps do not count).  Same C-ABI entry points as the step.
+    Returns {class: (ms per step, algorithmic bytes per step, launches per step)}."""
+    ops, r = wl.ops, wl.spec["rank"]
+    n, n_ad = wl.tl, wl.spec["n_adapters"]
+    sched = wl.sched
+    multi = sched != "single" and wl.pset is not None
+    wl.sched = "multi" if multi else "single"   # the classes run over the whole batch with the full plan
     wl.build_plans()
     for p in wl.proj:  # make v / dv valid for the classes that read them
         ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale)
         if n:
             ops.bwd(p["dx"], p["dA_t"], p["dB_t"], p["dv"], p["go"], p["x"], p["v"], p["wa"], p["wb"], wl.pplan,
-                    r, part_ids=wl.part_ids, part_scale=wl.scale)
-    classes = {
-        "fused_kernel(fwd x->v->y)": (
-            lambda p, i: ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids,
-                                 seg_scale=wl.scale, independent=wl.overlap and i > 0),
-            lambda p: e * (T * p["h_in"] + T * p["h_out"] + T * r + used * r * (p["h_in"] + p["h_out"]))),
-    }
+                    r, part_ids=wl.part_ids, part_scale=wl.scale, accumulate_grads=wl.accumulate_grads)
+    fwd_b, bdx_b, wg_b = class_bytes(wl)
+    nproj = len(wl.proj)
+    tc = r > 32
+    names = (("fused_tc_kernel" if tc else "fused_kernel"), ("wgrad_tc_kernel" if tc else "wgrad_kernel"))
+
+    def fwd_all():
+        if multi:
+            ops.fwd_multi(wl.pset, wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale)
+        else:
+            for i, p in enumerate(wl.proj):
+                ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale,
+                        independent=wl.overlap and i > 0)
+
+    def bdx_all():
+        if multi:
+            ops.bwd_dx_multi(wl.pset, wl.pplan, r, part_ids=wl.part_ids, part_scale=wl.scale)
+        else:
+            for i, p in enumerate(wl.proj):
+                ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], wl.pplan, r, part_ids=wl.part_ids,
+                           part_scale=wl.scale, independent=wl.overlap and i > 0)
+
+    def wg_all():
+        if multi:
+            ops.wgrad_pair_multi(wl.pset, wl.part, wl.pplan, r, part_ids=wl.part_ids, part_scale=wl.scale,
+                                 n_table=n_ad, accumulate=wl.accumulate_grads)
+        else:
+            for i, p in enumerate(wl.proj):
+                ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan, r,
+                               part_ids=wl.part_ids, part_scale=wl.scale, n_table=n_ad,
+                               accumulate=wl.accumulate_grads,
+                               workspace=ops.wgrad_workspace(wl.dev, n, wl.npart, r, p["h_out"], p["h_in"], slot=i),
+                               independent=wl.overlap and i > 0)
+
+    nl = 1 if multi and not tc else nproj
+    classes = {f"{names[0]}(fwd x->v->y)": (fwd_all, fwd_b)}
     if n:
-        classes.update({
-            "fused_kernel(bwd gO->dV->dX)": (
-                lambda p, i: ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], wl.pplan, r,
-                                        part_ids=wl.part_ids, part_scale=wl.scale,
-                                        independent=wl.overlap and i > 0),
-                lambda p: e * (n * p["h_out"] + n * p["h_in"] + n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
-            "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": (
-                lambda p, i: ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan,
-                                            r, part_ids=wl.part_ids, part_scale=wl.scale,
-                                            n_table=wl.spec["n_adapters"],
-                                            workspace=ops.wgrad_workspace(wl.dev, n, wl.npart, r, p["h_out"],
-                                                                          p["h_in"], slot=i),
-                                            independent=wl.overlap and i > 0),
-                lambda p: e * (n * (p["h_in"] + p["h_out"]) + 2 * n * r + used_ft * r * (p["h_in"] + p["h_out"]))),
-        })
+        classes[f"{names[0]}(bwd gO->dV->dX)"] = (bdx_all, bdx_b)
+        classes[f"{names[1]}(dB=gO^T.V, dA=dV^T.X)"] = (wg_all, wg_b)
     out = {}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=wl.dev)
     for name, (fn, nbytes) in classes.items():
-        tot = 0.0
+        ts = []
         for it in range(reps + 1):
             flush.zero_()  # evict L2 between repetitions of the same class
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            for i, p in enumerate(wl.proj):
-                fn(p, i)
+            fn()
             e1.record()
             torch.cuda.synchronize()
             if it > 0:
-                tot += e0.elapsed_time(e1)
-        out[name] = (tot / reps, float(sum(nbytes(p) for p in wl.proj)), len(wl.proj))
+                ts.append(e0.elapsed_time(e1))
+        out[name] = (float(np.median(ts)), float(nbytes), nl if not name.startswith("wgrad") else (1 if multi else nproj))
+    wl.sched = sched
     return out
+
+
+# ---------------------------------------------------------------------------
+# parity of the timed step
+# ---------------------------------------------------------------------------
+
+def check_step(wl, torch, rtol=1e-2, atol=1e-2):
+    """Compares what the step left in device memory - y and v of every projection over all rows, dX, dA
+    and dB of every projection and train partition - with the CPU oracle evaluated on the same 16-bit
+    inputs, at the rounding points of the reference (v and dV rounded to the storage type).  Bound per
+    element: |got - want| <= atol + rtol * |want|.  Returns {name: max|err| / max|want|} of every tensor
+    class; raises AssertionError naming the first tensor outside the bound."""
+    from oracle import smlm_oracle as O
+    spec = wl.spec
+    T, npart, tl, r = wl.T, wl.npart, wl.tl, spec["rank"]
+    seg = [int(v) for v in wl.seg_h]
+    ids = spec["ids"]
+    worst = {}
+
+    def cmp(name, got, want):
+        g, w = got.detach().to("cpu", torch.float32), want.detach().to("cpu", torch.float32)
+        assert g.shape == w.shape, f"{name}: shape {tuple(g.shape)} vs {tuple(w.shape)}"
+        assert bool(torch.isfinite(g).all()), f"{name}: non-finite values"
+        err = (g - w).abs()
+        bad = err > atol + rtol * w.abs()
+        rel = float(err.max()) / max(float(w.abs().max()), 1e-30)
+        key = name.split("[")[0].split(".")[-1]
+        worst[key] = max(worst.get(key, 0.0), rel)
+        if bool(bad.any()):
+            i = torch.nonzero(bad)[0].tolist()
+            raise AssertionError(f"{name}: {int(bad.sum())}/{g.numel()} elements outside rtol={rtol} atol={atol}; "
+                                 f"max abs err {float(err.max()):.4g}; first at {i}: got {float(g[tuple(i)])} "
+                                 f"want {float(w[tuple(i)])}")
+
+    for p in wl.proj:
+        x, A, B = p["x"].cpu(), p["A"].cpu(), p["B"].cpu()
+        y_ref, v_ref = O.add_lora_forward((T, p["h_out"]), x, [A[i] for i in ids], [B[i] for i in ids], seg, r,
+                                          round_v=True)
+        cmp(f"{p['name']}.y", p["y"], y_ref.to(torch.float32) * SCALE)
+        cmp(f"{p['name']}.v", p["v"], v_ref)
+        if tl:
+            # the scale is a power of two here, so scaling gO in the storage type is exact and the oracle's
+            # rounding points (dV = round(scale * gO . B)) are the kernels'
+            go = (p["go"].cpu().to(torch.float32) * SCALE).to(wl.dt)
+            gx, grads = O.add_lora_backward(go, x[:tl], [A[i] for i in ids[:npart]], [B[i] for i in ids[:npart]],
+                                            seg[:npart + 1], round_mid=True)
+            cmp(f"{p['name']}.dX", p["dx"], gx)
+            for k in range(npart):
+                cmp(f"{p['name']}.dA[{k}]", p["dA"][k], grads[2 * k])
+                cmp(f"{p['name']}.dB[{k}]", p["dB"][k], grads[2 * k + 1])
+    return worst
 
 
 # ---------------------------------------------------------------------------
 # end to end through host buffers
 # ---------------------------------------------------------------------------
 
-class HostPipeline:
-    """The step with HOST inputs and outputs: x and gO of every projection start in
-    pinned host memory, y, dX, dA and dB end in pinned host memory.  Copies run on
-    their own streams so that the upload of projection p+1 and the download of
-    projection p-1 overlap the kernels of projection p."""
+def bind_to_gpu_numa_node(local):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, so that the pinned buffers
+    allocated afterwards are local to the PCIe root of the GPU.  Reads sysfs and nvidia-smi only;
+    changes nothing but this process's own affinity.  Returns the node or None."""
+    try:
+        bdf = subprocess.run(["nvidia-smi", f"--id={local}", "--query-gpu=pci.bus_id", "--format=csv,noheader"],
+                             capture_output=True, text=True, timeout=20).stdout.strip().lower()
+        if bdf.count(":") == 2 and len(bdf.split(":")[0]) == 8:
+            bdf = bdf[4:]  # sysfs uses a 4-digit PCI domain
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read().strip())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            a, _, b = part.partition("-")
+            cpus.update(range(int(a), int(b or a) + 1))
+        allowed = os.sched_getaffinity(0)
+        if cpus & allowed:
+            os.sched_setaffinity(0, cpus & allowed)
+            return node
+    except Exception:
+        pass
+    return None
 
-    def __init__(self, wl, torch):
+
+class HostPipeline:
+    """The step with HOST inputs and outputs: x and gO of every projection start in pinned host memory;
+    y, dX, dA and dB end in pinned host memory.  The batch is cut into row blocks - the train rows, then
+    the other rows in equal parts - and every (projection, row block) is one unit: its rows are uploaded
+    on one stream, run through the single-projection entry points (fused forward; for the train rows also
+    the backward) on the compute stream, and downloaded on a third stream, so that only the first unit's
+    upload and the last unit's download are not overlapped.  Segments are independent, so a row block is
+    served by a plan on the segment index pointer clipped to its rows."""
+
+    def __init__(self, wl, torch, nblocks=4):
         self.wl, self.torch = wl, torch
         pin = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t)
         pin_out = lambda t: torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
@@ -431,6 +616,28 @@ class HostPipeline:
                 self.d2h_bytes += (p["dx"].numel() + p["dA"].numel() + p["dB"].numel()) * 2
             self.h.append(h)
         self.s_in, self.s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        # row blocks: [0, tl) holds the train rows; the rest in (nblocks - 1) parts cut at multiples of 64 rows
+        T, tl = wl.T, wl.tl
+        cuts = [0]
+        if tl:
+            cuts.append(tl)
+        rest = max(1, nblocks - (1 if tl else 0))
+        for k in range(1, rest + 1):
+            c = tl + ((T - tl) * k // rest) // 64 * 64 if k < rest else T
+            if c > cuts[-1]:
+                cuts.append(c)
+        self.blocks = []
+        seg = torch.tensor(wl.seg_h, dtype=torch.int64)
+        for lo, hi in zip(cuts[:-1], cuts[1:]):
+            clipped = seg.clamp(lo, hi).to(torch.int32).to(wl.dev)
+            self.blocks.append((lo, hi, clipped))
+        # units in upload order: an inference block first (the smallest first upload), the train rows second,
+        # the small-output projections last (the smallest last download)
+        order_p = sorted(range(len(wl.proj)), key=lambda i: -wl.proj[i]["h_out"])
+        order_b = list(range(len(self.blocks)))
+        if tl and len(order_b) > 1:
+            order_b = [1, 0] + order_b[2:]
+        self.units = [(i, b) for b in order_b for i in order_p]
 
     def step(self):
         torch, wl, ops = self.torch, self.wl, self.wl.ops
@@ -438,28 +645,36 @@ class HostPipeline:
         r = wl.spec["rank"]
         self.s_in.wait_stream(cur)
         self.s_out.wait_stream(cur)
-        wl.build_plans()
+        plans = [ops.Plan(ind, wl.T) for (_, _, ind) in self.blocks]
+        pplan = ops.Plan(wl.part, wl.tl) if wl.tl else None
+        wl.plan, wl.pplan, wl.iplan = plans[-1], pplan, None   # what the caller checks for recorded faults
+        self.plans = plans + ([pplan] if pplan is not None else [])
         ready = []
         with torch.cuda.stream(self.s_in):
-            for p, h in zip(wl.proj, self.h):
-                p["x"].copy_(h["x"], non_blocking=True)
-                if wl.tl:
+            for i, b in self.units:
+                p, h = wl.proj[i], self.h[i]
+                lo, hi, _ = self.blocks[b]
+                p["x"][lo:hi].copy_(h["x"][lo:hi], non_blocking=True)
+                if wl.tl and lo == 0:
                     p["go"].copy_(h["go"], non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record(self.s_in)
                 ready.append(ev)
-        for p, h, ev in zip(wl.proj, self.h, ready):
+        for (i, b), ev in zip(self.units, ready):
+            p, h = wl.proj[i], self.h[i]
+            lo, hi, _ = self.blocks[b]
             cur.wait_event(ev)
-            ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale)
-            if wl.tl:
+            ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], plans[b], r, seg_ids=wl.ids, seg_scale=wl.scale)
+            train = wl.tl and lo == 0
+            if train:
                 ops.bwd(p["dx"], p["dA_t"], p["dB_t"], p["dv"], p["go"], p["x"], p["v"], p["wa"], p["wb"],
-                        wl.pplan, r, part_ids=wl.part_ids, part_scale=wl.scale)
+                        pplan, r, part_ids=wl.part_ids, part_scale=wl.scale, accumulate_grads=wl.accumulate_grads)
             done = torch.cuda.Event()
             done.record(cur)
             with torch.cuda.stream(self.s_out):
                 self.s_out.wait_event(done)
-                h["y"].copy_(p["y"], non_blocking=True)
-                if wl.tl:
+                h["y"][lo:hi].copy_(p["y"][lo:hi], non_blocking=True)
+                if train:
                     h["dx"].copy_(p["dx"], non_blocking=True)
                     h["dA"].copy_(p["dA"], non_blocking=True)
                     h["dB"].copy_(p["dB"], non_blocking=True)
@@ -525,18 +740,230 @@ def run_cpu(spec, torch, budget_s=12.0, max_reps=5):
 # main
 # ---------------------------------------------------------------------------
 
+WORKLOAD_TEXT = {
+    "c2": "Llama-2-7B q_proj mixed batch, fp16, rank 16, 32 adapters, 2x1024 FT + 4x512 prefill + 64 decode",
+    "c3": "Llama-3-8B 7 LoRA projections of one layer, bf16, rank 16, 128 adapters, 8192 tokens, "
+          "Zipf(1.2) segment lengths in [1,2048], 25% fine-tune tokens (fwd+bwd), rest forward only",
+    "c4": "decode sweep, bf16, 1024 one-token segments, 256 adapters, rank 32, 4096->11008 and 11008->4096",
+    "c4s": "decode sweep as c4 with the tokens sorted by adapter and merged into segments, as the "
+           "reference's batch assembler orders decode requests",
+    "c5": "fine-tune heavy, bf16, rank 64, 64 adapters, 16x2048 FT tokens per GPU, 4096<->14336, "
+          "dA/dB all-reduced over NCCL"}
+
+
+def hbm_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class DataParallelStep:
+    """Workload c5 on one rank of a data-parallel group: forward + backward of both projections with the
+    sum of dA/dB over the ranks as the one exchange step.
+
+    Gradients go straight into the slots of a flat bucket (loquetier_b200.dp.GradBucket); only adapters
+    that some rank trains in this batch have a slot.  Order of a step: the up projection first, whole
+    (forward, dV/dX, weight gradients), then its slots are handed to NCCL and travel under everything
+    the down projection still has to do; the down projection's weight gradients are cut into `chunks`
+    slot ranges (the train partitions are ordered by adapter, so a slot range is a row range), and
+    every range is handed to NCCL as soon as its kernel has been issued, so that only the last range's
+    exchange has nothing to hide under."""
+
+    def __init__(self, wl, torch, dist, chunks=4):
+        from loquetier_b200.dp import GradBucket, touched_union
+        self.wl, self.torch, self.dist = wl, torch, dist
+        spec = wl.spec
+        self.bucket = GradBucket([(p["h_in"], p["h_out"]) for p in wl.proj], spec["n_adapters"], spec["rank"],
+                                 wl.dt, wl.dev)
+        self.local_ids = list(spec["ids"][:wl.npart])
+        assert self.local_ids == sorted(self.local_ids), "train partitions must be ordered by adapter"
+        self.union = touched_union(self.local_ids, spec["n_adapters"])
+        self.bucket.set_touched(self.union)
+        for i, p in enumerate(wl.proj):
+            p["dA_t"], p["dB_t"] = self.bucket.tables(i, self.local_ids)
+            p["dA"], p["dB"] = self.bucket.dA[i], self.bucket.dB[i]
+        wl.rebuild_projset()
+        # slot ranges of the last projection and the partitions (= row ranges) that fall into each
+        ns = self.bucket.n_slots
+        chunks = max(1, min(chunks, ns))
+        self.ranges = []
+        my_slots = self.bucket.slots(self.local_ids)
+        for c in range(chunks):
+            s0, s1 = ns * c // chunks, ns * (c + 1) // chunks
+            parts = [k for k, sl in enumerate(my_slots) if s0 <= sl < s1]
+            self.ranges.append((s0, s1, (parts[0], parts[-1] + 1) if parts else None))
+        self.exchange = True
+        self.sub = {}
+
+    def _sub(self, p0, p1):
+        """Index pointer, ids, tables and plan of partitions [p0, p1) for a partial weight-gradient launch."""
+        wl, ops = self.wl, self.wl.ops
+        key = (p0, p1)
+        if key not in self.sub:
+            self.sub[key] = dict(part=wl.part[p0:p1 + 1].contiguous(), ids=wl.part_ids[p0:p1].contiguous())
+        d = dict(self.sub[key])
+        d["plan"] = ops.Plan(d["part"], wl.tl)
+        return d
+
+    def step(self):
+        wl, ops, b = self.wl, self.wl.ops, self.bucket
+        r, n_ad = wl.spec["rank"], wl.spec["n_adapters"]
+        b.zero_except(self.local_ids)
+        wl.sched = "single"
+        wl.build_plans()
+        last = len(wl.proj) - 1
+        for i, p in enumerate(wl.proj):
+            ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale,
+                    independent=i > 0)
+            ops.bwd_dx(p["dx"], p["dv"], p["go"], p["wa"], p["wb"], wl.pplan, r, part_ids=wl.part_ids,
+                       part_scale=wl.scale, independent=True)
+            if i < last or len(self.ranges) == 1:
+                ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan, r,
+                               part_ids=wl.part_ids, part_scale=wl.scale, n_table=n_ad,
+                               workspace=ops.wgrad_workspace(wl.dev, wl.tl, wl.npart, r, p["h_out"], p["h_in"], slot=i))
+                if self.exchange:
+                    b.reduce_slots(i, 0, b.n_slots)
+            else:
+                for c, (s0, s1, parts) in enumerate(self.ranges):
+                    if parts is not None:
+                        p0, p1 = parts
+                        d = self._sub(p0, p1)
+                        ops.wgrad_pair(p["dA_t"][p0:p1], p["dB_t"][p0:p1], p["dv"], p["x"], p["v"], p["go"], d["part"],
+                                       d["plan"], r, part_ids=d["ids"], part_scale=wl.scale, n_table=n_ad,
+                                       workspace=ops.wgrad_workspace(wl.dev, wl.tl, wl.npart, r, p["h_out"], p["h_in"],
+                                                                     slot=100 + c))
+                    if self.exchange:
+                        b.reduce_slots(i, s0, s1)
+        b.finish()
+
+
+def capture(step, torch):
+    """Warm the step up on a side stream, then capture it into a CUDA graph.  Returns graph.replay."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(2):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    return graph.replay
+
+
+def run_c5(a, rank, world, local, torch, dist, blocks, steps):
+    """Workload c5 as a record of its own: device time per step with the exchange, without it (what one
+    GPU alone needs for the same work) and the difference, which is the exposed part of the exchange."""
+    spec = workload_spec("c5", rank, world)
+    if a.seg_len > 0:
+        spec["lens"] = [a.seg_len] * len(spec["lens"])
+    wl = Workload(spec, torch.device("cuda", local))
+    dp = DataParallelStep(wl, torch, dist if world > 1 else None, chunks=a.chunks)
+    T = wl.T
+    dp.step()
+    torch.cuda.synchronize()
+    for pl in wl.plans():
+        pl.raise_if_failed()
+    rec = dict(workload="c5: " + WORKLOAD_TEXT["c5"], tokens_per_gpu=T, n_gpus=world,
+               allreduce_bytes_per_step=dp.bucket.nbytes if world > 1 else 0, slots=dp.bucket.n_slots,
+               chunks_of_last_projection=len(dp.ranges))
+    mode = "eager"
+    fn = dp.step
+    if not a.no_graph:
+        try:
+            fn = capture(dp.step, torch)
+            mode = "cuda graph replay"
+        except Exception as e:  # a collective that cannot be captured on this stack: time the eager step
+            torch.cuda.synchronize()
+            rec["graph_capture_failed"] = str(e).splitlines()[0][:200]
+            fn = dp.step
+    ms, per = timed(fn, steps, max(3, a.warmup), torch, dist, None, blocks)
+    rec.update(ms_per_step=ms, ms_per_step_min=min(per), ms_per_step_max=max(per), blocks=len(per),
+               value=T * world / (ms * 1e-3), unit="tokens/s", launch_mode=mode)
+    fwd_b, bwd_b = algorithmic_bytes(spec)
+    peak, which = hbm_peak()
+    rec["step_hbm"] = dict(algorithmic_bytes=fwd_b + bwd_b, achieved_gbs=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9,
+                           frac=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9 / peak, peak_gbs=peak, peak_source=which)
+    if a.check and world == 1:
+        # (with several ranks the slots hold sums over ranks; the 2-GPU test compares those)
+        rec["parity_max_rel_err"] = check_step(wl, torch)
+        rec["parity_checked"] = True
+    if world > 1:
+        # the same step without the exchange: the compute one GPU needs alone (per-GPU work is fixed)
+        dp.exchange = False
+        fn0 = dp.step
+        if mode != "eager":
+            fn0 = capture(dp.step, torch)
+        ms0, _ = timed(fn0, steps, 3, torch, dist, None, max(1, blocks // 2))
+        dp.exchange = True
+        rec.update(ms_per_step_without_exchange=ms0, exposed_comm_ms=ms - ms0, efficiency_vs_n1=ms0 / ms)
+    return rec
+
+
+def run_linear_host(a, local, torch):
+    """Host time of one eager MixedLoraLinear.forward - what a model pays per LoRA linear and step on top
+    of the kernels: wall clock around many forwards without a synchronisation in between, for the segment
+    counts of c2 (70) and c4 (1024).  The context (plan, adapter index) is built once per step, as in a
+    model where all LoRA linears share it."""
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    dev = torch.device("cuda", local)
+    out = {}
+    for name in ("c2", "c4"):
+        spec = workload_spec(name)
+        dt = torch.float16 if spec["dtype"] == "fp16" else torch.bfloat16
+        _, hi, ho = spec["projections"][0]
+        r, n_ad = spec["rank"], spec["n_adapters"]
+        g = torch.Generator(device=dev).manual_seed(1)
+        base = torch.nn.Linear(hi, ho, bias=False, dtype=dt, device=dev)
+        ads = [NamedLoraLayer(f"a{i}", (torch.randn((r, hi), generator=g, device=dev) / np.sqrt(hi)).to(dt),
+                              (torch.randn((ho, r), generator=g, device=dev) * 0.02).to(dt), torch.nn.Identity(), 2.0)
+               for i in range(n_ad)]
+        ctx = MixedLoraContext()
+        lin = MixedLoraLinear(ctx, base, ads, r, dt)
+        lens, ids = spec["lens"], spec["ids"]
+        seg = torch.tensor(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32), device=dev)
+        blen = BatchLenInfo([], [], 0, [], dev)
+        ctx.update(blen, ids, torch.tensor(lens, dtype=torch.int32, device=dev), seg, [])
+        x = torch.randn((sum(lens), hi), generator=g, device=dev).to(dt)
+        with torch.no_grad():
+            for _ in range(5):
+                lin(x)
+            torch.cuda.synchronize()
+            n = 200
+            t0 = time.perf_counter()
+            for _ in range(n):
+                lin(x)
+            t1 = time.perf_counter()
+            torch.cuda.synchronize()
+            t2 = time.perf_counter()
+        out[name] = dict(segments=len(lens), host_us_per_forward=(t1 - t0) / n * 1e6,
+                         device_bound_us_per_forward=(t2 - t0) / n * 1e6)
+    return out
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm"])
+    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps; the median is reported")
+    ap.add_argument("--sched", default="multi", choices=["multi", "split", "single"],
+                    help="multi: one launch per kernel class over all projections; split: the same with the "
+                         "forward of the inference rows on a second stream; single: one launch per projection")
+    ap.add_argument("--no-check", dest="check", action="store_false",
+                    help="skip the comparison of every output of the timed step with the CPU oracle (rank 0)")
+    ap.add_argument("--no-extras", action="store_true", help="c3 only: skip the c5 and rmsnorm records")
+    ap.add_argument("--chunks", type=int, default=4, help="c5: slot ranges of the last projection's exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="do not mark launches independent of each other")
-    ap.add_argument("--streams", type=int, default=3, help="streams the backward launches are dealt over")
+    ap.add_argument("--streams", type=int, default=3, help="single: streams the backward launches are dealt over")
     ap.add_argument("--no-breakdown", action="store_true", help="skip the per-kernel-class timing pass")
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
@@ -545,6 +972,7 @@ def main():
                                                           "(a smaller footprint for profiler captures)")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
+    a.blocks = max(1, a.blocks)
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -552,7 +980,15 @@ def main():
     import torch
 
     if a.workload == "rmsnorm":
-        return run_rmsnorm(a, rank, world, local, torch)
+        line = run_rmsnorm(a, rank, world, local, torch)
+        if line is not None and rank == 0:
+            print(json.dumps(line))
+        return
+    if a.workload == "linear":
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+        print(json.dumps(dict(metric="host microseconds per eager MixedLoraLinear.forward", unit="us",
+                              higher_is_better=False, data="synthetic", result=run_linear_host(a, local, torch))))
+        return
     spec = workload_spec(a.workload, rank, world)
     if a.seg_len > 0:
         assert a.workload == "c5", "--seg-len applies to c5"
@@ -563,20 +999,13 @@ def main():
         assert spec["projections"], "--only matched no projection of the workload"
     T = sum(spec["lens"])
     fwd_b, bwd_b = algorithmic_bytes(spec)
-    cfg = dict(workload=f"{a.workload}: " + {
-        "c2": "Llama-2-7B q_proj mixed batch, fp16, rank 16, 32 adapters, 2x1024 FT + 4x512 prefill + 64 decode",
-        "c3": "Llama-3-8B 7 LoRA projections of one layer, bf16, rank 16, 128 adapters, 8192 tokens, "
-              "Zipf(1.2) segment lengths in [1,2048], 25% fine-tune tokens (fwd+bwd), rest forward only",
-        "c4": "decode sweep, bf16, 1024 one-token segments, 256 adapters, rank 32, 4096->11008 and 11008->4096",
-        "c4s": "decode sweep as c4 with the tokens sorted by adapter and merged into segments, as the "
-               "reference's batch assembler orders decode requests",
-        "c5": "fine-tune heavy, bf16, rank 64, 64 adapters, 16x2048 FT tokens per GPU, 4096<->14336, "
-              "dA/dB all-reduced over NCCL"}[a.workload],
+    cfg = dict(workload=f"{a.workload}: " + WORKLOAD_TEXT[a.workload],
         tokens_per_gpu=T, segments=len(spec["lens"]), finetune_tokens=sum(l for l, f in zip(spec["lens"], spec["ft"]) if f),
         l2="one step touches %.0f MB of distinct operands (> 126 MB L2); nothing is reused between steps"
            % ((fwd_b + bwd_b) / 1e6),
         sharding="segments partitioned by adapter owner (adapter mod N), no collective" if a.workload != "c5"
-                 else "data parallel, one all-reduce per projection of its dA/dB slice, started behind its weight-gradient kernel")
+                 else "data parallel; dA/dB of the adapters some rank trains are summed over the ranks, slot range "
+                      "by slot range, each range started behind the kernel that produces it")
 
     if a.impl == "reference":
         if rank != 0:
@@ -592,79 +1021,74 @@ def main():
         return
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+    numa = bind_to_gpu_numa_node(local) if world > 1 else None
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist = None
     if world > 1:
         import torch.distributed as dist_mod
-        dist_mod.init_process_group("nccl", device_id=dev)
+        try:
+            # the exchange of c5 runs next to kernels that fill every SM: give NCCL's stream priority
+            opts = dist_mod.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+            dist_mod.init_process_group("nccl", device_id=dev, pg_options=opts)
+        except Exception:
+            dist_mod.init_process_group("nccl", device_id=dev)
         dist = dist_mod
+    peak, which = hbm_peak()
+
+    if a.workload == "c5":
+        rec = run_c5(a, rank, world, local, torch, dist, a.blocks, a.steps)
+        line = dict(metric="SMLM fwd+bwd tokens/s", value=rec["value"], unit="tokens/s", n_gpus=world, steps=a.steps,
+                    warmup=a.warmup, ms_per_step=rec["ms_per_step"], higher_is_better=True, scaling="weak",
+                    vs_baseline=None, dtype=spec["dtype"], data="synthetic", config=cfg, c5=rec,
+                    gpu_launches=(2 + 2 * 2 + 1 + rec["chunks_of_last_projection"]) * a.steps,
+                    launch_mode=rec["launch_mode"], step_hbm=rec["step_hbm"])
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            print(json.dumps(line))
+        return
 
     wl = Workload(spec, dev)
     wl.overlap = not a.no_overlap
     wl.grouped = not a.no_group
     wl.n_streams = a.streams
-    bucket = None
-    if a.workload == "c5":
-        # data-parallel fine-tuning: dA/dB of all adapters live in one flat bucket that the backward
-        # kernels accumulate into and that is all-reduced once per step
-        from loquetier_b200.dp import GradBucket
-        bucket = GradBucket([(p["h_in"], p["h_out"]) for p in wl.proj], spec["n_adapters"], spec["rank"], wl.dt, dev)
-        for i, p in enumerate(wl.proj):
-            p["dA_t"], p["dB_t"] = bucket.tables(i, wl.part_ids)
-            p["dA"], p["dB"] = bucket.dA[i], bucket.dB[i]
-        wl.accumulate_grads = True
-        cfg["allreduce_bytes_per_step"] = bucket.nbytes
-        # the exchange of a projection starts right behind its weight-gradient kernel and runs under
-        # the backward of the next projection
-        wl.after_wgrad = bucket.reduce_projection
+    wl.sched = a.sched
 
-    def eager_step():
-        if bucket is not None:
-            bucket.zero()
-        wl.step()
-        if bucket is not None:
-            bucket.finish()
-
-    eager_step()
+    wl.step()
     torch.cuda.synchronize()
-    wl.plan.raise_if_failed()
-    if wl.pplan is not None:
-        wl.pplan.raise_if_failed()
+    for pl in wl.plans():
+        pl.raise_if_failed()
 
-    use_graph = not a.no_graph and not (bucket is not None and world > 1)
-    if use_graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for _ in range(2):
-                eager_step()
-        torch.cuda.current_stream().wait_stream(side)
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            eager_step()
-        step_fn = graph.replay
-    else:
-        step_fn = eager_step
+    use_graph = not a.no_graph
+    step_fn = capture(wl.step, torch) if use_graph else wl.step
 
     with ClockSampler(local) as clk:
         time.sleep(0.3)  # let the sampler come up so that its samples fall inside the timed region
-        ms = timed(step_fn, a.steps, a.warmup, torch, dist, clk)
+        ms, per = timed(step_fn, a.steps, a.warmup, torch, dist, clk, a.blocks)
     tokens_all = T * world
     value = tokens_all / (ms * 1e-3)
 
     line = dict(metric="SMLM fwd+bwd tokens/s", value=value, unit="tokens/s", n_gpus=world, steps=a.steps,
-                warmup=a.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak", vs_baseline=None,
+                warmup=a.warmup, ms_per_step=ms, ms_per_step_min=min(per), ms_per_step_max=max(per),
+                blocks=len(per), higher_is_better=True, scaling="weak", vs_baseline=None,
                 dtype=spec["dtype"], data="synthetic", config=cfg, clocks=clk.result,
-                gpu_launches=wl.launches_per_step * a.steps,
-                launch_mode="cuda graph replay" if use_graph else "eager")
+                gpu_launches=wl.launches_per_step * a.steps * len(per), gpu_launches_per_step=wl.launches_per_step,
+                launch_mode="cuda graph replay" if use_graph else "eager", sched=wl.sched)
+    if numa is not None:
+        line["numa_node"] = numa
+
+    if a.check and rank == 0:
+        # the outputs in device memory are those of the last replay of the very step that was timed
+        torch.cuda.synchronize()
+        for pl in wl.plans():
+            pl.raise_if_failed()
+        worst = check_step(wl, torch)
+        line["parity_checked"] = True
+        line["parity_max_rel_err"] = worst
 
     if rank == 0:
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-            peak, which = float(peaks["hbm_gbs"]), "measured"
-        except Exception:
-            peak, which = 6650.0, "fallback"
         line["step_hbm"] = dict(algorithmic_bytes=fwd_b + bwd_b, achieved_gbs=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9,
                                 frac=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9 / peak, peak_gbs=peak, peak_source=which)
     if rank == 0 and not a.no_breakdown:
@@ -672,20 +1096,40 @@ def main():
         top = max(kb, key=lambda k: kb[k][0])
         t_ms, nbytes, nl = kb[top]
         ach = nbytes / (t_ms * 1e-3) / 1e9
+        # traffic stays null: no ncu capture of this very kernel and workload is read here
         line["roofline"] = dict(bound="hbm", kernel=top, achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
-                                peak_source=which, traffic=(ach and nbytes / nl * TRAFFIC_PER_ALGORITHMIC_BYTE) if top.startswith('fused_kernel(fwd') else None,
-                                launches_per_step=nl,
+                                peak_source=which, traffic=None, launches_per_step=nl,
                                 avg_launch_us=t_ms * 1e3 / nl, algorithmic_bytes_per_launch=nbytes / nl)
         line["kernels"] = {k: dict(ms_per_step=v[0], gbs=v[1] / (v[0] * 1e-3) / 1e9, frac=v[1] / (v[0] * 1e-3) / 1e9 / peak,
-                                   share=v[0] / sum(x[0] for x in kb.values())) for k, v in kb.items()}
+                                   launches=v[2], share=v[0] / sum(x[0] for x in kb.values())) for k, v in kb.items()}
 
     if not a.no_e2e:
         hp = HostPipeline(wl, torch)
-        e_ms = timed(hp.step, max(3, min(a.steps, 10)), 3, torch, dist)
+        e_ms, e_per = timed(hp.step, max(3, min(a.steps, 10)), 3, torch, dist, None, 3)
+        for pl in hp.plans:
+            pl.raise_if_failed()
         line["e2e"] = dict(value=tokens_all / (e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=hp.h2d_bytes,
                            d2h_bytes_per_step=hp.d2h_bytes, ms_per_step=e_ms,
-                           note="inputs from pinned host memory, results to pinned host memory, copies "
-                                "overlapped with kernels on separate streams")
+                           host_gbs_all_ranks=(hp.h2d_bytes + hp.d2h_bytes) * world / (e_ms * 1e-3) / 1e9,
+                           units=len(hp.units),
+                           note="inputs from pinned host memory, results to pinned host memory; every (projection, "
+                                "row block) is uploaded, computed and downloaded on its own streams, so the copies of "
+                                "one unit overlap the kernels and copies of the others; bound by the host link")
+        if a.check and rank == 0:
+            line["e2e"]["parity_max_rel_err"] = check_step(wl, torch)
+    if a.workload == "c3" and not a.no_extras and not a.only:
+        del wl, step_fn
+        if not a.no_e2e:
+            del hp
+        torch.cuda.empty_cache()
+        line["c5"] = run_c5(a, rank, world, local, torch, dist, max(3, a.blocks // 5), max(5, min(a.steps, 20)))
+        torch.cuda.empty_cache()
+        sub = argparse.Namespace(**vars(a))
+        sub.no_e2e, sub.no_cpu, sub.blocks = True, True, max(3, a.blocks // 5)
+        rms = run_rmsnorm(sub, rank, world, local, torch, dist=dist, own_group=False)
+        if rms is not None:
+            line["rmsnorm"] = {k: rms[k] for k in ("metric", "value", "unit", "ms_per_step", "step_hbm", "kernels",
+                                                   "config") if k in rms}
     if rank == 0 and world == 1 and not a.no_cpu:
         base, _ = run_cpu(spec, torch)
         line["cpu_baseline"] = base
@@ -700,10 +1144,11 @@ def main():
 # RMSNorm, the caller on either side of the projections (--workload rmsnorm)
 # ---------------------------------------------------------------------------
 
-def run_rmsnorm(a, rank, world, local, torch):
+def run_rmsnorm(a, rank, world, local, torch, dist=None, own_group=True):
     """Forward + backward of the Llama-3-8B RMSNorm over 32768 token rows of 4096 columns, bf16.
     Rows shard over ranks with no collective (every rank holds the same weight; its dW would join the
-    gradient all-reduce of the model, which is not part of this operator)."""
+    gradient all-reduce of the model, which is not part of this operator).  Returns the JSON line as a
+    dict on rank 0 (None elsewhere); with ``own_group`` false it runs inside the caller's process group."""
     from oracle import smlm_oracle as O
     rows, cols, eps = 32768, 4096, 1e-5
     e = 2
@@ -743,20 +1188,17 @@ def run_rmsnorm(a, rank, world, local, torch):
         if rank != 0:
             return
         base, sec = cpu_leg(min(90.0, max(10.0, 0.5 * a.steps)), max(1, a.steps))
-        print(json.dumps(dict(metric="RMSNorm fwd+bwd tokens/s", value=base["value"], unit="tokens/s", n_gpus=a.gpus,
-                              steps=a.steps, warmup=a.warmup, ms_per_step=sec * 1e3, higher_is_better=True,
-                              scaling="weak", vs_baseline=None, dtype="fp32 on CPU (16-bit inputs upcast)",
-                              data="synthetic", config=cfg, impl="reference", cpu_baseline=base, gpu_launches=0,
-                              e2e=dict(value=base["value"], unit="tokens/s", h2d_bytes_per_step=0,
-                                       d2h_bytes_per_step=0))))
-        return
+        return dict(metric="RMSNorm fwd+bwd tokens/s", value=base["value"], unit="tokens/s", n_gpus=a.gpus,
+                    steps=a.steps, warmup=a.warmup, ms_per_step=sec * 1e3, higher_is_better=True,
+                    scaling="weak", vs_baseline=None, dtype="fp32 on CPU (16-bit inputs upcast)",
+                    data="synthetic", config=cfg, impl="reference", cpu_baseline=base, gpu_launches=0,
+                    e2e=dict(value=base["value"], unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
     from loquetier_b200 import ops
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
-    dist = None
-    if world > 1:
+    if world > 1 and own_group:
         import torch.distributed as dist_mod
         dist_mod.init_process_group("nccl", device_id=dev)
         dist = dist_mod
@@ -786,16 +1228,14 @@ def run_rmsnorm(a, rank, world, local, torch):
         step()
     with ClockSampler(local) as clk:
         time.sleep(0.3)
-        ms = timed(graph.replay, a.steps, a.warmup, torch, dist, clk)
+        ms, per = timed(graph.replay, a.steps, a.warmup, torch, dist, clk, a.blocks)
     line = dict(metric="RMSNorm fwd+bwd tokens/s", value=rows * world / (ms * 1e-3), unit="tokens/s", n_gpus=world,
-                steps=a.steps, warmup=a.warmup, ms_per_step=ms, higher_is_better=True, scaling="weak",
+                steps=a.steps, warmup=a.warmup, ms_per_step=ms, ms_per_step_min=min(per), ms_per_step_max=max(per),
+                blocks=len(per), higher_is_better=True, scaling="weak",
                 vs_baseline=None, dtype="bf16", data="synthetic", config=cfg, clocks=clk.result,
-                gpu_launches=3 * a.steps, launch_mode="cuda graph replay")
+                gpu_launches=3 * a.steps * len(per), launch_mode="cuda graph replay")
     if rank == 0:
-        try:
-            peak, which = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"]), "measured"
-        except Exception:
-            peak, which = 6650.0, "fallback"
+        peak, which = hbm_peak()
         line["step_hbm"] = dict(algorithmic_bytes=fwd_b + bwd_b, achieved_gbs=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9,
                                 frac=(fwd_b + bwd_b) / (ms * 1e-3) / 1e9 / peak, peak_gbs=peak, peak_source=which)
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -829,16 +1269,15 @@ def run_rmsnorm(a, rank, world, local, torch):
             ho.copy_(o, non_blocking=True)
             hdx.copy_(dx, non_blocking=True)
             hdw.copy_(dw, non_blocking=True)
-        e_ms = timed(e2e_step, max(3, min(a.steps, 10)), 3, torch, dist)
+        e_ms, _ = timed(e2e_step, max(3, min(a.steps, 10)), 3, torch, dist)
         line["e2e"] = dict(value=rows * world / (e_ms * 1e-3), unit="tokens/s", h2d_bytes_per_step=2 * rows * cols * e,
                            d2h_bytes_per_step=2 * rows * cols * e + cols * e, ms_per_step=e_ms)
     if rank == 0 and world == 1 and not a.no_cpu:
         line["cpu_baseline"], _ = cpu_leg(12.0, 5)
-    if dist is not None:
+    if dist is not None and own_group:
         dist.barrier()
         dist.destroy_process_group()
-    if rank == 0:
-        print(json.dumps(line))
+    return line if rank == 0 else None
 
 
 if __name__ == "__main__":

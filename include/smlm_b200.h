@@ -128,13 +128,18 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
  * (mixed_lora.py:214-217).  `v` [T, rank] is written in the storage type like the
  * reference's intermediate (kernel_utils.py:117) and is what the backward needs.
  *
- * `independent` = 1 is a promise by the caller: this call reads nothing that the
- * previous kernel enqueued on `stream` writes (for example q_proj, k_proj and
- * v_proj of one layer, which share their input).  The launch may then start while
- * that kernel is still running - its read phase overlaps the predecessor's write
- * phase, which is how both directions of HBM are kept busy - and it still completes
- * after it, so stream order holds for everything enqueued later.  With 0 the launch
- * waits for its predecessor like any kernel.  `grouped` as in smlm_b200_gemm. */
+ * `independent` = 1 is a promise by the caller about every kernel enqueued on `stream` since, and
+ * including, the most recent launch of this library with independent = 0 (call them the open
+ * kernels): this call reads nothing and writes nothing that an open kernel writes, and writes
+ * nothing that an open kernel reads.  Typical use: q_proj, k_proj and v_proj of one layer, which
+ * share their input and write different outputs.  An independent launch does not wait for its
+ * predecessors at its start - its read phase overlaps their write phase, which is how both
+ * directions of HBM are kept busy - so it can run alongside ALL open kernels, not only the
+ * previous one: in a chain D (dependent), I1, I2 (independent) the kernel I2 may run while D is
+ * still writing, hence a call that consumes D's output must be launched with independent = 0 even if
+ * an unrelated independent launch sits between them.  An independent launch still completes after
+ * the open kernels, so stream order holds for everything enqueued later.  With 0 the launch waits
+ * for its predecessor like any kernel.  `grouped` as in smlm_b200_gemm. */
 int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, const void* const* wb_table,
                   const int32_t* seg_ids, const float* seg_scale, void* plan, int n_table, int T, int nseg,
                   int h_in, int h_out, int rank, int dtype, int is_row_major, int accumulate, int independent,
@@ -222,6 +227,53 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
                   const int32_t* part_ids, const float* part_scale, const int32_t* part_indptr, void* plan,
                   void* workspace, size_t workspace_bytes, int n_table, int T, int npart, int h_in, int h_out,
                   int rank, int dtype, int is_row_major, int accumulate_grads, int grad_fp32, void* stream);
+
+/* ---- several projections of one layer per launch ----------------------------------------------
+ * No reference counterpart: the reference calls its operator once per product and projection
+ * (kernel_utils.py:118-119 inside MixedLoraLinear.forward, mixed_lora.py:198).  Projections that share
+ * the batch - q/k/v or gate/up of a layer, or every LoRA target when their inputs are at hand - also
+ * share the segment plan, the adapter ids, the rank and the scales, so their launches can be laid end
+ * to end in one grid: short launches then stop paying a set-up and a drain each.  Results are those of
+ * the single-projection entry points, bit for bit.
+ *
+ * `projs` is a HOST array of nproj <= SMLM_MAX_PROJ descriptors; only the fields an entry point names
+ * are read.  The projections must not depend on one another: none may read or write what another
+ * writes.  `independent` is the promise of smlm_b200_fwd for the call as a whole. */
+#define SMLM_MAX_PROJ 8
+typedef struct smlm_b200_proj {
+  const void* x;                 /* [T, h_in]      forward input                                   */
+  void* y;                       /* [T, h_out]     forward output                                  */
+  void* v;                       /* [T, rank]      forward intermediate (written by fwd)           */
+  const void* go;                /* [T_ft, h_out]  gradient of y over the train rows               */
+  void* dx;                      /* [T_ft, h_in]                                                   */
+  void* dv;                      /* [T_ft, rank]   backward intermediate (written by bwd_dx)       */
+  const void* const* wa_table;   /* adapter tables as in smlm_b200_fwd                             */
+  const void* const* wb_table;
+  void* const* dA_table;         /* per-partition gradient addresses as in smlm_b200_bwd           */
+  void* const* dB_table;
+  int h_in, h_out;
+} smlm_b200_proj;
+
+/* smlm_b200_fwd for every projection: reads x, wa_table, wb_table; writes y, v. */
+int smlm_b200_fwd_multi(const smlm_b200_proj* projs, int nproj, const int32_t* seg_ids, const float* seg_scale,
+                        void* plan, int n_table, int T, int nseg, int rank, int dtype, int is_row_major,
+                        int accumulate, int independent, int grouped, void* stream);
+
+/* smlm_b200_bwd_dx for every projection: reads go, wa_table, wb_table; writes dx, dv.  T is the number of
+ * train rows the partition plan covers. */
+int smlm_b200_bwd_dx_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_ids, const float* part_scale,
+                           void* plan, int n_table, int T, int npart, int rank, int dtype, int is_row_major,
+                           int independent, void* stream);
+
+/* Workspace of smlm_b200_wgrad_pair_multi for these projections (h_in, h_out are read); same rules as
+ * smlm_b200_wgrad_workspace_bytes. */
+size_t smlm_b200_wgrad_multi_workspace_bytes(const smlm_b200_proj* projs, int nproj, int T, int npart, int rank);
+
+/* smlm_b200_wgrad_pair for every projection: reads dv, x, v, go; writes through dA_table, dB_table. */
+int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_indptr,
+                               const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
+                               size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
+                               int is_row_major, int accumulate, int grad_fp32, int independent, void* stream);
 
 /* ---- RMSNorm: the caller on either side of the q/k/v and gate/up projections ----------------- */
 

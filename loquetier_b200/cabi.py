@@ -22,6 +22,17 @@ STATUS_NAMES = {
     12: "SMLM_ERR_GROUPED_PLAN",
 }
 
+SMLM_MAX_PROJ = 8
+
+
+class SmlmProj(ctypes.Structure):
+    """``smlm_b200_proj`` of include/smlm_b200.h: the tensors of one projection for the entry points
+    that serve several projections per launch."""
+    _fields_ = [("x", c_void_p), ("y", c_void_p), ("v", c_void_p), ("go", c_void_p), ("dx", c_void_p),
+                ("dv", c_void_p), ("wa_table", c_void_p), ("wb_table", c_void_p), ("dA_table", c_void_p),
+                ("dB_table", c_void_p), ("h_in", c_int), ("h_out", c_int)]
+
+
 # name -> (restype, argtypes); mirrors include/smlm_b200.h one to one
 SIGNATURES = {
     "smlm_b200_version": (c_int, []),
@@ -43,6 +54,11 @@ SIGNATURES = {
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 11 + [c_void_p]),
     "smlm_b200_bwd": (c_int, [c_void_p] * 14 + [c_size_t] + [c_int] * 10 + [c_void_p]),
+    "smlm_b200_fwd_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 9 + [c_void_p]),
+    "smlm_b200_bwd_dx_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]),
+    "smlm_b200_wgrad_multi_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
+    "smlm_b200_wgrad_pair_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_size_t] + [c_int] * 9 + [c_void_p]),
     "smlm_b200_rms_norm": (c_int, [c_void_p] * 4 + [c_int, c_int, c_float, c_int, c_void_p]),
     "smlm_b200_rms_norm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_rms_norm_bwd": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 4 + [c_void_p]),

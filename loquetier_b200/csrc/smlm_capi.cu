@@ -6,6 +6,7 @@
 #include <algorithm>
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/smlm_b200.h"
 #include "rms_norm.cuh"
@@ -46,17 +47,55 @@ EncodeTiledFn encode_tiled_fn() {
 
 // Row-major [rows, cols] matrix of 16-bit elements, boxes of [box_rows, 64] elements
 // (128 bytes wide) stored with the 128-byte swizzle; out-of-range parts read as zero.
+// Encoding a map is a driver call of about a microsecond, and a module forward encodes several per
+// launch for tensors that mostly stay where they are (activations of a captured graph, pre-allocated
+// buffers of a serving loop), so the most recent encodings are kept in a small direct-mapped table.
+// A map depends only on (address, shape, box, type) - not on the device or the contents - so an
+// entry can never go stale.
+struct MapKey {
+  const void* base;
+  int rows, cols, box_rows, dtype;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && dtype == o.dtype;
+  }
+};
+constexpr int kMapCacheSlots = 256;
+struct MapCacheEntry {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+std::mutex g_map_mutex;
+MapCacheEntry g_map_cache[kMapCacheSlots];
+
 bool make_map_2d(CUtensorMap* m, const void* base, int rows, int cols, int box_rows, int dtype) {
+  const MapKey key = {base, rows, cols, box_rows, dtype};
+  const uintptr_t h = (reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull +
+                      static_cast<uintptr_t>(cols) * 31u + static_cast<uintptr_t>(rows) * 7u + box_rows + dtype;
+  MapCacheEntry& e = g_map_cache[(h >> 20) % kMapCacheSlots];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (e.valid && e.key == key) {
+      *m = e.map;
+      return true;
+    }
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return false;
   const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
   const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(cols) * 2};
   const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
   const cuuint32_t estr[2] = {1, 1};
-  return fn(m, dtype == SMLM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-            const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(m, dtype == SMLM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+         const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  e.key = key;
+  e.map = *m;
+  e.valid = true;
+  return true;
 }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -82,16 +121,39 @@ inline int tall_rows_for(int T, int nseg) {
 }
 inline int max_tall_pieces_of(int T, int nseg) { return T / tall_rows_for(T, nseg) + nseg; }
 
+// The opt-in to more than 48 KB of dynamic shared memory is a property of (kernel, device): it is
+// set on the first launch of a kernel on a device and remembered, not repeated per launch.
+constexpr int kMaxDevices = 64;
+std::mutex g_attr_mutex;
+std::vector<const void*> g_attr_done[kMaxDevices];
+
+bool ensure_dynamic_smem(const void* kern, int smem_bytes) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    cudaGetLastError();
+    return false;
+  }
+  {
+    std::lock_guard<std::mutex> lock(g_attr_mutex);
+    for (const void* k : g_attr_done[dev])
+      if (k == kern) return true;
+  }
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  std::lock_guard<std::mutex> lock(g_attr_mutex);
+  g_attr_done[dev].push_back(kern);
+  return true;
+}
+
 template <typename Kern, typename... Args>
 int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cudaStream_t stream,
            const Args&... args) {
   if (grid.x == 0 || grid.y == 0) return SMLM_OK;
-  if (smem_bytes > 48 * 1024) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes) != cudaSuccess) {
-      cudaGetLastError();
-      return SMLM_ERR_CUDA;
-    }
-  }
+  // every instantiation is launched with one shared-memory size, so "done" needs no size
+  if (smem_bytes > 48 * 1024 && !ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes))
+    return SMLM_ERR_CUDA;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
   cfg.blockDim = dim3(threads, 1, 1);
@@ -118,8 +180,8 @@ int launch(Kern kern, dim3 grid, int threads, int cluster_x, int smem_bytes, cud
 // ---- fused shrink + expand ----------------------------------------------------
 
 template <typename T, int R16, bool RM>
-int launch_fused(const FusedArgs& a, const FusedMaps& tm, int max_pieces, bool grouped, cudaStream_t stream) {
-  const dim3 grid(max_pieces * a.ksplit, 1, 1);
+int launch_fused(const FusedArgs& a, const FusedMapsN& tm, int ctas, bool grouped, cudaStream_t stream) {
+  const dim3 grid(ctas, 1, 1);
   return grouped ? launch(fused_kernel<T, R16, RM, true>, grid, kFusedThreads, a.ksplit, FusedSmem<R16, RM>::kTotal,
                           stream, a, tm)
                  : launch(fused_kernel<T, R16, RM, false>, grid, kFusedThreads, a.ksplit,
@@ -127,12 +189,12 @@ int launch_fused(const FusedArgs& a, const FusedMaps& tm, int max_pieces, bool g
 }
 
 template <typename T, bool RM>
-int dispatch_fused_r(const FusedArgs& a, const FusedMaps& tm, int max_pieces, bool grouped, cudaStream_t stream) {
+int dispatch_fused_r(const FusedArgs& a, const FusedMapsN& tm, int ctas, bool grouped, cudaStream_t stream) {
   const int r16 = (a.R + 15) / 16;
-  if (r16 <= 1) return launch_fused<T, 1, RM>(a, tm, max_pieces, grouped, stream);
-  if (r16 <= 2) return launch_fused<T, 2, RM>(a, tm, max_pieces, grouped, stream);
-  if (r16 <= 4) return launch_fused<T, 4, RM>(a, tm, max_pieces, grouped, stream);
-  return launch_fused<T, 8, RM>(a, tm, max_pieces, grouped, stream);
+  if (r16 <= 1) return launch_fused<T, 1, RM>(a, tm, ctas, grouped, stream);
+  if (r16 <= 2) return launch_fused<T, 2, RM>(a, tm, ctas, grouped, stream);
+  if (r16 <= 4) return launch_fused<T, 4, RM>(a, tm, ctas, grouped, stream);
+  return launch_fused<T, 8, RM>(a, tm, ctas, grouped, stream);
 }
 
 // ---- the tcgen05 variant for ranks above 32 ----------------------------------
@@ -160,91 +222,136 @@ inline bool use_tensor_core_kernel(int T, int nseg, int R, int mode) {
   return T >= 128 * 96 && T / std::max(nseg, 1) >= 96;
 }
 
-// OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
-int run_fused(void* out, void* mid, const void* in, const void* const* w1_table, const void* const* w2_table,
-              const int32_t* ids, const float* scale, void* plan, int n_table, int T, int nseg, int K1, int R,
-              int N2, int dtype, int row_major, int scale_mid, int accumulate, int independent, int mode,
+// One job of a fused launch: OUT[T, N2] (+)= s2 * round(s1 * IN[T, K1] . W1) . W2 per segment, MID[T, R] written.
+struct FusedJobDesc {
+  void* out;
+  void* mid;
+  const void* in;
+  const void* const* w1_table;
+  const void* const* w2_table;
+  int K1, N2, accumulate;
+};
+
+// Runs njobs jobs that share the plan, the adapter ids, the rank and the scale.  The jobs must not
+// depend on one another (none reads what another writes).  Up to kFusedMaxJobs of them share one
+// launch; the tcgen05 variant is launched once per job.
+int run_fused(const FusedJobDesc* jobs, int njobs, const int32_t* ids, const float* scale, void* plan, int n_table,
+              int T, int nseg, int R, int dtype, int row_major, int scale_mid, int independent, int mode,
               int grouped, cudaStream_t stream) {
-  FusedArgs a;
-  a.out = out; a.mid = mid; a.w1_table = w1_table; a.w2_table = w2_table; a.ids = ids; a.scale = scale;
-  a.plan = static_cast<int*>(plan);
-  a.n_table = n_table; a.K1 = K1; a.R = R; a.N2 = N2; a.scale_mid = scale_mid; a.accumulate = accumulate;
-  a.independent = independent;
-  a.mode = mode;
   if (use_tensor_core_kernel(T, nseg, R, mode)) {
-    TcArgs t;
-    t.out = out; t.mid = mid; t.w1_table = w1_table; t.w2_table = w2_table; t.ids = ids; t.scale = scale;
-    t.plan = static_cast<int*>(plan);
-    t.n_table = n_table; t.K1 = K1; t.R = R; t.N2 = N2; t.scale_mid = scale_mid; t.accumulate = accumulate;
-    t.independent = independent;
-    TcMaps m;
-    if (!make_map_2d(&m.in16, in, T, K1, 16, dtype) || !make_map_2d(&m.out16, out, T, N2, 16, dtype))
-      return SMLM_ERR_CUDA;
     const int mt = max_tall_pieces_of(T, nseg);
-    if (dtype == SMLM_F16)
-      return row_major ? dispatch_tc<__half, true>(t, m, mt, stream) : dispatch_tc<__half, false>(t, m, mt, stream);
-    return row_major ? dispatch_tc<__nv_bfloat16, true>(t, m, mt, stream)
-                     : dispatch_tc<__nv_bfloat16, false>(t, m, mt, stream);
+    for (int j = 0; j < njobs; ++j) {
+      const FusedJobDesc& d = jobs[j];
+      TcArgs t;
+      t.out = d.out; t.mid = d.mid; t.w1_table = d.w1_table; t.w2_table = d.w2_table; t.ids = ids; t.scale = scale;
+      t.plan = static_cast<int*>(plan);
+      t.n_table = n_table; t.K1 = d.K1; t.R = R; t.N2 = d.N2; t.scale_mid = scale_mid; t.accumulate = d.accumulate;
+      t.independent = (independent || j > 0) ? 1 : 0;
+      TcMaps m;
+      if (!make_map_2d(&m.in16, d.in, T, d.K1, 16, dtype) || !make_map_2d(&m.out16, d.out, T, d.N2, 16, dtype))
+        return SMLM_ERR_CUDA;
+      int rc;
+      if (dtype == SMLM_F16)
+        rc = row_major ? dispatch_tc<__half, true>(t, m, mt, stream) : dispatch_tc<__half, false>(t, m, mt, stream);
+      else
+        rc = row_major ? dispatch_tc<__nv_bfloat16, true>(t, m, mt, stream)
+                       : dispatch_tc<__nv_bfloat16, false>(t, m, mt, stream);
+      if (rc != SMLM_OK) return rc;
+    }
+    return SMLM_OK;
   }
   const int mp = max_pieces_of(T, nseg);
-  // One CTA per SM.  A piece can be split over the KS CTAs of a cluster; pick the KS that
-  // minimises (waves of 148 CTAs) x (work per CTA + fixed cost of set-up and the cluster reduce).
   const int r16b = (R + 15) / 16;
   const int r16 = r16b > 4 ? 8 : (r16b > 2 ? 4 : r16b);
   const int kc = 64 * fused_chunks(r16);
-  const int ksteps = (K1 + kc - 1) / kc, nslabs = (N2 + fused_slab(r16) - 1) / fused_slab(r16);
-  // Estimated launch time in microseconds for a split of k (constants fitted to device-side
-  // timelines on B200): set-up, a read phase that is bound either by the latency of its ring
-  // stages or by what one SM can ingest, the reduce across the cluster, and a write phase
-  // bound the same way.
   // pieces the plan is expected to hold: its capacity, except that a grouped plan turns the short
   // segments of an adapter into one gather piece, so no more than one piece per adapter comes from them
   const int est_pieces = grouped ? std::min(mp, T / piece_rows_for(T) + std::min(nseg, n_table)) : mp;
-  int ks = 1;
-  double best = 1e30;
   const double stage_kb = 64.0 * kc * 2 / 1024.0 * 1.28, slab_kb = 64.0 * fused_slab(r16) * 2 / 1024.0;
-  for (int k = 1; k <= 4; ++k) {
-    if (k > 1 && ((mode != kFusedExpandOnly && ksteps < k) || (mode != kFusedShrinkOnly && nslabs < k))) break;
-    const int slots = kNumSMs * fused_ctas_per_sm(r16);
-    const int ctas = std::max(est_pieces, 1) * k;
-    const int waves = (ctas + slots - 1) / slots;
-    const double load = std::max(1.0, std::min<double>(ctas, slots) / kNumSMs);  // CTAs sharing one SM
-    const int nk = (ksteps + k - 1) / k, ns = (nslabs + k - 1) / k;
-    const double ph1 = mode == kFusedExpandOnly ? 0.0 : std::max(2.5 + 0.9 * nk, load * nk * stage_kb / 35.0);
-    const double ph3 = mode == kFusedShrinkOnly ? 0.0 : std::max(1.0 + 1.2 * ns, load * ns * slab_kb / 33.0);
-    const double ph2 = (k > 1 && mode != kFusedExpandOnly) ? 1.0 * k : 0.6;
-    const double cost = waves * (2.0 + ph1 + ph2 + ph3);
-    if (cost < best - 1e-9) {
-      best = cost;
-      ks = k;
+  const int slots = kNumSMs * fused_ctas_per_sm(r16);
+  for (int j0 = 0; j0 < njobs; j0 += kFusedMaxJobs) {
+    const int nj = std::min(kFusedMaxJobs, njobs - j0);
+    // A piece can be split over the KS CTAs of a cluster; pick the KS that minimises the estimated
+    // time of the launch in microseconds (constants fitted to device-side timelines on B200): per
+    // CTA a set-up, a read phase that is bound either by the latency of its ring stages or by what
+    // one SM can ingest, the reduce across the cluster, and a write phase bound the same way.  One
+    // job: waves of CTAs x time per CTA.  Several jobs: their CTAs differ in length, so the launch
+    // takes the summed CTA time over the CTA slots, and never less than its longest CTA.
+    int ks = 1;
+    double best = 1e30;
+    for (int k = 1; k <= 4; ++k) {
+      bool fits = true;
+      double sum = 0.0, longest = 0.0;
+      const int ctas = std::max(est_pieces, 1) * k * nj;
+      const double load = std::max(1.0, std::min<double>(ctas, slots) / kNumSMs);  // CTAs sharing one SM
+      for (int j = 0; j < nj; ++j) {
+        const FusedJobDesc& d = jobs[j0 + j];
+        const int ksteps = (d.K1 + kc - 1) / kc, nslabs = (d.N2 + fused_slab(r16) - 1) / fused_slab(r16);
+        if (k > 1 && ((mode != kFusedExpandOnly && ksteps < k) || (mode != kFusedShrinkOnly && nslabs < k)))
+          fits = false;
+        const int nk = (ksteps + k - 1) / k, ns = (nslabs + k - 1) / k;
+        const double ph1 = mode == kFusedExpandOnly ? 0.0 : std::max(2.5 + 0.9 * nk, load * nk * stage_kb / 35.0);
+        const double ph3 = mode == kFusedShrinkOnly ? 0.0 : std::max(1.0 + 1.2 * ns, load * ns * slab_kb / 33.0);
+        const double ph2 = (k > 1 && mode != kFusedExpandOnly) ? 1.0 * k : 0.6;
+        const double t = 2.0 + ph1 + ph2 + ph3;
+        sum += t * std::max(est_pieces, 1) * k;
+        longest = std::max(longest, t);
+      }
+      if (!fits) break;
+      const int waves = (ctas + slots - 1) / slots;
+      const double cost = nj == 1 ? waves * longest : std::max(longest, sum / std::min(ctas, slots));
+      if (cost < best - 1e-9) {
+        best = cost;
+        ks = k;
+      }
     }
+    FusedArgs a;
+    FusedMapsN tm;
+    a.ids = ids; a.scale = scale; a.plan = static_cast<int*>(plan);
+    a.n_table = n_table; a.R = R; a.ksplit = ks; a.ctas_per_job = mp * ks; a.scale_mid = scale_mid;
+    a.independent = (independent || j0 > 0) ? 1 : 0;
+    a.mode = mode;
+    for (int j = 0; j < kFusedMaxJobs; ++j) {
+      const FusedJobDesc& d = jobs[j0 + std::min(j, nj - 1)];  // unused slots repeat the last job
+      // a half-only launch has no IN (expand only) or no OUT (shrink only): describe the tensor it does
+      // have in the unused slots, they are never dereferenced
+      const void* in_t = mode == kFusedExpandOnly ? d.out : d.in;
+      const int in_cols = mode == kFusedExpandOnly ? d.N2 : d.K1;
+      void* out_t = mode == kFusedShrinkOnly ? const_cast<void*>(d.in) : d.out;
+      const int out_cols = mode == kFusedShrinkOnly ? d.K1 : d.N2;
+      FusedJob& fj = a.job[j];
+      fj.in = in_t; fj.out = d.out; fj.mid = d.mid; fj.w1_table = d.w1_table; fj.w2_table = d.w2_table;
+      fj.K1 = d.K1; fj.N2 = d.N2; fj.accumulate = d.accumulate; fj.pad_ = 0;
+      if (j >= nj) {
+        tm.m[j] = tm.m[nj - 1];
+        continue;
+      }
+      if (!make_map_2d(&tm.m[j].in8, in_t, T, in_cols, 8, dtype) ||
+          !make_map_2d(&tm.m[j].in16, in_t, T, in_cols, 16, dtype) ||
+          !make_map_2d(&tm.m[j].out, out_t, T, out_cols, 16, dtype) ||
+          !make_map_2d(&tm.m[j].out8, out_t, T, out_cols, 8, dtype))
+        return SMLM_ERR_CUDA;
+    }
+    const bool g = grouped != 0;
+    const int ctas = mp * ks * nj;
+    int rc;
+    if (dtype == SMLM_F16)
+      rc = row_major ? dispatch_fused_r<__half, true>(a, tm, ctas, g, stream)
+                     : dispatch_fused_r<__half, false>(a, tm, ctas, g, stream);
+    else
+      rc = row_major ? dispatch_fused_r<__nv_bfloat16, true>(a, tm, ctas, g, stream)
+                     : dispatch_fused_r<__nv_bfloat16, false>(a, tm, ctas, g, stream);
+    if (rc != SMLM_OK) return rc;
   }
-  a.ksplit = ks;
-  FusedMaps tm;
-  // a half-only launch has no IN (expand only) or no OUT (shrink only): describe the tensor it does
-  // have in the unused slots, they are never dereferenced
-  const void* in_t = mode == kFusedExpandOnly ? out : in;
-  const int in_cols = mode == kFusedExpandOnly ? N2 : K1;
-  void* out_t = mode == kFusedShrinkOnly ? const_cast<void*>(in) : out;
-  const int out_cols = mode == kFusedShrinkOnly ? K1 : N2;
-  a.in = in_t;
-  if (!make_map_2d(&tm.in8, in_t, T, in_cols, 8, dtype) || !make_map_2d(&tm.in16, in_t, T, in_cols, 16, dtype) ||
-      !make_map_2d(&tm.out, out_t, T, out_cols, 16, dtype) || !make_map_2d(&tm.out8, out_t, T, out_cols, 8, dtype))
-    return SMLM_ERR_CUDA;
-  const bool g = grouped != 0;
-  if (dtype == SMLM_F16)
-    return row_major ? dispatch_fused_r<__half, true>(a, tm, mp, g, stream)
-                     : dispatch_fused_r<__half, false>(a, tm, mp, g, stream);
-  return row_major ? dispatch_fused_r<__nv_bfloat16, true>(a, tm, mp, g, stream)
-                   : dispatch_fused_r<__nv_bfloat16, false>(a, tm, mp, g, stream);
+  return SMLM_OK;
 }
 
 // ---- wgrad ------------------------------------------------------------------
 
 template <typename T, int RT>
 int launch_wgrad(const WgradArgs& a, const WgradMaps& tm, int groups, cudaStream_t stream) {
-  return launch(wgrad_kernel<T, RT>, dim3(groups, a.job[0].slabs + a.job[1].slabs, 1), kWgThreads, 1,
-                WgradSmem<RT>::kTotal, stream, a, tm);
+  return launch(wgrad_kernel<T, RT>, dim3(groups, a.slabs_total, 1), kWgThreads, 1, WgradSmem<RT>::kTotal, stream, a,
+                tm);
 }
 
 struct WgradJobDesc {
@@ -261,7 +368,7 @@ inline int wgrad_rt(int R) {
   return rtb > 4 ? 8 : (rtb > 2 ? 4 : rtb);
 }
 
-// How a batch of T token rows in npart partitions is cut for the two jobs' column counts.
+// How a batch of T token rows in npart partitions is cut for the jobs' column counts.
 struct WgradShape {
   int slab, slabs_total, group, groups;
   size_t ticket_bytes, scratch_bytes;
@@ -274,30 +381,28 @@ inline bool wgrad_uses_tensor_cores(int R) {
   return R > 32 ? m >= 0 : m > 0;
 }
 
-WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1, bool tc) {
+WgradShape wgrad_shape(int T, int npart, int R, const int* h, int nh, bool tc) {
   WgradShape s;
   const int rt = tc ? std::max(2, wgrad_rt(R)) : wgrad_rt(R);  // the tcgen05 kernel pads ranks below 32
   s.slab = tc ? wg_tc_slab(rt) : 4 * wgrad_cols_per_warp(rt);
-  s.slabs_total = (h0 + s.slab - 1) / s.slab + (h1 > 0 ? (h1 + s.slab - 1) / s.slab : 0);
+  s.slabs_total = 0;
+  for (int i = 0; i < nh; ++i)
+    if (h[i] > 0) s.slabs_total += (h[i] + s.slab - 1) / s.slab;
   const int mp = std::max(1, max_pieces_of(T, npart));
-  long long g;
-  if (tc) {
-    // one CTA per SM: the group size that minimises (waves of 148 CTAs) x (pieces per CTA + a
-    // fixed cost of about two pieces for set-up and closing runs)
-    long long best = -1;
-    g = 1;
-    for (int c = 1; c <= kWgMaxGroup; ++c) {
-      const long long ctas = static_cast<long long>((mp + c - 1) / c) * s.slabs_total;
-      const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (c + 2);
-      if (best < 0 || cost < best) {
-        best = cost;
-        g = c;
-      }
+  // CTAs that run side by side: one per SM for the tcgen05 kernel, two for the other.  The group
+  // size (pieces per CTA) that minimises  rounds of CTAs x (pieces per CTA + a fixed cost for set-up
+  // and closing runs, worth about two pieces of the tcgen05 kernel's 512-column slabs and four of the
+  // other's 256-column ones); a launch with fewer CTAs than slots takes one round.
+  const long long slots = tc ? kNumSMs : 2 * kNumSMs;
+  const int fixed = tc ? 2 : 4;
+  long long best = -1, g = 1;
+  for (int c = 1; c <= kWgMaxGroup; ++c) {
+    const long long ctas = static_cast<long long>((mp + c - 1) / c) * s.slabs_total;
+    const long long cost = ((ctas + slots - 1) / slots) * (c + fixed);
+    if (best < 0 || cost < best) {
+      best = cost;
+      g = c;
     }
-  } else {
-    // one wave of two CTAs per SM, each with at most kWgMaxGroup pieces
-    g = (static_cast<long long>(mp) * s.slabs_total + 2 * kNumSMs - 1) / (2 * kNumSMs);
-    g = std::max(1LL, std::min<long long>(g, kWgMaxGroup));
   }
   s.group = static_cast<int>(g);
   s.groups = (mp + s.group - 1) / s.group;
@@ -306,32 +411,36 @@ WgradShape wgrad_shape(int T, int npart, int R, int h0, int h1, bool tc) {
   return s;
 }
 
-// One launch for one or two jobs (job1 == nullptr: one).
-int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t* part_indptr, const float* scale,
+// One launch for up to kWgMaxJobs jobs.
+int run_wgrad(const WgradJobDesc* jobs, int njobs, const int32_t* part_indptr, const float* scale,
               const int32_t* ids, int n_table, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
-              int R, int dtype, int accumulate, int grad_fp32, int independent, cudaStream_t stream) {
+              int R, int dtype, int accumulate, int grad_fp32, int independent, bool tc, cudaStream_t stream) {
+  if (njobs < 1 || njobs > kWgMaxJobs) return SMLM_ERR_INVALID_ARGUMENT;
   WgradArgs a;
   WgradMaps tm;
-  const bool tc = wgrad_uses_tensor_cores(R);
   const int rt = tc ? std::max(2, wgrad_rt(R)) : wgrad_rt(R);
-  const WgradShape sh = wgrad_shape(T, npart, R, job0->H, job1 ? job1->H : 0, tc);
+  int hs[kWgMaxJobs];
+  for (int j = 0; j < njobs; ++j) hs[j] = jobs[j].H;
+  const WgradShape sh = wgrad_shape(T, npart, R, hs, njobs, tc);
   if (workspace == nullptr || workspace_bytes < sh.ticket_bytes + sh.scratch_bytes) return SMLM_ERR_WORKSPACE;
   if (!aligned16(workspace)) return SMLM_ERR_MISALIGNED;
-  const WgradJobDesc* jobs[2] = {job0, job1};
   WgradTcMaps tcm = {};
-  for (int j = 0; j < 2; ++j) {
+  int slab_at = 0;
+  for (int j = 0; j < kWgMaxJobs; ++j) {
     WgradJob& w = a.job[j];
-    if (jobs[j] == nullptr) {
-      w.g_table = nullptr; w.p = nullptr; w.H = 0; w.transposed = 0; w.use_scale = 0; w.slabs = 0;
+    if (j >= njobs) {
+      w.g_table = nullptr; w.p = nullptr; w.H = 0; w.transposed = 0; w.use_scale = 0; w.slab_begin = slab_at;
       tm.q[j] = tm.q[0];
       tcm.p[j] = tcm.p[0];
       continue;
     }
-    if (tc && !make_map_2d(&tcm.p[j], jobs[j]->p, T, R, 16, dtype)) return SMLM_ERR_CUDA;
-    w.g_table = jobs[j]->g_table; w.p = jobs[j]->p; w.H = jobs[j]->H; w.transposed = jobs[j]->transposed;
-    w.use_scale = jobs[j]->use_scale; w.slabs = (jobs[j]->H + sh.slab - 1) / sh.slab;
-    if (!make_map_2d(&tm.q[j], jobs[j]->q, T, jobs[j]->H, 16, dtype)) return SMLM_ERR_CUDA;
+    if (tc && !make_map_2d(&tcm.p[j], jobs[j].p, T, R, 16, dtype)) return SMLM_ERR_CUDA;
+    w.g_table = jobs[j].g_table; w.p = jobs[j].p; w.H = jobs[j].H; w.transposed = jobs[j].transposed;
+    w.use_scale = jobs[j].use_scale; w.slab_begin = slab_at;
+    slab_at += (jobs[j].H + sh.slab - 1) / sh.slab;
+    if (!make_map_2d(&tm.q[j], jobs[j].q, T, jobs[j].H, 16, dtype)) return SMLM_ERR_CUDA;
   }
+  a.njobs = njobs; a.slabs_total = sh.slabs_total;
   a.part_indptr = part_indptr; a.scale = scale; a.ids = ids; a.n_table = n_table;
   a.plan = static_cast<int*>(plan);
   a.tickets = static_cast<int*>(workspace);
@@ -339,9 +448,8 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   a.npart = npart; a.T = T; a.R = R; a.group = sh.group; a.accumulate = accumulate; a.out_fp32 = grad_fp32;
   a.independent = independent;
   if (tc) {
-    tcm.q[0] = tm.q[0];
-    tcm.q[1] = tm.q[1];
-    const dim3 grid(sh.groups, a.job[0].slabs + a.job[1].slabs, 1);
+    for (int j = 0; j < kWgMaxJobs; ++j) tcm.q[j] = tm.q[j];
+    const dim3 grid(sh.groups, sh.slabs_total, 1);
     if (dtype == SMLM_F16) {
       if (rt <= 2) return launch(wgrad_tc_kernel<__half, 2>, grid, kWgTcThreads, 1, WgradTcSmem<2>::kTotal, stream, a, tcm);
       return rt <= 4 ? launch(wgrad_tc_kernel<__half, 4>, grid, kWgTcThreads, 1, WgradTcSmem<4>::kTotal, stream, a, tcm)
@@ -366,6 +474,14 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
   return launch_wgrad<__nv_bfloat16, 8>(a, tm, sh.groups, stream);
 }
 
+// Workspace that serves either kernel variant, so that a buffer sized before a change of the
+// tensor-core mode stays valid.
+size_t wgrad_workspace_need(int T, int npart, int R, const int* h, int nh) {
+  const WgradShape a = wgrad_shape(T, npart, R, h, nh, false);
+  const WgradShape b = wgrad_shape(T, npart, R, h, nh, true);
+  return std::max(a.ticket_bytes + a.scratch_bytes, b.ticket_bytes + b.scratch_bytes);
+}
+
 // ---- built-in scratch for callers that cannot allocate ------------------------------
 // Some hosts of this library run where device allocation is off the table: inside a
 // latency-critical serving loop that has pre-carved all of its memory, in a plugin that
@@ -376,7 +492,6 @@ int run_wgrad(const WgradJobDesc* job0, const WgradJobDesc* job1, const int32_t*
 constexpr size_t kStaticWgradBytes = SMLM_STATIC_WGRAD_BYTES;
 static __device__ __align__(256) unsigned char g_wgrad_static_scratch[kStaticWgradBytes];
 
-constexpr int kMaxDevices = 64;
 std::mutex g_static_mutex;
 void* g_static_scratch_ptr[kMaxDevices] = {};
 
@@ -463,6 +578,9 @@ int launch_rms_bwd(void* dx, void* dw, const void* go, const void* x, const void
                 static_cast<const float*>(partial), g, cols, dw_fp32);
 }
 
+inline bool projs_ok(const smlm_b200_proj* projs, int nproj) {
+  return projs != nullptr && nproj >= 1 && nproj <= SMLM_MAX_PROJ;
+}
 inline bool small_dim_ok(int v) { return v >= 8 && v <= 128 && (v % 8) == 0; }
 inline bool large_dim_ok(int v) { return v >= 8 && (v % 8) == 0; }
 
@@ -573,13 +691,15 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
     // shrink: the small dimension is the output width; y plays the part of MID
     if (!small_dim_ok(d_out) || !large_dim_ok(d_in)) return SMLM_ERR_NO_KERNEL;
     if (accumulate) return SMLM_ERR_NO_KERNEL;
-    return run_fused(nullptr, y, x, w_table, nullptr, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, d_out, 64,
-                     dtype, is_row_major, 1, 0, 0, kFusedShrinkOnly, grouped, st);
+    const FusedJobDesc job = {nullptr, y, x, w_table, nullptr, d_in, 64, 0};
+    return run_fused(&job, 1, seg_ids, seg_scale, plan, n_table, T, nseg, d_out, dtype, is_row_major, 1, 0,
+                     kFusedShrinkOnly, grouped, st);
   }
   // expand: the small dimension is the input width; x plays the part of MID
   if (!small_dim_ok(d_in) || !large_dim_ok(d_out)) return SMLM_ERR_NO_KERNEL;
-  return run_fused(y, const_cast<void*>(x), nullptr, nullptr, w_table, seg_ids, seg_scale, plan, n_table, T, nseg, 64,
-                   d_in, d_out, dtype, is_row_major, 0, accumulate, 0, kFusedExpandOnly, grouped, st);
+  const FusedJobDesc job = {y, const_cast<void*>(x), nullptr, nullptr, w_table, 64, d_out, accumulate};
+  return run_fused(&job, 1, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, dtype, is_row_major, 0, 0,
+                   kFusedExpandOnly, grouped, st);
 }
 
 int smlm_b200_set_tensor_core_mode(int mode) {
@@ -599,21 +719,16 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(y) || !aligned16(x) || !aligned16(v) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
-  return run_fused(y, v, x, wa_table, wb_table, seg_ids, seg_scale, plan, n_table, T, nseg, h_in, rank, h_out,
-                   dtype, is_row_major, /*scale_mid=*/0, accumulate, independent != 0, kFusedBoth, grouped,
-                   static_cast<cudaStream_t>(stream));
+  const FusedJobDesc job = {y, v, x, wa_table, wb_table, h_in, h_out, accumulate};
+  return run_fused(&job, 1, seg_ids, seg_scale, plan, n_table, T, nseg, rank, dtype, is_row_major, /*scale_mid=*/0,
+                   independent != 0, kFusedBoth, grouped, static_cast<cudaStream_t>(stream));
 }
 
 size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1) {
   if (T < 0 || npart < 0 || rank <= 0 || h0 <= 0 || h1 < 0) return 0;
   // enough for either kernel, so that a buffer sized before a change of the tensor-core mode stays valid
-  const WgradShape sh = wgrad_shape(T, npart, rank, h0, h1, false);
-  size_t need = sh.ticket_bytes + sh.scratch_bytes;
-  {
-    const WgradShape st = wgrad_shape(T, npart, rank, h0, h1, true);
-    need = std::max(need, st.ticket_bytes + st.scratch_bytes);
-  }
-  return need;
+  const int hs[2] = {h0, h1};
+  return wgrad_workspace_need(T, npart, rank, hs, 2);
 }
 
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
@@ -627,8 +742,9 @@ int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const in
   if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
   const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
-  return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, workspace, workspace_bytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, 0, static_cast<cudaStream_t>(stream));
+  return run_wgrad(&job, 1, part_indptr, part_scale, nullptr, 0, plan, workspace, workspace_bytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, 0, wgrad_uses_tensor_cores(rank),
+                   static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
@@ -641,7 +757,10 @@ int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, c
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(p) || !aligned16(q) || !aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h)) return SMLM_ERR_NO_KERNEL;
-  const WgradShape sh = wgrad_shape(T, npart, rank, h, 0, wgrad_uses_tensor_cores(rank));
+  // the kernel variant is chosen once, here: the size check, the ticket range that is cleared and the
+  // launch all follow this one reading of the process-wide mode
+  const bool tc = wgrad_uses_tensor_cores(rank);
+  const WgradShape sh = wgrad_shape(T, npart, rank, &h, 1, tc);
   if (sh.ticket_bytes + sh.scratch_bytes > kStaticWgradBytes) return SMLM_ERR_STATIC_LIMIT;
   void* scratch = nullptr;
   const int rc = static_scratch_of_current_device(&scratch);
@@ -653,8 +772,8 @@ int smlm_b200_wgrad_static(void* const* g_table, const void* p, const void* q, c
     return SMLM_ERR_CUDA;
   }
   const WgradJobDesc job = {g_table, p, q, h, transposed, part_scale != nullptr};
-  return run_wgrad(&job, nullptr, part_indptr, part_scale, nullptr, 0, plan, scratch, kStaticWgradBytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, 0, st);
+  return run_wgrad(&job, 1, part_indptr, part_scale, nullptr, 0, plan, scratch, kStaticWgradBytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, 0, tc, st);
 }
 
 int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const void* dv, const void* x,
@@ -671,10 +790,11 @@ int smlm_b200_wgrad_pair(void* const* dA_table, void* const* dB_table, const voi
   if (!aligned16(dv) || !aligned16(x) || !aligned16(v) || !aligned16(go) || !aligned16(plan))
     return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank) || !large_dim_ok(h_in) || !large_dim_ok(h_out)) return SMLM_ERR_NO_KERNEL;
-  const WgradJobDesc jb = {dB_table, v, go, h_out, is_row_major ? 0 : 1, part_scale != nullptr};
-  const WgradJobDesc ja = {dA_table, dv, x, h_in, is_row_major ? 1 : 0, 0};
-  return run_wgrad(&jb, &ja, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes, npart, T,
-                   rank, dtype, accumulate, grad_fp32, independent != 0, static_cast<cudaStream_t>(stream));
+  const WgradJobDesc jobs[2] = {{dB_table, v, go, h_out, is_row_major ? 0 : 1, part_scale != nullptr},
+                                {dA_table, dv, x, h_in, is_row_major ? 1 : 0, 0}};
+  return run_wgrad(jobs, 2, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, independent != 0, wgrad_uses_tensor_cores(rank),
+                   static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_table, const void* const* wb_table,
@@ -692,9 +812,9 @@ int smlm_b200_bwd_dx(void* dx, void* dv, const void* go, const void* const* wa_t
   // dV = scale * gO . B : B is [h_out, r] (r contiguous) in the PEFT layout, i.e. a row-major
   // [K = h_out][N = r] operand; the math layout B [r, h_out] is the column-major one.  The layout
   // flag therefore flips for both products of this launch (dX = dV . A likewise).
-  return run_fused(dx, dv, go, wb_table, wa_table, part_ids, part_scale, plan, n_table, T, npart, h_out, rank,
-                   h_in, dtype, !is_row_major, /*scale_mid=*/1, 0, independent != 0, kFusedBoth, grouped,
-                   static_cast<cudaStream_t>(stream));
+  const FusedJobDesc job = {dx, dv, go, wb_table, wa_table, h_out, h_in, 0};
+  return run_fused(&job, 1, part_ids, part_scale, plan, n_table, T, npart, rank, dtype, !is_row_major,
+                   /*scale_mid=*/1, independent != 0, kFusedBoth, grouped, static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* dv, const void* go,
@@ -713,6 +833,94 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
   return smlm_b200_wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, part_ids, part_scale, plan, workspace,
                               workspace_bytes, n_table, npart, T, h_in, h_out, rank, dtype, is_row_major,
                               accumulate_grads, grad_fp32, 0, stream);
+}
+
+// ---- several projections per launch ---------------------------------------------------
+
+int smlm_b200_fwd_multi(const smlm_b200_proj* projs, int nproj, const int32_t* seg_ids, const float* seg_scale,
+                        void* plan, int n_table, int T, int nseg, int rank, int dtype, int is_row_major,
+                        int accumulate, int independent, int grouped, void* stream) {
+  if (T < 0 || nseg < 0 || n_table < 0 || !projs_ok(projs, nproj)) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || nseg == 0) return SMLM_OK;
+  if (plan == nullptr || !aligned16(plan)) return plan == nullptr ? SMLM_ERR_INVALID_ARGUMENT : SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank)) return SMLM_ERR_NO_KERNEL;
+  FusedJobDesc jobs[SMLM_MAX_PROJ];
+  for (int j = 0; j < nproj; ++j) {
+    const smlm_b200_proj& p = projs[j];
+    if (p.y == nullptr || p.x == nullptr || p.v == nullptr || p.wa_table == nullptr || p.wb_table == nullptr)
+      return SMLM_ERR_INVALID_ARGUMENT;
+    if (!aligned16(p.y) || !aligned16(p.x) || !aligned16(p.v)) return SMLM_ERR_MISALIGNED;
+    if (!large_dim_ok(p.h_in) || !large_dim_ok(p.h_out)) return SMLM_ERR_NO_KERNEL;
+    jobs[j] = {p.y, p.v, p.x, p.wa_table, p.wb_table, p.h_in, p.h_out, accumulate};
+  }
+  // the longest jobs first, so that the launch ends on its shortest CTAs
+  std::stable_sort(jobs, jobs + nproj, [](const FusedJobDesc& a, const FusedJobDesc& b) {
+    return static_cast<long long>(a.K1) + a.N2 > static_cast<long long>(b.K1) + b.N2;
+  });
+  return run_fused(jobs, nproj, seg_ids, seg_scale, plan, n_table, T, nseg, rank, dtype, is_row_major, 0,
+                   independent != 0, kFusedBoth, grouped, static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_bwd_dx_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_ids, const float* part_scale,
+                           void* plan, int n_table, int T, int npart, int rank, int dtype, int is_row_major,
+                           int independent, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0 || !projs_ok(projs, nproj)) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (T == 0 || npart == 0) return SMLM_OK;
+  if (plan == nullptr || !aligned16(plan)) return plan == nullptr ? SMLM_ERR_INVALID_ARGUMENT : SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank)) return SMLM_ERR_NO_KERNEL;
+  FusedJobDesc jobs[SMLM_MAX_PROJ];
+  for (int j = 0; j < nproj; ++j) {
+    const smlm_b200_proj& p = projs[j];
+    if (p.dx == nullptr || p.dv == nullptr || p.go == nullptr || p.wa_table == nullptr || p.wb_table == nullptr)
+      return SMLM_ERR_INVALID_ARGUMENT;
+    if (!aligned16(p.dx) || !aligned16(p.dv) || !aligned16(p.go)) return SMLM_ERR_MISALIGNED;
+    if (!large_dim_ok(p.h_in) || !large_dim_ok(p.h_out)) return SMLM_ERR_NO_KERNEL;
+    jobs[j] = {p.dx, p.dv, p.go, p.wb_table, p.wa_table, p.h_out, p.h_in, 0};
+  }
+  std::stable_sort(jobs, jobs + nproj, [](const FusedJobDesc& a, const FusedJobDesc& b) {
+    return static_cast<long long>(a.K1) + a.N2 > static_cast<long long>(b.K1) + b.N2;
+  });
+  // the layout flag flips for both products of the backward, as in smlm_b200_bwd_dx
+  return run_fused(jobs, nproj, part_ids, part_scale, plan, n_table, T, npart, rank, dtype, !is_row_major, 1,
+                   independent != 0, kFusedBoth, 0, static_cast<cudaStream_t>(stream));
+}
+
+size_t smlm_b200_wgrad_multi_workspace_bytes(const smlm_b200_proj* projs, int nproj, int T, int npart, int rank) {
+  if (T < 0 || npart < 0 || rank <= 0 || !projs_ok(projs, nproj)) return 0;
+  int hs[2 * SMLM_MAX_PROJ];
+  for (int j = 0; j < nproj; ++j) {
+    hs[2 * j] = projs[j].h_out;
+    hs[2 * j + 1] = projs[j].h_in;
+  }
+  return wgrad_workspace_need(T, npart, rank, hs, 2 * nproj);
+}
+
+int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_indptr,
+                               const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
+                               size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
+                               int is_row_major, int accumulate, int grad_fp32, int independent, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0 || !projs_ok(projs, nproj)) return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (npart == 0 || T == 0) return SMLM_OK;
+  if (part_indptr == nullptr || plan == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
+  if (!small_dim_ok(rank)) return SMLM_ERR_NO_KERNEL;
+  WgradJobDesc jobs[2 * SMLM_MAX_PROJ];
+  for (int j = 0; j < nproj; ++j) {
+    const smlm_b200_proj& p = projs[j];
+    if (p.dA_table == nullptr || p.dB_table == nullptr || p.dv == nullptr || p.x == nullptr || p.v == nullptr ||
+        p.go == nullptr)
+      return SMLM_ERR_INVALID_ARGUMENT;
+    if (!aligned16(p.dv) || !aligned16(p.x) || !aligned16(p.v) || !aligned16(p.go)) return SMLM_ERR_MISALIGNED;
+    if (!large_dim_ok(p.h_in) || !large_dim_ok(p.h_out)) return SMLM_ERR_NO_KERNEL;
+    jobs[2 * j] = {p.dB_table, p.v, p.go, p.h_out, is_row_major ? 0 : 1, part_scale != nullptr};
+    jobs[2 * j + 1] = {p.dA_table, p.dv, p.x, p.h_in, is_row_major ? 1 : 0, 0};
+  }
+  return run_wgrad(jobs, 2 * nproj, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes,
+                   npart, T, rank, dtype, accumulate, grad_fp32, independent != 0, wgrad_uses_tensor_cores(rank),
+                   static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_rms_norm(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,

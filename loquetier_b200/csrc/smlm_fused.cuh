@@ -35,9 +35,17 @@
 //   shared memory in a fixed order (deterministic; no global scratch, no atomics);
 //   every CTA ends up with the whole MID tile.
 // Phase 3 - the HBM-bound write.  Every CTA expands MID against its slice of the N2
-//   columns, one slab at a time (W2 slab double-buffered with 16-byte cp.async), and
-//   each warp hands finished 16 x 128 blocks to TMA as tensor stores - or tensor
-//   reduce-adds when accumulating into OUT.
+//   columns, one slab at a time (W2 slab double-buffered with 16-byte cp.async).  A warp
+//   owns 64-column groups of the slab and walks down the piece's row blocks with the W2
+//   fragments of its group held in registers (ranks up to 32), so a 16 x 64 block costs
+//   eight MMAs, the conversion and four stmatrix; the blocks go to TMA as tensor stores -
+//   or tensor reduce-adds when accumulating into OUT.  A scale that is a power of two is
+//   folded into the MID operand (exact), which removes the multiply from this phase.
+//
+// One launch can serve several jobs - the same segment plan, adapter ids, rank and scale
+// applied to different tensors, e.g. the q/k/v or gate/up projections of one layer, or all
+// LoRA targets of a benchmark step: the grid is the jobs' grids laid end to end, so that
+// short launches do not each pay their own set-up and drain.
 #pragma once
 #include <cooperative_groups.h>
 #include <cuda.h>
@@ -98,30 +106,45 @@ struct FusedSmem {
   static constexpr int kRed = kFusedConsumers * 16 * KP * 4;   // one 16 x KP fp32 block per consumer warp
   static constexpr int kMidOff = kRedOff + kRed;
   static constexpr int kMid = kBM * KP * 2;
-  static constexpr int kBarOff = kMidOff + kMid;
+  static constexpr int kRowOff = kMidOff + kMid;                  // int[kBM]: token rows of a gather piece
+  static constexpr int kBarOff = kRowOff + kBM * 4;
   static constexpr int kTotal = kBarOff + 2 * kStages * 8 + 1024;  // + alignment slack
   static_assert(kTotal <= (fused_ctas_per_sm(R16) == 2 ? 113 : 227) * 1024, "shared memory budget");
   static_assert(kW2Slab % 1024 == 0 && kStage % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
-struct FusedArgs {
+constexpr int kFusedMaxJobs = 8;   // jobs one launch can serve
+
+// What differs between the jobs of one launch: the tensors and the two large dimensions.
+struct FusedJob {
   const void* in;               // [T, K1] (gather pieces read it through this pointer, the others through TMA)
   void* out;                    // [T, N2]
   void* mid;                    // [T, R]
   const void* const* w1_table;  // shrink panels
   const void* const* w2_table;  // expand panels
+  int K1, N2;
+  int accumulate;               // OUT += instead of OUT =
+  int pad_;
+};
+
+struct FusedArgs {
+  FusedJob job[kFusedMaxJobs];
   const int32_t* ids;           // per-segment adapter index, or null: tables are per segment
   const float* scale;           // per adapter (ids != null) or per segment, or null
   int* plan;
   int n_table;
-  int K1, R, N2;
+  int R;
   int ksplit;
+  int ctas_per_job;             // CTAs of the grid per job (plan capacity x ksplit)
   int scale_mid;                // 1: the scale multiplies MID (backward); 0: it multiplies OUT (forward)
-  int accumulate;               // OUT += instead of OUT =
-  int independent;              // 1: reads nothing the previous kernel of the stream wrote
+  int independent;              // 1: see smlm_b200_fwd in include/smlm_b200.h
   int mode;                     // kFusedBoth, or one half only (one reference operator call):
                                 // kFusedShrinkOnly: MID = s * IN . W1, nothing else;
                                 // kFusedExpandOnly: OUT (+)= s * MID . W2 with MID read, not written
+};
+
+struct FusedMapsN {
+  FusedMaps m[kFusedMaxJobs];
 };
 
 constexpr int kFusedBoth = 0;
@@ -139,8 +162,8 @@ __device__ __forceinline__ void cluster_wait() {
 }
 
 template <typename T, int R16, bool RM, bool GATHER>
-__global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_kernel(const FusedArgs a,
-                                                                const __grid_constant__ FusedMaps tm) {
+__global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_kernel(
+    const __grid_constant__ FusedArgs a, const __grid_constant__ FusedMapsN tmn) {
   extern __shared__ unsigned char smem_raw[];
   using SM = FusedSmem<R16, RM>;
   constexpr int NT = SM::NT;
@@ -156,8 +179,13 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int KS = a.ksplit;
-  const int piece_idx = blockIdx.x / KS;
-  const int z = blockIdx.x - piece_idx * KS;
+  // the grid is the jobs' grids laid end to end; a cluster never straddles two jobs
+  const int jidx = blockIdx.x / a.ctas_per_job;
+  const int local = blockIdx.x - jidx * a.ctas_per_job;
+  const int piece_idx = local / KS;
+  const int z = local - piece_idx * KS;
+  const FusedJob& jb = a.job[jidx];
+  const FusedMaps& tm = tmn.m[jidx];
 
   // A launch that depends on its predecessor waits for it here.  An independent one starts at
   // once - it overlaps its read phase with the predecessor's write phase - and waits just before
@@ -171,7 +199,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
     return;
   }
   const int nrows = pc.nrows;
-  const int K1 = a.K1, R = a.R, N2 = a.N2;
+  const int K1 = jb.K1, R = a.R, N2 = jb.N2;
   int* err = a.plan + 1;
   // GATHER is a compile-time switch because the extra paths cost the ordinary launch about 3 %: only
   // launches whose caller announces a grouped plan run the instantiation that knows gather pieces
@@ -190,18 +218,26 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const T* w2 = nullptr;
   float sc = 1.0f;
   if (!gather) {
-    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
-    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
+    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(jb.w1_table, a.ids, a.n_table, pc.seg, err));
+    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(jb.w2_table, a.ids, a.n_table, pc.seg, err));
     sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
   } else if (a.ids != nullptr && pc.seg >= 0 && pc.seg < a.n_table) {
-    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(a.w1_table, nullptr, a.n_table, pc.seg, err));
-    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(a.w2_table, nullptr, a.n_table, pc.seg, err));
+    if (mode != kFusedExpandOnly) w1 = static_cast<const T*>(adapter_ptr(jb.w1_table, nullptr, a.n_table, pc.seg, err));
+    if (mode != kFusedShrinkOnly) w2 = static_cast<const T*>(adapter_ptr(jb.w2_table, nullptr, a.n_table, pc.seg, err));
     sc = a.scale != nullptr ? a.scale[pc.seg] : 1.0f;
   }
   const bool w_ok = (w1 != nullptr || mode == kFusedExpandOnly) && (w2 != nullptr || mode == kFusedShrinkOnly) &&
                     !(gather && a.ids == nullptr);
   const float sc_mid = (a.scale_mid || mode == kFusedShrinkOnly) ? sc : 1.0f;
   const float sc_out = (a.scale_mid || mode == kFusedShrinkOnly) ? 1.0f : sc;
+  // A scale of 2, 4, ... 256 multiplies the MID operand of the second product instead of every output
+  // element: scaling by a power of two is exact in the storage type (bf16 has the exponent range of
+  // fp32, so nothing overflows that would not overflow in OUT as well; fp16 could, and is left alone),
+  // hence the result is bit-identical and the write phase saves one multiply per element.  MID as
+  // written to global memory never carries this factor.
+  const bool fold = std::is_same<T, __nv_bfloat16>::value && sc_out >= 2.0f && sc_out <= 256.0f &&
+                    (__float_as_uint(sc_out) & 0x007fffffu) == 0u;
+  const float sc_w = fold ? 1.0f : sc_out;
 
   const int ksteps = (K1 + KC - 1) / KC;
   const int per = (ksteps + KS - 1) / KS;
@@ -225,6 +261,9 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
     }
     fence_mbar_init();
   }
+  // token rows of the piece, looked up once (a gather piece's rows come from the plan's row index)
+  int* const rowsm = reinterpret_cast<int*>(smem + SM::kRowOff);
+  if (tid < kBM) rowsm[tid] = gather ? (tid < nrows ? rowidx[tid] : 0) : pc.row0 + tid;
   if (gather && (K1 & 15) != 0 && tid < nrows) {
     // the last 16-column step of a row reaches 8 columns past K1, which a bulk copy does not fill:
     // clear them in every stage (W1 holds zeros there, but zero times a non-finite leftover is not zero)
@@ -290,7 +329,7 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
         }
       } else {
         // one bulk copy per row: its kcols columns of this K step, into rows XPad bytes apart
-        const T* in = static_cast<const T*>(a.in);
+        const T* in = static_cast<const T*>(jb.in);
         for (int r = lane; r < nrows; r += 32)
           bulk_load(xs + r * SM::XPad, in + static_cast<size_t>(rowidx[r]) * K1 + k0, kcols * 2, fb);
       }
@@ -365,14 +404,14 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const uint32_t mids = base + SM::kMidOff;  // MID tile [64][KP] in the storage type, swizzled rows
   {
     const int load_rows = min(kBM, ((nrows + 15) >> 4) << 4);
-    T* const mbase = static_cast<T*>(a.mid);
+    T* const mbase = static_cast<T*>(jb.mid);
     constexpr int HP = KP / 2;
     for (int e = tid; e < load_rows * HP; e += kFusedThreads) {
       const int r = e / HP;
       const int n = (e - r * HP) * 2;
       const int fm = r >> 4, r16 = r & 15;
       const bool inside = r < nrows && n < R && w_ok;
-      T* mrow = inside ? mbase + static_cast<size_t>(gather ? rowidx[r] : pc.row0 + r) * R + n : mbase;
+      T* mrow = inside ? mbase + static_cast<size_t>(rowsm[r]) * R + n : mbase;
       uint32_t packed = 0;
       if (mode == kFusedExpandOnly) {
         if (inside) packed = *reinterpret_cast<const uint32_t*>(mrow);
@@ -390,6 +429,10 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
         }
         packed = pack2<T>(s.x * sc_mid, s.y * sc_mid);
         if (z == 0 && inside) *reinterpret_cast<uint32_t*>(mrow) = packed;
+      }
+      if (fold) {
+        const float2 f = unpack2<T>(packed);
+        packed = pack2<T>(f.x * sc_out, f.y * sc_out);
       }
       const int c = n >> 3;
       asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(mids + r * (XC * 16) + (swz<XC>(r, c) << 4) + (n & 7) * 2),
@@ -444,35 +487,25 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
     load_slab(0, slab_of(0));
     cp_async_commit();
 
-    const int WN = WK;
-    const int wn = wk;
-    const bool has_rows = (wm * 16 < nrows);
-    uint32_t af[R16][4];
-    if (has_rows) {
+    // A warp owns 64-column groups of the slab (group = warp, warp + 8, ...) and walks down the
+    // piece's row blocks of 16.  Up to rank 32 the W2 fragments of a group are fetched once and
+    // serve all row blocks.
+    constexpr bool kHold = R16 <= 2;
+    const int nblk = (nrows + 15) >> 4;
+    auto load_a = [&](uint32_t (&dst)[R16][4], int rb) {
 #pragma unroll
       for (int kk = 0; kk < R16; ++kk) {
         const int m = lane >> 3;
-        const int r = wm * 16 + (m & 1) * 8 + (lane & 7);
+        const int r = rb * 16 + (m & 1) * 8 + (lane & 7);
         const int c = kk * 2 + (m >> 1);
-        ldsm_x4(af[kk], mids + r * (XC * 16) + (swz<XC>(r, c) << 4));
+        ldsm_x4(dst[kk], mids + r * (XC * 16) + (swz<XC>(r, c) << 4));
       }
-    }
-    const int rows_here = min(16, nrows - wm * 16);
-    const bool full_block = !gather && ((rows_here == 16) || (rows_here == 8));
-    const CUtensorMap* omap = rows_here == 8 ? &tm.out8 : &tm.out;
+    };
+    // per warp four staging blocks of 16 x 64 (2 KB): the tensor stores in flight
     const uint32_t ostage = base + SM::kOutOff + warp * 8192;
-    // rows a lane writes in the plain-store path (row q * 4 + lane / 8 of the warp's block), as element
-    // offsets into OUT; a gather piece looks its rows up once, here
-    size_t orow_off[4];
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const int r = q * 4 + (lane >> 3);
-      int orow = pc.row0 + wm * 16 + r;
-      if (gather && r < rows_here) orow = rowidx[wm * 16 + r];
-      orow_off[q] = static_cast<size_t>(orow) * N2;
-    }
-    T* const obase = static_cast<T*>(a.out);
-    int obuf = 0;
+    T* const obase = static_cast<T*>(jb.out);
+    const int accumulate = jb.accumulate;
+    int oslot = 0;
 
     for (int si = 0; si < ns; ++si) {
       const int slab = slab_of(si);
@@ -484,91 +517,101 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       named_bar_sync(1, kFusedCThreads);  // slab si has landed for all consumer warps
       const uint32_t ws = wslab0 + (si & 1) * SM::kW2Slab;
       const int ngroups = (ncols + 63) >> 6;
-      if (has_rows) {
-        // two groups of 64 columns per iteration: one 16 x 128 block per TMA batch
-        for (int g0 = wn * 2; g0 < ngroups; g0 += WN * 2) {
-          const int ng = min(2, ngroups - g0);
-          if (lane == 0) bulk_wait_read<1>();  // the staging block about to be reused has been read
-          __syncwarp();
-          const uint32_t os = ostage + obuf * 4096;
+      for (int grp = warp; grp < ngroups; grp += NW) {
+        // W2 fragments of this group: bfr[kk][jj] covers n-tiles 2jj, 2jj+1 at k step kk
+        auto load_b = [&](uint32_t (&dst)[4], int kk, int jj) {
+          const int m = lane >> 3;
+          if constexpr (!RM) {
+            const int n = grp * 64 + (2 * jj + (m >> 1)) * 8 + (lane & 7);
+            const int c = kk * 2 + (m & 1);
+            ldsm_x4(dst, ws + n * (XC * 16) + (swz<XC>(n, c) << 4));
+          } else {
+            const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
+            const int c = grp * 8 + 2 * jj + (m >> 1);
+            ldsm_x4_t(dst, ws + k * (SLAB * 2) + (((c & ~7) | ((c ^ k) & 7)) << 4));
+          }
+        };
+        uint32_t bfr[kHold ? R16 : 1][4][4];
+        if constexpr (kHold) {
 #pragma unroll
-          for (int gi = 0; gi < 2; ++gi) {
-            if (gi < ng) {
-              const int grp = g0 + gi;
-              float o[8][4];
+          for (int kk = 0; kk < R16; ++kk)
 #pragma unroll
-              for (int j = 0; j < 8; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+            for (int jj = 0; jj < 4; ++jj) load_b(bfr[kk][jj], kk, jj);
+        }
 #pragma unroll
-              for (int kk = 0; kk < R16; ++kk) {
+        for (int rb = 0; rb < 4; ++rb) {
+          if (rb >= nblk) break;
+          float o[8][4];
+          uint32_t af[R16][4];   // the row block's MID fragments: one ldmatrix per k step and 16 x 64 block
+          load_a(af, rb);
 #pragma unroll
-                for (int j = 0; j < 8; j += 2) {
-                  uint32_t bf[4];
-                  const int m = lane >> 3;
-                  if constexpr (!RM) {
-                    const int n = grp * 64 + (j + (m >> 1)) * 8 + (lane & 7);
-                    const int c = kk * 2 + (m & 1);
-                    ldsm_x4(bf, ws + n * (XC * 16) + (swz<XC>(n, c) << 4));
-                  } else {
-                    const int k = kk * 16 + (m & 1) * 8 + (lane & 7);
-                    const int c = grp * 8 + j + (m >> 1);
-                    ldsm_x4_t(bf, ws + k * (SLAB * 2) + (((c & ~7) | ((c ^ k) & 7)) << 4));
-                  }
-                  mma16816<T>(o[j], af[kk], bf[0], bf[1]);
-                  mma16816<T>(o[j + 1], af[kk], bf[2], bf[3]);
-                }
-              }
+          for (int kk = 0; kk < R16; ++kk)
 #pragma unroll
-              for (int j = 0; j < 8; j += 2) {
-                const int m = lane >> 3;
-                const int r = (m & 1) * 8 + (lane & 7);
-                const int c = j + (m >> 1);
-                stsm_x4(os + gi * 2048 + r * 128 + ((c ^ (r & 7)) << 4),
-                        pack2<T>(o[j][0] * sc_out, o[j][1] * sc_out), pack2<T>(o[j][2] * sc_out, o[j][3] * sc_out),
-                        pack2<T>(o[j + 1][0] * sc_out, o[j + 1][1] * sc_out),
-                        pack2<T>(o[j + 1][2] * sc_out, o[j + 1][3] * sc_out));
+            for (int jj = 0; jj < 4; ++jj) {
+              if constexpr (!kHold) load_b(bfr[0][jj], kk, jj);
+              const uint32_t (&b4)[4] = bfr[kHold ? kk : 0][jj];
+              if (kk == 0) {
+                mma16816_z<T>(o[2 * jj], af[kk], b4[0], b4[1]);
+                mma16816_z<T>(o[2 * jj + 1], af[kk], b4[2], b4[3]);
+              } else {
+                mma16816<T>(o[2 * jj], af[kk], b4[0], b4[1]);
+                mma16816<T>(o[2 * jj + 1], af[kk], b4[2], b4[3]);
               }
             }
+          if (sc_w != 1.0f) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              o[j][0] *= sc_w; o[j][1] *= sc_w; o[j][2] *= sc_w; o[j][3] *= sc_w;
+            }
           }
-          if (full_block) {
+          if (lane == 0) bulk_wait_read<3>();  // the staging block about to be reused has been read
+          __syncwarp();
+          const uint32_t os = ostage + oslot * 2048;
+#pragma unroll
+          for (int j = 0; j < 8; j += 2) {
+            const int m = lane >> 3;
+            const int r = (m & 1) * 8 + (lane & 7);
+            const int c = j + (m >> 1);
+            stsm_x4(os + r * 128 + ((c ^ (r & 7)) << 4), pack2<T>(o[j][0], o[j][1]), pack2<T>(o[j][2], o[j][3]),
+                    pack2<T>(o[j + 1][0], o[j + 1][1]), pack2<T>(o[j + 1][2], o[j + 1][3]));
+          }
+          const int rows_here = min(16, nrows - rb * 16);
+          if (!gather && (rows_here == 16 || rows_here == 8)) {
             fence_proxy_async();
             __syncwarp();
             if (lane == 0) {
-              for (int gi = 0; gi < ng; ++gi) {
-                const int col0 = n0 + (g0 + gi) * 64;
-                if (a.accumulate) tma_reduce_add_2d<T>(omap, col0, pc.row0 + wm * 16, os + gi * 2048);
-                else tma_store_2d(omap, col0, pc.row0 + wm * 16, os + gi * 2048);
-              }
+              const CUtensorMap* omap = rows_here == 8 ? &tm.out8 : &tm.out;
+              if (accumulate) tma_reduce_add_2d<T>(omap, n0 + grp * 64, pc.row0 + rb * 16, os);
+              else tma_store_2d(omap, n0 + grp * 64, pc.row0 + rb * 16, os);
               bulk_commit();
             }
-            obuf ^= 1;
+            oslot = (oslot + 1) & 3;
           } else {
-            // ragged tail of the piece: plain 16-byte stores of the rows that exist
+            // ragged tail of the piece, or a gather piece: plain 16-byte stores of the rows that exist
             __syncwarp();
-            for (int gi = 0; gi < ng; ++gi) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const int i = q * 32 + lane;
-                const int r = i >> 3, c = i & 7;
-                const int col = (g0 + gi) * 64 + c * 8;
-                if (r < rows_here && col < ncols) {
-                  uint4 v;
-                  asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
-                               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                               : "r"(os + gi * 2048 + r * 128 + ((c ^ (r & 7)) << 4)));
-                  uint4* dst = reinterpret_cast<uint4*>(obase + orow_off[q] + n0 + col);
-                  if (a.accumulate) {
-                    const uint4 old = *dst;
-                    const uint32_t* ov = reinterpret_cast<const uint32_t*>(&old);
-                    uint32_t* nv = reinterpret_cast<uint32_t*>(&v);
+            for (int q = 0; q < 4; ++q) {
+              const int i = q * 32 + lane;
+              const int r = i >> 3, c = i & 7;
+              const int col = grp * 64 + c * 8;
+              if (r < rows_here && col < ncols) {
+                uint4 v;
+                asm volatile("ld.shared.v4.b32 {%0,%1,%2,%3}, [%4];\n"
+                             : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                             : "r"(os + r * 128 + ((c ^ (r & 7)) << 4)));
+                uint4* dst = reinterpret_cast<uint4*>(obase + static_cast<size_t>(rowsm[rb * 16 + r]) * N2 + n0 + col);
+                if (accumulate) {
+                  const uint4 old = *dst;
+                  const uint32_t* ov = reinterpret_cast<const uint32_t*>(&old);
+                  uint32_t* nv = reinterpret_cast<uint32_t*>(&v);
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                      const float2 p = unpack2<T>(ov[e]);
-                      const float2 n2 = unpack2<T>(nv[e]);
-                      nv[e] = pack2<T>(p.x + n2.x, p.y + n2.y);
-                    }
+                  for (int e = 0; e < 4; ++e) {
+                    const float2 p = unpack2<T>(ov[e]);
+                    const float2 n2 = unpack2<T>(nv[e]);
+                    nv[e] = pack2<T>(p.x + n2.x, p.y + n2.y);
                   }
-                  *dst = v;
                 }
+                *dst = v;
               }
             }
             __syncwarp();

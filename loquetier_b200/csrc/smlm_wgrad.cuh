@@ -59,17 +59,21 @@ struct WgradSmem {
   static constexpr int kPartialFloats = KP * SLAB;             // one CTA's partial sums for one run
 };
 
+constexpr int kWgMaxJobs = 16;             // jobs one launch can serve (dB and dA of eight projections)
+
 struct WgradJob {
   void* const* g_table;   // device array of npart output pointers
   const void* p;          // [T, R]
   int H;
   int transposed;         // 0: G is [R, H]; 1: G is [H, R]
   int use_scale;
-  int slabs;              // ceil(H / SLAB)
+  int slab_begin;         // first slab of this job among the slabs of the launch (grid.y)
 };
 
 struct WgradArgs {
-  WgradJob job[2];
+  WgradJob job[kWgMaxJobs];
+  int njobs;
+  int slabs_total;             // slabs of all jobs = grid.y
   const int32_t* part_indptr;  // [npart + 1]
   const float* scale;          // per partition (ids == null) or per adapter, or null
   const int32_t* ids;          // per-partition adapter index for `scale`, or null
@@ -87,11 +91,12 @@ struct WgradArgs {
 };
 
 struct WgradMaps {
-  CUtensorMap q[2];  // Q of job 0 / job 1: boxes of 16 tokens x 64 columns
+  CUtensorMap q[kWgMaxJobs];  // Q of every job: boxes of 16 tokens x 64 columns
 };
 
 template <typename T, int RT>
-__global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, const __grid_constant__ WgradMaps tm) {
+__global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant__ WgradArgs a,
+                                                           const __grid_constant__ WgradMaps tm) {
   extern __shared__ unsigned char smem_raw[];
   using SM = WgradSmem<RT>;
   constexpr int CW = SM::CW;
@@ -104,16 +109,18 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
   const int warp = tid >> 5;
   const int G = a.group;
   const int grp = blockIdx.x;
-  const int slabs_total = a.job[0].slabs + a.job[1].slabs;
+  const int slabs_total = a.slabs_total;
   const int slab_global = blockIdx.y;
-  const int ji = slab_global >= a.job[0].slabs ? 1 : 0;
-  // field-by-field selection keeps the job descriptor in parameter space
-  void* const* g_table = ji ? a.job[1].g_table : a.job[0].g_table;
-  const T* P = static_cast<const T*>(ji ? a.job[1].p : a.job[0].p);
-  const int H = ji ? a.job[1].H : a.job[0].H;
-  const int transposed = ji ? a.job[1].transposed : a.job[0].transposed;
-  const int use_scale = ji ? a.job[1].use_scale : a.job[0].use_scale;
-  const int col0 = (slab_global - (ji ? a.job[0].slabs : 0)) * SLAB;
+  int ji = 0;
+  for (int j = 1; j < a.njobs; ++j)
+    if (slab_global >= a.job[j].slab_begin) ji = j;
+  const WgradJob& jb = a.job[ji];
+  void* const* g_table = jb.g_table;
+  const T* P = static_cast<const T*>(jb.p);
+  const int H = jb.H;
+  const int transposed = jb.transposed;
+  const int use_scale = jb.use_scale;
+  const int col0 = (slab_global - jb.slab_begin) * SLAB;
   const int R = a.R;
   const int ncols = min(SLAB, H - col0);
   int* err = a.plan + 1;
@@ -366,11 +373,11 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
           const int t = kk * 16 + (m >> 1) * 8 + (lane & 7);
           ldsm_x4_t(af[i], ps + t * (R * 2) + ((i * 2 + (m & 1)) << 4));
         }
+        // registers 0,1 hold tokens 2t, 2t+1; registers 2,3 hold tokens 2t+8, 2t+9 (in both operands)
+        const int tk = (lane & 3) * 2;
+        const uint32_t lo = (tk < valid ? 0x0000ffffu : 0u) | (tk + 1 < valid ? 0xffff0000u : 0u);
+        const uint32_t hi = (tk + 8 < valid ? 0x0000ffffu : 0u) | (tk + 9 < valid ? 0xffff0000u : 0u);
         if (valid < 16) {
-          // registers 0,1 hold tokens 2t, 2t+1; registers 2,3 hold tokens 2t+8, 2t+9
-          const int tk = (lane & 3) * 2;
-          const uint32_t lo = (tk < valid ? 0x0000ffffu : 0u) | (tk + 1 < valid ? 0xffff0000u : 0u);
-          const uint32_t hi = (tk + 8 < valid ? 0x0000ffffu : 0u) | (tk + 9 < valid ? 0xffff0000u : 0u);
 #pragma unroll
           for (int i = 0; i < RT; ++i) {
             af[i][0] &= lo;
@@ -386,6 +393,14 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const WgradArgs a, co
           const int t = (m & 1) * 8 + (lane & 7);
           const int c = c0 + j + (m >> 1);
           ldsm_x4_t(bf, qs + (kk * NCH + ch) * 2048 + t * 128 + ((c ^ (t & 7)) << 4));
+          if (valid < 16) {
+            // the Q rows past the piece's end belong to the next partition (or to rows that are not
+            // fine-tuned at all): a non-finite value there must not meet the zeroed P (0 x Inf = NaN)
+            bf[0] &= lo;
+            bf[1] &= hi;
+            bf[2] &= lo;
+            bf[3] &= hi;
+          }
 #pragma unroll
           for (int i = 0; i < RT; ++i) {
             mma16816<T>(acc[i][j], af[i], bf[0], bf[1]);

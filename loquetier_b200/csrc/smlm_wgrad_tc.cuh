@@ -50,12 +50,12 @@ struct WgradTcSmem {
 };
 
 struct WgradTcMaps {
-  CUtensorMap q[2];  // Q of job 0 / job 1: boxes of 16 tokens x 64 columns
-  CUtensorMap p[2];  // P of job 0 / job 1: the same boxes over [T, R]
+  CUtensorMap q[kWgMaxJobs];  // Q of every job: boxes of 16 tokens x 64 columns
+  CUtensorMap p[kWgMaxJobs];  // P of every job: the same boxes over [T, R]
 };
 
 template <typename T, int RT>
-__global__ void __launch_bounds__(kWgTcThreads, 1) wgrad_tc_kernel(const WgradArgs a,
+__global__ void __launch_bounds__(kWgTcThreads, 1) wgrad_tc_kernel(const __grid_constant__ WgradArgs a,
                                                                    const __grid_constant__ WgradTcMaps tm) {
   extern __shared__ unsigned char smem_raw[];
   using SM = WgradTcSmem<RT>;
@@ -66,14 +66,17 @@ __global__ void __launch_bounds__(kWgTcThreads, 1) wgrad_tc_kernel(const WgradAr
   const int warp = tid >> 5;
   const int G = a.group;
   const int grp = blockIdx.x;
-  const int slabs_total = a.job[0].slabs + a.job[1].slabs;
+  const int slabs_total = a.slabs_total;
   const int slab_global = blockIdx.y;
-  const int ji = slab_global >= a.job[0].slabs ? 1 : 0;
-  void* const* g_table = ji ? a.job[1].g_table : a.job[0].g_table;
-  const int H = ji ? a.job[1].H : a.job[0].H;
-  const int transposed = ji ? a.job[1].transposed : a.job[0].transposed;
-  const int use_scale = ji ? a.job[1].use_scale : a.job[0].use_scale;
-  const int col0 = (slab_global - (ji ? a.job[0].slabs : 0)) * SLAB;
+  int ji = 0;
+  for (int j = 1; j < a.njobs; ++j)
+    if (slab_global >= a.job[j].slab_begin) ji = j;
+  const WgradJob& jb = a.job[ji];
+  void* const* g_table = jb.g_table;
+  const int H = jb.H;
+  const int transposed = jb.transposed;
+  const int use_scale = jb.use_scale;
+  const int col0 = (slab_global - jb.slab_begin) * SLAB;
   const int R = a.R;
   const int ncols = min(SLAB, H - col0);
   int* err = a.plan + 1;
@@ -187,11 +190,19 @@ __global__ void __launch_bounds__(kWgTcThreads, 1) wgrad_tc_kernel(const WgradAr
       const int ntok = pcs[it].nrows;
       const int kmax = (ntok + 15) >> 4;
       if (ntok & 15) {
-        // the last 16-token step reaches past the piece: those rows of P must not contribute
+        // the last 16-token step reaches past the piece: those rows of P must not contribute, and the
+        // same rows of Q - tokens of the next partition, or of rows that are not fine-tuned - are
+        // cleared too, so that a non-finite value there never meets the zeroed P (0 x Inf = NaN).
+        // A row is 128 bytes in every block, so clearing whole rows is independent of the swizzle.
         const int nz = kmax * 16 - ntok;
         for (int i = lane; i < NB * nz * 8; i += 32) {
           const int c = i & 7, r = ntok + (i >> 3) % nz, nb = i / (8 * nz);
           asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(ps + nb * 8192 + r * 128 + (c << 4)), "r"(0)
+                       : "memory");
+        }
+        for (int i = lane; i < nch * nz * 8; i += 32) {
+          const int c = i & 7, r = ntok + (i >> 3) % nz, qb = i / (8 * nz);
+          asm volatile("st.shared.v4.b32 [%0], {%1,%1,%1,%1};\n" ::"r"(qs + qb * 8192 + r * 128 + (c << 4)), "r"(0)
                        : "memory");
         }
         fence_proxy_async();

@@ -72,12 +72,16 @@ class add_lora(Function):
     train_partition, *trainable)`` with ``trainable`` = (A_0, B_0, A_1, B_1, ...),
     one pair per train partition, in the PEFT layout."""
 
-    # set by callers that already planned the batch (the LoRA linear does, once per
-    # step); consumed by the next forward whose ``s`` is the very same tensor
+    # Set by a caller that has already planned the batch and consumed by the next forward whose ``s`` is
+    # the very same tensor object.  The plan describes the CONTENTS of ``s`` at the time it was built:
+    # a caller that rewrites ``s`` in place must drop the shared plan (set it to None) or build a new one.
     _shared_plan: Optional[ops.Plan] = None
 
     @staticmethod
-    def forward(y_shape, x, wa_ptr, wb_ptr, s, lora_rank, train_len, train_partition, *args):
+    def forward(ctx: FunctionCtx, y_shape, x, wa_ptr, wb_ptr, s, lora_rank, train_len, train_partition, *args):
+        # The reference splits this into forward + setup_context (kernel_utils.py:102-127); the combined
+        # form is used here because the backward needs ``v``, which is not an output: it goes straight
+        # into ``ctx`` instead of through any state shared between calls or threads.
         y = torch.empty(y_shape, dtype=x.dtype, device=x.device)
         v = torch.empty((x.size(0), lora_rank), dtype=x.dtype, device=x.device)
         plan = add_lora._shared_plan
@@ -85,18 +89,11 @@ class add_lora(Function):
             plan = ops.Plan(s, x.size(0))
         if x.size(0) > 0 and s.numel() > 1:
             ops.fwd(y, x, v, wa_ptr, wb_ptr, plan, lora_rank, is_row_major=False)
-        add_lora._last_v = v
+        ctx.tp = train_partition
+        ctx.rank = lora_rank
+        tl = int(train_len)
+        ctx.save_for_backward(x[:tl, ...], v[:tl, ...], *args)
         return y
-
-    @staticmethod
-    def setup_context(ctx: FunctionCtx, inputs: Tuple, output: torch.Tensor):
-        _, x, _, _, _, rank, tl, tp, *weight_list = inputs
-        ctx.tp = tp
-        ctx.rank = rank
-        tl = int(tl)
-        v = add_lora._last_v
-        add_lora._last_v = None
-        ctx.save_for_backward(x[:tl, ...], v[:tl, ...], *weight_list)
 
     @staticmethod
     def backward(ctx: FunctionCtx, grad_output: torch.Tensor):

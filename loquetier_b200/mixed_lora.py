@@ -59,8 +59,11 @@ class MixedLoraContext:
             seg = self._segment.to(device=device, dtype=torch.int32).contiguous()
             seg_ids = torch.tensor(list(self._lora_ids), dtype=torch.int32, device=device)
             # grouped plan when it helps: decode tokens of one adapter then share its panels wherever they
-            # sit in the batch
-            lens = [int(b) - int(a) for a, b in zip(self._segment[:-1], self._segment[1:])]
+            # sit in the batch.  The reference keeps `segment` on the device (model_generation.py:279-283):
+            # its lengths come back in ONE copy, outside any stream capture (the state is built on the
+            # first forward after `update`), never element by element.
+            bounds = self._segment.tolist()
+            lens = [b - a for a, b in zip(bounds[:-1], bounds[1:])]
             if wants_grouped_plan(lens, list(self._lora_ids)):
                 plan = ops.Plan(seg, T, seg_ids=seg_ids, n_table=max(self._lora_ids) + 1)
             else:

@@ -99,8 +99,12 @@ def fwd(y, x, v, wa_table, wb_table, plan: Plan, rank: int, is_row_major=False, 
         accumulate=False, independent=False):
     """Fused shrink + expand (+ scale, + accumulate into y); writes v [T, rank].
 
-    ``independent=True`` promises that this call reads nothing the previous kernel on
-    the stream writes; the launch then overlaps with that kernel's write phase."""
+    ``independent=True`` is a promise about every kernel enqueued on the stream since, and including,
+    the most recent launch with ``independent=False``: this call neither reads nor writes anything
+    those kernels write, and writes nothing they read.  The launch then does not wait at its start
+    and may run alongside all of them (its read phase overlaps their write phases); it still
+    completes after them.  A call that consumes the output of an earlier launch must therefore pass
+    ``independent=False`` even when unrelated independent launches sit between the two."""
     with torch.cuda.device(x.device):
         check(lib.smlm_b200_fwd(y.data_ptr(), x.data_ptr(), v.data_ptr(), wa_table.data_ptr(),
                                 wb_table.data_ptr(), _p(seg_ids), _p(seg_scale), plan.buf.data_ptr(),
@@ -153,8 +157,8 @@ def wgrad(g_table, p, q, part_indptr, plan: Plan, transposed: bool, part_scale=N
 def wgrad_pair(dA_table, dB_table, dv, x, v, go, part_indptr, plan: Plan, rank: int, is_row_major=False,
                part_ids=None, part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None,
                independent=False):
-    """dA and dB of every train partition in one launch.  ``independent=True``: reads nothing the
-    previous kernel on the stream writes and does not share ``workspace`` with it."""
+    """dA and dB of every train partition in one launch.  ``independent=True``: the promise of
+    ``fwd``, and in addition the call shares its ``workspace`` with none of those kernels."""
     ws = workspace if workspace is not None else wgrad_workspace(go.device, plan.T, plan.nseg, rank, go.size(1),
                                                                  x.size(1))
     with torch.cuda.device(go.device):
@@ -180,6 +184,93 @@ def bwd(dx, dA_table, dB_table, dv, go, x, v, wa_table, wb_table, plan: Plan, ra
                                 plan.nseg, int(x.size(1)), int(go.size(1)), int(rank), _dtype_code(go),
                                 int(bool(is_row_major)), int(bool(accumulate_grads)), int(bool(grad_fp32)),
                                 _stream(go)), "smlm_b200_bwd")
+
+
+# ---------------------------------------------------------------------------
+# several projections per launch
+# ---------------------------------------------------------------------------
+
+class ProjSet:
+    """Host-side descriptor array (``smlm_b200_proj``) of up to ``cabi.SMLM_MAX_PROJ`` projections that share a
+    batch: the same segment plan, adapter ids, rank and scales, different tensors.  ``projs`` is a list of
+    dicts with the tensors the entry points to be called need: ``x, y, v, wa, wb`` for the forward;
+    ``go, dx, dv, wa, wb`` for dV/dX; ``dv, x, v, go, dA_t, dB_t`` for the weight gradients (``wa``/``wb``/
+    ``dA_t``/``dB_t`` are int64 pointer tables on the device).  The set keeps the tensors alive."""
+
+    def __init__(self, projs):
+        import ctypes
+        n = len(projs)
+        if not 1 <= n <= cabi.SMLM_MAX_PROJ:
+            raise RuntimeError(f"a projection set holds 1..{cabi.SMLM_MAX_PROJ} projections")
+        self.keep = list(projs)
+        self.n = n
+        self.arr = (cabi.SmlmProj * n)()
+        ref = None
+        for i, p in enumerate(projs):
+            d = self.arr[i]
+            for f, k in (("x", "x"), ("y", "y"), ("v", "v"), ("go", "go"), ("dx", "dx"), ("dv", "dv"),
+                         ("wa_table", "wa"), ("wb_table", "wb"), ("dA_table", "dA_t"), ("dB_table", "dB_t")):
+                t = p.get(k)
+                if t is not None:
+                    if not t.is_cuda or not t.is_contiguous():
+                        raise RuntimeError(f"{k} must be a contiguous CUDA tensor")
+                    setattr(d, f, t.data_ptr())
+                    ref = ref if ref is not None else t
+            if "h_in" in p:
+                d.h_in, d.h_out = int(p["h_in"]), int(p["h_out"])
+            else:
+                d.h_in = int((p["x"] if p.get("x") is not None else p["dx"]).size(1))
+                d.h_out = int((p["y"] if p.get("y") is not None else p["go"]).size(1))
+        self.ref = ref
+        self.ptr = ctypes.cast(self.arr, ctypes.c_void_p)
+
+    def _dt(self, key):
+        return _dtype_code(self.keep[0][key])
+
+
+def fwd_multi(ps: ProjSet, plan: Plan, rank: int, is_row_major=False, seg_ids=None, seg_scale=None,
+              accumulate=False, independent=False):
+    """``fwd`` for every projection of the set in one launch."""
+    with torch.cuda.device(ps.ref.device):
+        check(lib.smlm_b200_fwd_multi(ps.ptr, ps.n, _p(seg_ids), _p(seg_scale), plan.buf.data_ptr(),
+                                      int(ps.keep[0]["wa"].numel()), plan.T, plan.nseg, int(rank), ps._dt("x"),
+                                      int(bool(is_row_major)), int(bool(accumulate)), int(bool(independent)),
+                                      int(plan.n_table > 0), _stream(ps.ref)), "smlm_b200_fwd_multi")
+
+
+def bwd_dx_multi(ps: ProjSet, plan: Plan, rank: int, is_row_major=False, part_ids=None, part_scale=None,
+                 independent=False):
+    """``bwd_dx`` for every projection of the set in one launch."""
+    with torch.cuda.device(ps.ref.device):
+        check(lib.smlm_b200_bwd_dx_multi(ps.ptr, ps.n, _p(part_ids), _p(part_scale), plan.buf.data_ptr(),
+                                         int(ps.keep[0]["wa"].numel()), plan.T, plan.nseg, int(rank), ps._dt("go"),
+                                         int(bool(is_row_major)), int(bool(independent)), _stream(ps.ref)),
+              "smlm_b200_bwd_dx_multi")
+
+
+def wgrad_multi_workspace(ps: ProjSet, T: int, npart: int, rank: int, slot: str = "multi") -> torch.Tensor:
+    """Zero-filled workspace of ``wgrad_pair_multi`` for this set, cached per device and slot."""
+    need = int(lib.smlm_b200_wgrad_multi_workspace_bytes(ps.ptr, ps.n, int(T), int(npart), int(rank)))
+    dev = ps.ref.device
+    ws = _WORKSPACES.get((dev, slot))
+    if ws is None or ws.numel() < need:
+        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
+        _WORKSPACES[(dev, slot)] = ws
+    return ws
+
+
+def wgrad_pair_multi(ps: ProjSet, part_indptr, plan: Plan, rank: int, is_row_major=False, part_ids=None,
+                     part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None,
+                     independent=False):
+    """``wgrad_pair`` for every projection of the set in one launch."""
+    ws = workspace if workspace is not None else wgrad_multi_workspace(ps, plan.T, plan.nseg, rank)
+    with torch.cuda.device(ps.ref.device):
+        check(lib.smlm_b200_wgrad_pair_multi(ps.ptr, ps.n, part_indptr.data_ptr(), _p(part_ids), _p(part_scale),
+                                             plan.buf.data_ptr(), ws.data_ptr(), ws.numel(), int(n_table),
+                                             int(part_indptr.numel()) - 1, plan.T, int(rank), ps._dt("go"),
+                                             int(bool(is_row_major)), int(bool(accumulate)), int(bool(grad_fp32)),
+                                             int(bool(independent)), _stream(ps.ref)),
+              "smlm_b200_wgrad_pair_multi")
 
 
 # ---------------------------------------------------------------------------

@@ -217,6 +217,26 @@ def golden_rms_norm(ku, name, seed, dtype, rows, cols, eps):
                       meta=np.asarray([rows, cols, eps], dtype=np.float64), dtype=str(dtype))
 
 
+def golden_prepare_weight(ml, name, seed, dtype):
+    """MixedLoraModel._prepare_weight (mixed_lora.py:501-521) called unbound on the three kinds of input
+    it sees at load time: an A panel whose rank is below the model-wide rank (zero-padded along dim 0)
+    with the scale baked in, a B panel padded along dim 1 without a scale, and a panel of full rank
+    with a scale.  Inputs are fp32 as PEFT holds them; outputs are in the module dtype."""
+    g = torch.Generator().manual_seed(seed)
+    me = types.SimpleNamespace(rank=16, dtype=dtype)
+    a_small = torch.randn((8, 64), generator=g) / 8
+    b_small = torch.randn((48, 8), generator=g) * 0.02
+    a_full = torch.randn((16, 64), generator=g) / 8
+    cpu = torch.device("cpu")
+    f = ml.MixedLoraModel._prepare_weight
+    out = dict(a_small=a_small.numpy(), b_small=b_small.numpy(), a_full=a_full.numpy(),
+               a_small_out=_bits(f(me, a_small, cpu, 0, 2.0)),
+               b_small_out=_bits(f(me, b_small, cpu, 1, None)),
+               a_full_out=_bits(f(me, a_full, cpu, 0, 0.3)),
+               dtype=str(dtype))
+    return name, out
+
+
 def golden_batch_len_info(ku):
     cases = [
         dict(trains=[], prefills=[], decode=0, evals=[]),
@@ -351,6 +371,8 @@ def main():
         golden_add_lora_bwd(ku, "bwd_math_fp16", 1008, torch.float16, [0, 70], 64, 64, 8, 70),
         golden_rms_norm(ku, "rmsnorm_bf16", 1009, torch.bfloat16, 37, 256, 1e-6),
         golden_rms_norm(ku, "rmsnorm_fp16", 1010, torch.float16, 5, 520, 1e-5),
+        golden_prepare_weight(ml, "prepare_weight_bf16", 1011, torch.bfloat16),
+        golden_prepare_weight(ml, "prepare_weight_fp16", 1012, torch.float16),
     ]
     for name, arrs in cases:
         np.savez_compressed(os.path.join(a.out, name + ".npz"), **arrs)

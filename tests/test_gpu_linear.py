@@ -210,3 +210,123 @@ def test_linear_with_unsorted_decode_tokens_uses_a_grouped_plan():
     assert_close(y, y_ref, what="fused, grouped plan")
     assert_close(y_ops, y_ref, what="reference operator sequence")
     assert_close(y, y_ops.float(), rtol=1e-2, atol=1e-2, what="fused vs operator sequence")
+
+
+def test_add_and_del_adapter_keep_tables_and_results_in_step():
+    """add_adapter / del_adapter (mixed_lora.py:106-148 of the reference) followed by a forward: the pointer and
+    scale tables follow the adapter list, and a batch that uses the changed list gives the oracle's result."""
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    dt = torch.bfloat16
+    h_in, h_out, r = 256, 192, 16
+    g = torch.Generator().manual_seed(21)
+    mk = lambda i, sc: (NamedLoraLayer(f"a{i}", (torch.randn((r, h_in), generator=g) / 16).to(dt).to(DEV).contiguous(),
+                                       (torch.randn((h_out, r), generator=g) * 0.02).to(dt).to(DEV).contiguous(),
+                                       nn.Identity(), sc))
+    ads = [mk(0, 2.0), mk(1, 0.5), mk(2, 1.0)]
+    wbase = (torch.randn((h_out, h_in), generator=g) * 0.02).to(dt)
+    base = nn.Linear(h_in, h_out, bias=False, dtype=dt, device=DEV)
+    with torch.no_grad():
+        base.weight.copy_(wbase)
+    ctx = MixedLoraContext()
+    lin = MixedLoraLinear(ctx, base, list(ads), r, dt)
+
+    def run(lens, ids):
+        T = sum(lens)
+        x = torch.randn((T, h_in), generator=g).to(dt)
+        seg = torch.cumsum(torch.tensor([0] + lens, dtype=torch.int32, device=DEV), 0, dtype=torch.int32)
+        ctx.update(BatchLenInfo([], [], 0, [], torch.device(DEV)), ids,
+                   torch.tensor(lens, dtype=torch.int32, device=DEV), seg, [])
+        with torch.no_grad():
+            y = lin(x.to(DEV))
+        cur = lin.adapters
+        want = O.lora_linear_forward(x, wbase, [a.wa.cpu() for a in cur], [a.wb.cpu() for a in cur],
+                                     [a.scaling for a in cur], ids, lens, r, dt)
+        assert_close(y, want, what=f"{len(cur)} adapters")
+
+    run([20, 3, 40], [2, 0, 1])
+    extra = mk(3, 4.0)
+    lin.add_adapter(extra)
+    assert lin.wa_ptrs.tolist() == [a.wa.data_ptr() for a in ads + [extra]]
+    assert lin.wb_ptrs.tolist() == [a.wb.data_ptr() for a in ads + [extra]]
+    assert lin.scaling.tolist() == [2.0, 0.5, 1.0, 4.0] and lin.scaling.dtype == dt
+    run([5, 33, 1, 17], [3, 0, 3, 1])            # the new adapter is index 3
+    lin.del_adapter(1)                           # indices above it move down by one
+    assert [a.adapter_name for a in lin.adapters] == ["a0", "a2", "a3"]
+    assert lin.wa_ptrs.tolist() == [ads[0].wa.data_ptr(), ads[2].wa.data_ptr(), extra.wa.data_ptr()]
+    assert lin.scaling.tolist() == [2.0, 1.0, 4.0]
+    run([9, 64, 2], [2, 1, 0])
+    with pytest.raises(AssertionError):
+        lin.del_adapter(3)
+
+
+def test_segments_rebuilt_inside_a_cuda_graph_follow_new_requests():
+    """merge of the requests into segments -> plan (grouped) -> fused forward, all captured in ONE graph; between
+    replays only the per-request device arrays are rewritten, and each replay gives the oracle's answer for the
+    batch those arrays describe."""
+    from loquetier_b200 import ops
+    from loquetier_b200.cabi import check, lib
+    dt = torch.bfloat16
+    h_in, h_out, r, n_ad, n_req, T = 256, 320, 16, 4, 12, 96
+    g = torch.Generator().manual_seed(31)
+    was = [(torch.randn((r, h_in), generator=g) / 16).to(dt) for _ in range(n_ad)]
+    wbs = [(torch.randn((h_out, r), generator=g) * 0.02).to(dt) for _ in range(n_ad)]
+    wa_d = [w.to(DEV).contiguous() for w in was]
+    wb_d = [w.to(DEV).contiguous() for w in wbs]
+    tab = lambda ts: torch.tensor([t.data_ptr() for t in ts], dtype=torch.int64, device=DEV)
+    wa_t, wb_t = tab(wa_d), tab(wb_d)
+    req_ids = torch.zeros(n_req, dtype=torch.int32, device=DEV)
+    req_len = torch.zeros(n_req, dtype=torch.int32, device=DEV)
+    seg_ids = torch.zeros(n_req, dtype=torch.int32, device=DEV)
+    seg_len = torch.zeros(n_req, dtype=torch.int32, device=DEV)
+    segment = torch.zeros(n_req + 1, dtype=torch.int32, device=DEV)
+    nseg = torch.zeros(1, dtype=torch.int32, device=DEV)
+    x = torch.zeros((T, h_in), dtype=dt, device=DEV)
+    y = torch.zeros((T, h_out), dtype=dt, device=DEV)
+    v = torch.zeros((T, r), dtype=dt, device=DEV)
+    nbytes = lib.smlm_b200_plan_bytes(T, n_req)
+    plan_buf = torch.zeros((nbytes + 3) // 4, dtype=torch.int32, device=DEV)
+
+    def step():
+        st = torch.cuda.current_stream().cuda_stream
+        check(lib.smlm_b200_merge_segments(req_ids.data_ptr(), req_len.data_ptr(), n_req, seg_ids.data_ptr(),
+                                           seg_len.data_ptr(), segment.data_ptr(), nseg.data_ptr(), st), "merge")
+        check(lib.smlm_b200_plan_grouped(plan_buf.data_ptr(), nbytes, segment.data_ptr(), seg_ids.data_ptr(), n_req,
+                                         n_ad, T, st), "plan")
+        check(lib.smlm_b200_fwd(y.data_ptr(), x.data_ptr(), v.data_ptr(), wa_t.data_ptr(), wb_t.data_ptr(),
+                                seg_ids.data_ptr(), None, plan_buf.data_ptr(), n_ad, T, n_req, h_in, h_out, r, 1, 0,
+                                0, 0, 1, st), "fwd")
+
+    batches = [
+        ([1, 1, 0, 2, 2, 2, 3, 0, 1, 3, 0, 0], [10, 6, 1, 20, 1, 1, 30, 1, 1, 1, 1, 1]),     # 74 rows, 9 segments
+        ([0, 3, 0, 3, 0, 3, 1, 1, 2, 2, 2, 2], [1, 1, 1, 1, 1, 1, 40, 2, 8, 8, 8, 8]),      # 80 rows, scattered decode
+        ([2] * 12, [8] * 12),                                                                  # one segment of 96 rows
+    ]
+    req_ids.copy_(torch.tensor(batches[0][0], dtype=torch.int32))
+    req_len.copy_(torch.tensor(batches[0][1], dtype=torch.int32))
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        step()
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        step()
+    for ids, lens in batches:
+        n = sum(lens)
+        xb = torch.randn((T, h_in), generator=g).to(dt)
+        req_ids.copy_(torch.tensor(ids, dtype=torch.int32))
+        req_len.copy_(torch.tensor(lens, dtype=torch.int32))
+        x.copy_(xb)
+        y.fill_(7.0)
+        graph.replay()
+        torch.cuda.synchronize()
+        mids, mlens, mseg = O.merge_segments(list(zip(ids, lens)))
+        assert int(nseg.item()) == len(mids)
+        assert seg_ids[:len(mids)].tolist() == mids and segment[:len(mids) + 1].tolist() == mseg
+        want, _ = O.add_lora_forward((T, h_out), xb, [was[i] for i in mids], [wbs[i] for i in mids], mseg, r,
+                                     fill=7.0)
+        assert_close(y[:n], want[:n], what=f"replay with {len(mids)} segments")
+        assert bool((y[n:] == 7.0).all()), "rows past the batch must stay untouched"
+        hdr = plan_buf[:4].tolist()
+        assert hdr[1] == 0, f"plan recorded fault bits {hdr[1]}"

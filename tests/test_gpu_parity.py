@@ -359,3 +359,56 @@ def test_device_segment_merge_is_bit_exact():
     from gpu_util import oracle_forward
     y_ref, _ = oracle_forward(c)
     assert_close(y, y_ref, what="y through device-merged segments")
+
+
+def test_independent_promise_covers_every_open_kernel():
+    """A chain D (dependent), I (independent, unrelated), C: C consumes D's output, so C has to be
+    launched with independent = 0 although an unrelated independent launch sits between the two - an
+    independent launch may run alongside ALL kernels since the last dependent one.  Launched that way
+    the chain gives the oracle's answer."""
+    from gpu_util import dev, ptr_table, to_dev
+    from loquetier_b200 import ops
+    lens, ids = [200, 3, 130, 64], [1, 0, 2, 1]
+    c = to_dev(O.make_case(77, lens, ids, 3, 512, 512, 16, torch.bfloat16))
+    T = sum(lens)
+    wa = ptr_table([c["wa_d"][i] for i in ids])
+    wb = ptr_table([c["wb_d"][i] for i in ids])
+    plan = ops.Plan(c["seg_d"], T)
+    y_d = torch.zeros((T, 512), dtype=torch.bfloat16, device=dev())
+    y_i = torch.zeros_like(y_d)
+    y_c = torch.zeros_like(y_d)
+    v = [torch.zeros((T, 16), dtype=torch.bfloat16, device=dev()) for _ in range(3)]
+    other = torch.randn((T, 512), device=dev()).to(torch.bfloat16)
+    ops.fwd(y_d, c["x"], v[0], wa, wb, plan, 16)                              # D: writes y_d
+    ops.fwd(y_i, other, v[1], wa, wb, plan, 16, independent=True)             # I: touches nothing of D or C
+    ops.fwd(y_c, y_d, v[2], wa, wb, plan, 16, independent=False)              # C: reads y_d
+    torch.cuda.synchronize()
+    plan.raise_if_failed()
+    want_d, _ = O.add_lora_forward((T, 512), c["x"].cpu(), [c["wa"][i] for i in ids], [c["wb"][i] for i in ids],
+                                   c["seg"], 16)
+    want_c, _ = O.add_lora_forward((T, 512), y_d.cpu(), [c["wa"][i] for i in ids], [c["wb"][i] for i in ids],
+                                   c["seg"], 16)
+    assert_close(y_d, want_d, what="D")
+    assert_close(y_c, want_c, what="C reads D's output")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rank", [16, 64])
+def test_backward_literal_tolerance_at_reference_rounding_points(dtype, rank):
+    """dX, dA and dB against the oracle evaluated the way the reference evaluates them - dV and the
+    recomputed v rounded to the storage type (round_mid=True) - at the literal rtol = atol = 1e-2, over
+    partitions of 1 to 1500 rows.  (The normwise bound of the other backward tests belongs to the
+    comparison with the unrounded ideal, where the rounding of v and dV alone contributes
+    2^-9 |v| per token, summed over a partition's tokens.)"""
+    part = [0, 1, 18, 1518, 1519, 1627]
+    c = _case(500 + rank, [1700], 5, 512, 384, rank, dtype, False, ids=[0])
+    dx, dA, dB = _run_bwd(c, part)
+    npart = len(part) - 1
+    gx, grads = O.add_lora_backward(c["go"], c["x"], c["wa"][:npart], c["wb"][:npart], part, round_mid=True)
+    assert_close(dx[:part[-1]], gx[:part[-1]], rtol=1e-2, atol=1e-2, what="dX")
+    worst = 0.0
+    for p in range(npart):
+        for got, want, nm in ((dA[p], grads[2 * p], "dA"), (dB[p], grads[2 * p + 1], "dB")):
+            assert_close(got, want, rtol=1e-2, atol=1e-2, what=f"{nm}{p}")
+            worst = max(worst, float((got.float() - want.float()).abs().max()) / max(float(want.float().abs().max()), 1e-30))
+    print(f"observed max|err|/max|ref| over dA, dB: {worst:.3e}")

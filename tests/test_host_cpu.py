@@ -131,3 +131,44 @@ def test_grouped_plan_is_requested_only_when_it_changes_something():
     assert wants_grouped_plan([100, 1, 50, 8], [0, 1, 2, 1])        # adapter 1: rows 100 and 151..158
     assert not wants_grouped_plan([0, 0, 4], [3, 3, 3])             # empty segments do not count
     assert wants_grouped_plan([1] * 4, [7, 2, 5, 7])
+
+
+@pytest.mark.parametrize("name", ["prepare_weight_bf16", "prepare_weight_fp16"])
+def test_prepare_weight_matches_the_reference_bit_for_bit(name):
+    """Against MixedLoraModel._prepare_weight of the reference (mixed_lora.py:501-521) run on the same inputs:
+    padding along either dimension, the scale baked in before the cast."""
+    from helpers import load_npz
+    from loquetier_b200.mixed_lora import prepare_weight
+    z = load_npz(name)
+    dt = z["dtype"]
+    for key, rank_dim, scaling in (("a_small", 0, 2.0), ("b_small", 1, None), ("a_full", 0, 0.3)):
+        got = prepare_weight(z[key], 16, dt, "cpu", rank_dim=rank_dim, scaling=scaling)
+        want = z[key + "_out"]
+        assert got.dtype == dt and got.is_contiguous() and got.shape == want.shape
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), key
+
+
+def test_install_as_loquetier_kernels_resolves_the_reference_import():
+    """`from loquetier.ops import _kernels` (src/loquetier_src/kernel_utils.py:8 of the reference) must find the
+    three names its pybind module registers for this path (kernel_src/csrc/loquetier_ops.cc:371-373)."""
+    import sys
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "loquetier" or k.startswith("loquetier.")}
+    try:
+        from loquetier_b200 import kernels
+        me = kernels.install_as_loquetier_kernels()
+        from loquetier.ops import _kernels as kernel
+        assert kernel is me is kernels
+        import loquetier.ops._kernels as again
+        assert again is kernels
+        for name in ("smlm_forward_cutlass", "smlm_forward_cutlass_tmp_size", "rms_norm"):
+            assert callable(getattr(kernel, name)), name
+        assert kernel.smlm_forward_cutlass_tmp_size(70) == 4200
+        # the argument checks of the dispatcher run before any device work
+        t = torch.zeros((4, 8))
+        with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
+            kernel.smlm_forward_cutlass(t, t, torch.zeros(1, dtype=torch.int64), torch.zeros(2, dtype=torch.int32),
+                                        torch.zeros(60, dtype=torch.uint8), False)
+    finally:
+        for k in [k for k in sys.modules if k == "loquetier" or k.startswith("loquetier.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)
