@@ -902,6 +902,72 @@ def run_c5(a, rank, world, local, torch, dist, blocks, steps):
     return rec
 
 
+def run_decode(a, rank, world, local, torch, dist, blocks, steps):
+    """Decode attention over the paged key-value cache (the step between the q/k/v and o projections of a
+    decode batch) with the key/value append in front of it: Llama-3-8B heads (32 query, 8 kv, dim 128),
+    page size 16, one layer's pages, 128 one-token requests with context lengths uniform in [512, 4096].
+    Requests shard over ranks with no collective.  Algorithmic bytes: every K and V entry of every context
+    once, q and o once."""
+    from loquetier_b200 import kvcache
+    dev = torch.device("cuda", local)
+    B, N, G, P, D = 128, 8, 4, 16, 128
+    rng = np.random.default_rng(9000 + rank)
+    seqlens = [int(v) for v in rng.integers(512, 4097, size=B)]
+    pool = kvcache.KvPool(1, N, D, P, torch.bfloat16, dev, pages_per_slab=4096)
+    caches = [kvcache.KvCache(pool, L) for L in seqlens]
+    for slab in pool._slabs:
+        slab.normal_()
+    bkv = kvcache.BatchedKvCache(caches)
+    g = torch.Generator(device=dev).manual_seed(9000 + rank)
+    q = torch.randn((B, N * G, D), generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn((B, N, D), generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn((B, N, D), generator=g, device=dev).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    ws = kvcache.decode_workspace(dev, B, N * G, N)
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        kvcache.append_kv_raw(bkv.ptrs, bkv.indptr, bkv.last_page_offset, k, v, 1, 0, N, P, status_word=word)
+        kvcache.batch_decode_into(o, q, bkv.ptrs, bkv.indptr, bkv.last_page_offset, 1, 0, N, 500000.0, P, workspace=ws,
+                                  status_word=word)
+
+    step()
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0, "the kernels recorded a fault"
+    fn = capture(step, torch) if not a.no_graph else step
+    ms, per = timed(fn, steps, max(3, a.warmup), torch, dist, None, blocks)
+    nbytes = 2 * (2 * sum(seqlens) * N * D + 2 * B * N * G * D + 2 * B * N * D)
+    peak, which = hbm_peak()
+    rec = dict(workload="decode: paged-KV batch decode attention + append, bf16, 128 requests, contexts 512..4096, "
+                        "32 query / 8 kv heads of dim 128, page size 16",
+               metric="decode attention tokens/s", value=B * world / (ms * 1e-3), unit="tokens/s", n_gpus=world,
+               ms_per_step=ms, ms_per_step_min=min(per), ms_per_step_max=max(per), blocks=len(per),
+               context_tokens=sum(seqlens), pages=int(bkv.ptrs.numel()),
+               l2="%.0f MB of keys and values per step (> 126 MB L2)" % (nbytes / 1e6),
+               step_hbm=dict(algorithmic_bytes=nbytes, achieved_gbs=nbytes / (ms * 1e-3) / 1e9,
+                             frac=nbytes / (ms * 1e-3) / 1e9 / peak, peak_gbs=peak, peak_source=which),
+               launch_mode="eager" if a.no_graph else "cuda graph replay", gpu_launches_per_step=2)
+    if a.check and rank == 0:
+        from oracle import attention_oracle as AO
+        sel = [int(i) for i in np.argsort(seqlens)[[0, B // 2, B - 1]]]   # shortest, median, longest context
+        pages = []
+        ind, last = [0], []
+        for i in sel:
+            c = caches[i]
+            pages += [pg.cpu() for pg in c.pages]
+            ind.append(ind[-1] + c.num_pages)
+            last.append(AO.last_page_offset_of(c.seqlen, P))
+        want = AO.batch_decode(q[sel].cpu(), pages, ind, last, 0, 500000.0)
+        err = (o[sel].cpu().float() - want.float()).abs()
+        assert bool((err <= 1e-2 + 1e-2 * want.float().abs()).all()), "decode differs from the oracle"
+        for j, i in enumerate(sel):   # the appended key/value sits in the last valid entry
+            got = caches[i].pages[-1][0, 0, :, last[j] - 1, :]
+            assert torch.equal(got, k[i]), "append differs from the oracle"
+        rec["parity_checked"] = True
+        rec["parity_max_abs_err"] = float(err.max())
+    return rec
+
+
 def run_linear_host(a, local, torch):
     """Host time of one eager MixedLoraLinear.forward - what a model pays per LoRA linear and step on top
     of the kernels: wall clock around many forwards without a synchronisation in between, for the segment
@@ -949,7 +1015,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear"])
+    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear", "decode"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps; the median is reported")
     ap.add_argument("--sched", default="multi", choices=["multi", "split", "single"],
@@ -983,6 +1049,23 @@ def main():
         line = run_rmsnorm(a, rank, world, local, torch)
         if line is not None and rank == 0:
             print(json.dumps(line))
+        return
+    if a.workload == "decode":
+        assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
+        torch.cuda.set_device(local)
+        dist = None
+        if world > 1:
+            import torch.distributed as dist_mod
+            dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
+            dist = dist_mod
+        rec = run_decode(a, rank, world, local, torch, dist, a.blocks, a.steps)
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        if rank == 0:
+            rec.update(steps=a.steps, warmup=a.warmup, higher_is_better=True, scaling="weak", vs_baseline=None,
+                       dtype="bf16", data="synthetic", config=dict(workload=rec["workload"]))
+            print(json.dumps(rec))
         return
     if a.workload == "linear":
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
@@ -1130,6 +1213,10 @@ def main():
         if rms is not None:
             line["rmsnorm"] = {k: rms[k] for k in ("metric", "value", "unit", "ms_per_step", "step_hbm", "kernels",
                                                    "config") if k in rms}
+        torch.cuda.empty_cache()
+        dec = run_decode(sub, rank, world, local, torch, dist, max(3, a.blocks // 5), max(5, min(a.steps, 20)))
+        if rank == 0:
+            line["attention_decode"] = dec
     if rank == 0 and world == 1 and not a.no_cpu:
         base, _ = run_cpu(spec, torch)
         line["cpu_baseline"] = base

@@ -33,7 +33,7 @@ class SmlmProj(ctypes.Structure):
                 ("dB_table", c_void_p), ("h_in", c_int), ("h_out", c_int)]
 
 
-# name -> (restype, argtypes); mirrors include/smlm_b200.h one to one
+# name -> (restype, argtypes); mirrors include/smlm_b200.h and include/smlm_b200_kv.h one to one
 SIGNATURES = {
     "smlm_b200_version": (c_int, []),
     "smlm_b200_status_string": (c_char_p, [c_int]),
@@ -59,6 +59,10 @@ SIGNATURES = {
     "smlm_b200_wgrad_multi_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad_pair_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_size_t] + [c_int] * 9 + [c_void_p]),
+    "smlm_b200_batch_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "smlm_b200_batch_decode": (c_int, [c_void_p] * 6 + [c_size_t, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p]),
+    "smlm_b200_append_kv": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
+    "smlm_b200_init_kv": (c_int, [c_void_p] * 7 + [c_int] * 9 + [c_void_p]),
     "smlm_b200_rms_norm": (c_int, [c_void_p] * 4 + [c_int, c_int, c_float, c_int, c_void_p]),
     "smlm_b200_rms_norm_bwd_workspace_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_rms_norm_bwd": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 4 + [c_void_p]),

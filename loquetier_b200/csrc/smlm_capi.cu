@@ -5,10 +5,13 @@
 
 #include <algorithm>
 #include <atomic>
+#include <cmath>
 #include <mutex>
 #include <vector>
 
 #include "../../include/smlm_b200.h"
+#include "../../include/smlm_b200_kv.h"
+#include "paged_kv.cuh"
 #include "rms_norm.cuh"
 #include "smlm_fused.cuh"
 #include "smlm_fused_tc.cuh"
@@ -578,6 +581,71 @@ int launch_rms_bwd(void* dx, void* dw, const void* go, const void* x, const void
                 static_cast<const float*>(partial), g, cols, dw_fp32);
 }
 
+// ---- paged key-value cache ----------------------------------------------------------
+// Page ranges a (request, kv head) is cut into, so that small batches still fill the machine.  The
+// sequence lengths live on the device, so the choice depends on the batch shape only.
+inline int decode_splits(int batch, int num_kv_heads) {
+  const int ctas = std::max(1, batch * num_kv_heads);
+  return std::max(1, std::min(kPdMaxSplits, (2 * kNumSMs + ctas - 1) / ctas));
+}
+
+inline size_t decode_ticket_bytes(int batch, int num_kv_heads) {
+  return (static_cast<size_t>(batch) * num_kv_heads * sizeof(int) + 255) / 256 * 256;
+}
+
+template <typename T, int G>
+int launch_decode(const PdArgs& a, cudaStream_t stream) {
+  const int stage = 2 * a.page_size * kPdDim * static_cast<int>(sizeof(T));
+  constexpr int kRed = (G / pd_heads_per_thread(G)) * kPdEntryLanes * pd_heads_per_thread(G) * kPdRec * 4;
+  const int smem = std::max(kPdStages * stage, kRed);
+  return launch(paged_decode_kernel<T, G>, dim3(a.batch * a.num_kv_heads * a.splits, 1, 1), pd_threads(G), 1, smem,
+                stream, a);
+}
+
+template <typename T>
+int dispatch_decode(const PdArgs& a, int group, cudaStream_t stream) {
+  switch (group) {
+    case 1: return launch_decode<T, 1>(a, stream);
+    case 2: return launch_decode<T, 2>(a, stream);
+    case 4: return launch_decode<T, 4>(a, stream);
+    case 8: return launch_decode<T, 8>(a, stream);
+    default: return SMLM_ERR_NO_KERNEL;
+  }
+}
+
+inline bool kv_shape_ok(int head_dim, int page_size) {
+  return head_dim == kPdDim && page_size >= 8 && page_size <= 64 && page_size % 8 == 0;
+}
+
+int run_append(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset, const void* k,
+               const void* v, const int32_t* append_indptr, int* err, int batch, int total_pages, int max_tokens,
+               int num_layers, int layer_idx, int num_kv_heads, int head_dim, int page_size, int dtype,
+               cudaStream_t stream) {
+  if (batch < 0 || total_pages < 0 || num_layers <= 0 || layer_idx < 0 || layer_idx >= num_layers || num_kv_heads <= 0)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (!kv_shape_ok(head_dim, page_size)) return SMLM_ERR_NO_KERNEL;
+  if (batch == 0) return SMLM_OK;
+  if (kv_ptrs == nullptr || kv_indptr == nullptr || last_page_offset == nullptr || k == nullptr || v == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(k) || !aligned16(v)) return SMLM_ERR_MISALIGNED;
+  AppendArgs a;
+  a.kv_ptrs = kv_ptrs; a.kv_indptr = kv_indptr; a.last_page_offset = last_page_offset; a.k = k; a.v = v;
+  a.append_indptr = append_indptr; a.err = err;
+  a.batch = batch; a.num_kv_heads = num_kv_heads; a.num_layers = num_layers; a.layer_idx = layer_idx;
+  a.page_size = page_size; a.total_pages = total_pages;
+  // token chunks per (request, head): enough CTAs to fill the machine when few requests bring long runs
+  const int rows = batch * num_kv_heads;
+  int chunks = 1;
+  if (append_indptr != nullptr) {
+    const int per = std::max(1, (max_tokens + 7) / 8);
+    chunks = std::max(1, std::min(per, (4 * kNumSMs + rows - 1) / rows));
+  }
+  const dim3 grid(rows, chunks, 1);
+  return dtype == SMLM_F16 ? launch(append_kv_kernel<__half>, grid, 128, 1, 0, stream, a)
+                           : launch(append_kv_kernel<__nv_bfloat16>, grid, 128, 1, 0, stream, a);
+}
+
 inline bool projs_ok(const smlm_b200_proj* projs, int nproj) {
   return projs != nullptr && nproj >= 1 && nproj <= SMLM_MAX_PROJ;
 }
@@ -921,6 +989,70 @@ int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int
   return run_wgrad(jobs, 2 * nproj, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes,
                    npart, T, rank, dtype, accumulate, grad_fp32, independent != 0, wgrad_uses_tensor_cores(rank),
                    static_cast<cudaStream_t>(stream));
+}
+
+// ---- paged key-value cache ------------------------------------------------------------------
+
+size_t smlm_b200_batch_decode_workspace_bytes(int batch_size, int num_qo_heads, int num_kv_heads) {
+  if (batch_size <= 0 || num_qo_heads <= 0 || num_kv_heads <= 0) return 0;
+  return decode_ticket_bytes(batch_size, num_kv_heads) +
+         static_cast<size_t>(batch_size) * num_qo_heads * decode_splits(batch_size, num_kv_heads) * kPdRec *
+             sizeof(float);
+}
+
+int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, const int32_t* kv_indptr,
+                           const int32_t* last_page_offset, void* workspace, size_t workspace_bytes, int* status_word,
+                           int batch_size, int total_pages, int num_qo_heads, int num_kv_heads, int head_dim,
+                           int num_layers, int layer_idx, int page_size, float rope_theta, int dtype, void* stream) {
+  if (batch_size < 0 || total_pages < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_layers <= 0 ||
+      layer_idx < 0 || layer_idx >= num_layers || !(rope_theta > 0.f))
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  // the reference's "No suitable kernel." (loquetier_ops.cc:157-159): head_dim, page size, group size
+  if (num_qo_heads % num_kv_heads != 0 || !kv_shape_ok(head_dim, page_size)) return SMLM_ERR_NO_KERNEL;
+  const int group = num_qo_heads / num_kv_heads;
+  if (group != 1 && group != 2 && group != 4 && group != 8) return SMLM_ERR_NO_KERNEL;
+  if (batch_size == 0) return SMLM_OK;
+  if (o == nullptr || q == nullptr || kv_ptrs == nullptr || kv_indptr == nullptr || last_page_offset == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(q)) return SMLM_ERR_MISALIGNED;
+  PdArgs a;
+  a.splits = decode_splits(batch_size, num_kv_heads);
+  if (a.splits > 1) {
+    if (workspace == nullptr || workspace_bytes < smlm_b200_batch_decode_workspace_bytes(batch_size, num_qo_heads,
+                                                                                          num_kv_heads))
+      return SMLM_ERR_WORKSPACE;
+    if (!aligned16(workspace)) return SMLM_ERR_MISALIGNED;
+  }
+  a.o = o; a.q = q; a.kv_ptrs = kv_ptrs; a.kv_indptr = kv_indptr; a.last_page_offset = last_page_offset;
+  a.err = status_word;
+  a.tickets = static_cast<int*>(workspace);
+  a.partial = workspace == nullptr ? nullptr
+                                   : reinterpret_cast<float*>(static_cast<char*>(workspace) +
+                                                              decode_ticket_bytes(batch_size, num_kv_heads));
+  a.batch = batch_size; a.num_kv_heads = num_kv_heads; a.num_layers = num_layers; a.layer_idx = layer_idx;
+  a.page_size = page_size; a.total_pages = total_pages;
+  a.log2_theta = std::log2(rope_theta);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == SMLM_F16 ? dispatch_decode<__half>(a, group, st) : dispatch_decode<__nv_bfloat16>(a, group, st);
+}
+
+int smlm_b200_append_kv(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset,
+                        const void* k, const void* v, int* status_word, int batch_size, int total_pages,
+                        int num_layers, int layer_idx, int num_kv_heads, int head_dim, int page_size, int dtype,
+                        void* stream) {
+  return run_append(kv_ptrs, kv_indptr, last_page_offset, k, v, nullptr, status_word, batch_size, total_pages, 1,
+                    num_layers, layer_idx, num_kv_heads, head_dim, page_size, dtype, static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_init_kv(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset,
+                      const void* k, const void* v, const int32_t* seqlen_indptr, int* status_word, int batch_size,
+                      int total_pages, int total_tokens, int num_layers, int layer_idx, int num_kv_heads, int head_dim,
+                      int page_size, int dtype, void* stream) {
+  if (seqlen_indptr == nullptr || total_tokens < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  return run_append(kv_ptrs, kv_indptr, last_page_offset, k, v, seqlen_indptr, status_word, batch_size, total_pages,
+                    total_tokens, num_layers, layer_idx, num_kv_heads, head_dim, page_size, dtype,
+                    static_cast<cudaStream_t>(stream));
 }
 
 int smlm_b200_rms_norm(void* out, float* rms_out, const void* x, const void* w, int rows, int cols, float eps,

@@ -1,6 +1,7 @@
 """Drop-in for the reference's native module ``loquetier.ops._kernels`` on the SMLM
-path and for the RMSNorm next to it: the same names with the same arguments and error
-behaviour (pybind registrations at kernel_src/csrc/loquetier_ops.cc:371-373).
+path, for the RMSNorm next to it and for the decode side of the paged key-value cache: the same
+names with the same arguments and error behaviour (pybind registrations at
+kernel_src/csrc/loquetier_ops.cc:365-373).
 
 ``install_as_loquetier_kernels()`` registers this module under that import name so
 that the reference's ``from loquetier.ops import _kernels as kernel``
@@ -77,9 +78,95 @@ def rms_norm(output: torch.Tensor, rms_output: torch.Tensor, input: torch.Tensor
     ops.rms_norm(output, rms_output, input, weight, epsilon)
 
 
+def _chk_kv(kv_ptrs, kv_indptr, last_page_offset, batch_size):
+    for t, name in ((kv_ptrs, "kv_ptrs"), (kv_indptr, "kv_indptr"), (last_page_offset, "last_page_offset")):
+        ops._chk_cuda_contig(t, name, 1)
+    if kv_ptrs.dtype != torch.int64 or kv_indptr.dtype != torch.int32 or last_page_offset.dtype != torch.int32:
+        raise RuntimeError("kv_ptrs must be int64, kv_indptr and last_page_offset int32")
+    if kv_indptr.size(0) != batch_size + 1:
+        raise RuntimeError(f"CHECK_EQ(kv_indptr.size(0), batch_size + 1) failed. {kv_indptr.size(0)} vs {batch_size + 1}")
+    if last_page_offset.size(0) != batch_size:
+        raise RuntimeError(f"CHECK_EQ(last_page_offset.size(0), batch_size) failed. "
+                           f"{last_page_offset.size(0)} vs {batch_size}")
+
+
+def _no_kernel(e, q, page_size, group_size):
+    from .cabi import SmlmError
+    if isinstance(e, SmlmError) and e.status in (2, 3):
+        return RuntimeError(f"No suitable kernel. dtype={q.dtype} page_size={page_size} group_size={group_size} "
+                            f"head_dim={q.size(2)}")
+    return e
+
+
+def batch_decode(o: torch.Tensor, q: torch.Tensor, kv_ptrs: torch.Tensor, kv_indptr: torch.Tensor,
+                 last_page_offset: torch.Tensor, tmpbuf: torch.Tensor, num_layers: int, layer_idx: int,
+                 num_kv_heads: int, base: float, page_size: int) -> None:
+    """Decode attention over the paged cache with the arguments and checks of the reference's binding
+    (batch_decode, loquetier_ops.cc:138-180).  ``tmpbuf`` is accepted for compatibility (the reference
+    wants at least 64 MiB of it) and not used: its contents are undefined, whereas this kernel's
+    workspace has to start zeroed, so the workspace is kept by the wrapper.  Does not synchronise."""
+    from . import kvcache
+    for t, name in ((o, "o"), (q, "q")):
+        ops._chk_cuda_contig(t, name, 3)
+    if o.shape != q.shape:
+        raise RuntimeError("CHECK_SHAPE(o, q) failed")
+    batch_size, num_qo_heads = int(o.size(0)), int(o.size(1))
+    group_size = num_qo_heads // max(int(num_kv_heads), 1)
+    if num_qo_heads != group_size * num_kv_heads:
+        raise RuntimeError(f"CHECK_EQ(num_qo_heads, group_size * num_kv_heads) failed. "
+                           f"{num_qo_heads} vs {group_size * num_kv_heads}")
+    _chk_kv(kv_ptrs, kv_indptr, last_page_offset, batch_size)
+    if tmpbuf.numel() * tmpbuf.element_size() < 4 * (4 * batch_size + 1):
+        raise RuntimeError("CHECK_GE(tmpbuf.nbytes(), sizeof(int32_t) * (4 * batch_size + 1)) failed")
+    try:
+        kvcache.batch_decode_into(o, q, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx, num_kv_heads,
+                                  base, page_size)
+    except RuntimeError as e:
+        raise _no_kernel(e, q, page_size, group_size) from None
+
+
+def init_kv(kv_ptrs: torch.Tensor, kv_indptr: torch.Tensor, last_page_offset: torch.Tensor, k: torch.Tensor,
+            v: torch.Tensor, seqlen_indptr: torch.Tensor, num_layers: int, layer_idx: int, num_kv_heads: int,
+            page_size: int) -> None:
+    """Copies a run of keys/values per request into its pages (init_kv, loquetier_ops.cc:182-228)."""
+    from . import kvcache
+    for t, name in ((k, "k"), (v, "v")):
+        ops._chk_cuda_contig(t, name, 3)
+    if k.shape != v.shape:
+        raise RuntimeError("CHECK_SHAPE(k, v) failed")
+    batch_size = int(last_page_offset.size(0))
+    _chk_kv(kv_ptrs, kv_indptr, last_page_offset, batch_size)
+    ops._chk_cuda_contig(seqlen_indptr, "seqlen_indptr", 1)
+    if seqlen_indptr.size(0) != batch_size + 1:
+        raise RuntimeError(f"CHECK_EQ(seqlen_indptr.size(0), batch_size + 1) failed. "
+                           f"{seqlen_indptr.size(0)} vs {batch_size + 1}")
+    try:
+        kvcache.init_kv_raw(kv_ptrs, kv_indptr, last_page_offset, k, v, seqlen_indptr, num_layers, layer_idx,
+                            num_kv_heads, page_size)
+    except RuntimeError as e:
+        raise _no_kernel(e, k, page_size, 1) from None
+
+
+def append_kv(kv_ptrs: torch.Tensor, kv_indptr: torch.Tensor, last_page_offset: torch.Tensor, k: torch.Tensor,
+              v: torch.Tensor, num_layers: int, layer_idx: int, num_kv_heads: int, page_size: int) -> None:
+    """Writes one new key/value per request into its cache (append_kv, loquetier_ops.cc:230-273)."""
+    from . import kvcache
+    for t, name in ((k, "k"), (v, "v")):
+        ops._chk_cuda_contig(t, name, 3)
+    if k.shape != v.shape:
+        raise RuntimeError("CHECK_SHAPE(k, v) failed")
+    _chk_kv(kv_ptrs, kv_indptr, last_page_offset, int(k.size(0)))
+    try:
+        kvcache.append_kv_raw(kv_ptrs, kv_indptr, last_page_offset, k, v, num_layers, layer_idx, num_kv_heads,
+                              page_size)
+    except RuntimeError as e:
+        raise _no_kernel(e, k, page_size, 1) from None
+
+
 def install_as_loquetier_kernels() -> types.ModuleType:
-    """Make ``import loquetier.ops._kernels`` resolve to this module (only the names of
-    the SMLM path and ``rms_norm`` exist on it)."""
+    """Make ``import loquetier.ops._kernels`` resolve to this module.  It carries the names of the SMLM
+    path, ``rms_norm`` and the decode side of the paged cache (``batch_decode``, ``init_kv``,
+    ``append_kv``); the reference's ``batch_prefill`` is not provided."""
     me = sys.modules[__name__]
     pkg = sys.modules.get("loquetier")
     if pkg is None:

@@ -27,6 +27,10 @@ def lib():
         L.ref_smlm_forward.argtypes = [c_void_p] * 5 + [c_int] * 5 + [c_void_p]
         L.ref_rms_norm.restype = c_int
         L.ref_rms_norm.argtypes = [c_void_p] * 4 + [c_int, c_int, c_float, c_int, c_void_p]
+        L.ref_batch_decode.restype = c_int
+        L.ref_batch_decode.argtypes = [c_void_p] * 6 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]
+        L.ref_append_kv.restype = c_int
+        L.ref_append_kv.argtypes = [c_void_p] * 6 + [c_int] * 6 + [c_void_p]
         _lib = L
     return _lib
 
@@ -59,3 +63,32 @@ def rms_norm(out, rms_out, x, w, eps):
     if not ok:
         raise RuntimeError("No suitable kernel.")
     return out
+
+
+def batch_decode(o, q, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx, num_kv_heads, base):
+    """The reference's decode attention (flashinfer's BatchDecodeWithPagedKVCacheKernel with the adapter's
+    settings); page size 16, head dim 128, group size 1, 4 or 8."""
+    B = int(q.size(0))
+    aux = torch.zeros(4 * (B + 1), dtype=torch.int32, device=q.device)
+    torch.cuda.synchronize()
+    ok = lib().ref_batch_decode(o.data_ptr(), q.data_ptr(), kv_ptrs.data_ptr(), kv_indptr.data_ptr(),
+                                last_page_offset.data_ptr(), aux.data_ptr(), int(num_layers), int(layer_idx),
+                                int(q.size(1)) // int(num_kv_heads), int(num_kv_heads), float(base), B, _code(q),
+                                torch.cuda.current_stream(q.device).cuda_stream)
+    torch.cuda.synchronize()
+    if not ok:
+        raise RuntimeError("No suitable kernel.")
+    return o
+
+
+def append_kv(kv_ptrs, kv_indptr, last_page_offset, k, v, num_layers, layer_idx, num_kv_heads, page_size,
+              seqlen_indptr=None):
+    """The reference's append kernels: one token per request, or (with ``seqlen_indptr``) a run per request."""
+    torch.cuda.synchronize()
+    ok = lib().ref_append_kv(kv_ptrs.data_ptr(), kv_indptr.data_ptr(), last_page_offset.data_ptr(), k.data_ptr(),
+                             v.data_ptr(), None if seqlen_indptr is None else seqlen_indptr.data_ptr(),
+                             int(num_layers), int(layer_idx), int(num_kv_heads), int(page_size),
+                             int(last_page_offset.numel()), _code(k), torch.cuda.current_stream(k.device).cuda_stream)
+    torch.cuda.synchronize()
+    if not ok:
+        raise RuntimeError("No suitable kernel.")

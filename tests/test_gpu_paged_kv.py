@@ -1,0 +1,205 @@
+"""The paged key-value cache on the GPU through the C ABI: appending keys/values (bit-exact) and batch
+decode attention (rtol = atol = 1e-2 for 16-bit storage with fp32 arithmetic) against the CPU oracle,
+and - where oracle/_ref/libref.so has been built - against the reference's own kernels."""
+import numpy as np
+import pytest
+import torch
+
+import ref_cuda
+from helpers import assert_close
+from oracle import attention_oracle as A
+
+pytestmark = pytest.mark.gpu
+DEV = torch.device("cuda:0")
+THETA = 10000.0
+
+
+def _to_dev(pages, indptr, last):
+    pd = [p.to(DEV).contiguous() for p in pages]
+    ptrs = torch.tensor([p.data_ptr() for p in pd], dtype=torch.int64, device=DEV)
+    return pd, ptrs, torch.tensor(indptr, dtype=torch.int32, device=DEV), torch.tensor(last, dtype=torch.int32, device=DEV)
+
+
+def _decode(q, ptrs, ind, last, Lyr, layer, N, P):
+    from loquetier_b200 import kvcache
+    o = torch.full(q.shape, 7.0, dtype=q.dtype, device=DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kvcache.batch_decode_into(o, q, ptrs, ind, last, Lyr, layer, N, THETA, P, status_word=word)
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0, f"fault bits {int(word.item())}"
+    return o
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group,P", [(1, 16), (2, 8), (4, 16), (8, 16), (4, 32), (8, 8)])
+def test_decode_matches_oracle_small_batch_many_splits(dtype, group, P):
+    N, Lyr, layer = 2, 3, 1
+    seqlens = [1, 15, 16, 17, 100, 333, 1000]      # 7 requests x 2 kv heads: the launch cuts them into page ranges
+    pages, indptr, last = A.make_cache(11 + group + P, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(group * 31 + P)
+    q = torch.randn((len(seqlens), N * group, 128), generator=g).to(dtype)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _decode(q.to(DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    want = A.batch_decode(q, pages, indptr, last, layer, THETA)
+    assert_close(o, want, what=f"group {group} page {P}")
+    # bit-exact on a second run: the merge order of the page ranges is fixed
+    o2 = _decode(q.to(DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    assert torch.equal(o, o2)
+
+
+def test_decode_matches_oracle_large_batch_one_range_per_request():
+    """Enough (request, kv head) pairs to fill the machine: no page ranges, no workspace traffic."""
+    from loquetier_b200.cabi import lib
+    N, group, P, Lyr = 8, 4, 16, 1
+    rng = np.random.default_rng(5)
+    seqlens = [int(v) for v in rng.integers(1, 200, size=48)]
+    assert lib.smlm_b200_batch_decode_workspace_bytes(48, 32, 8) < (1 << 20)
+    pages, indptr, last = A.make_cache(21, seqlens, Lyr, N, P, 128, torch.bfloat16)
+    g = torch.Generator().manual_seed(22)
+    q = torch.randn((48, N * group, 128), generator=g).to(torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _decode(q.to(DEV), ptrs, ind, lst, Lyr, 0, N, P)
+    assert_close(o, A.batch_decode(q, pages, indptr, last, 0, THETA), what="48 requests")
+
+
+def test_decode_long_sequence_rotation_stays_accurate():
+    """8000 positions: the rotation is carried by a recurrence between accurate evaluations."""
+    N, group, P = 1, 4, 16
+    pages, indptr, last = A.make_cache(31, [8000, 4097], 1, N, P, 128, torch.bfloat16)
+    g = torch.Generator().manual_seed(32)
+    q = torch.randn((2, 4, 128), generator=g).to(torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _decode(q.to(DEV), ptrs, ind, lst, 1, 0, N, P)
+    assert_close(o, A.batch_decode(q, pages, indptr, last, 0, THETA), what="long")
+
+
+def test_append_and_init_are_bit_exact_and_touch_nothing_else():
+    from loquetier_b200 import kvcache
+    P, N, Lyr, dt = 16, 4, 2, torch.bfloat16
+    seqlens = [17, 3, 32, 16, 1]
+    pages, indptr, last = A.make_cache(41, seqlens, Lyr, N, P, 128, dt)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    g = torch.Generator().manual_seed(42)
+    k, v = torch.randn((5, N, 128), generator=g).to(dt), torch.randn((5, N, 128), generator=g).to(dt)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kvcache.append_kv_raw(ptrs, ind, lst, k.to(DEV), v.to(DEV), Lyr, 1, N, P, status_word=word)
+    A.append_kv(pages, indptr, last, k, v, 1)
+    runs = [4, 3, 20, 16, 1]
+    sind = [0] + list(np.cumsum(runs))
+    k2, v2 = torch.randn((44, N, 128), generator=g).to(dt), torch.randn((44, N, 128), generator=g).to(dt)
+    kvcache.init_kv_raw(ptrs, ind, lst, k2.to(DEV), v2.to(DEV), torch.tensor(sind, dtype=torch.int32, device=DEV), Lyr, 0,
+                        N, P, status_word=word)
+    A.init_kv(pages, indptr, last, k2, v2, sind, 0)
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0
+    for got, want in zip(pd, pages):
+        assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+
+
+def test_reference_named_operators_and_cache_classes_decode_step():
+    """One decode step as the reference's model issues it (mixed_llama.py:176-186 there): reserve a slot per
+    sequence, append the new key/value, attend - with the mirrored KvPool / KvCache / BatchedKvCache and
+    the operators under the reference's names."""
+    from loquetier_b200 import kernels, kvcache
+    dt = torch.bfloat16
+    Lyr, N, G, P = 2, 2, 4, 16
+    pool = kvcache.KvPool(Lyr, N, 128, P, dt, DEV, pages_per_slab=8)
+    lens = [5, 16, 31]
+    g = torch.Generator().manual_seed(51)
+    caches, hist = [], []
+    for L in lens:
+        c = kvcache.KvCache(pool, L)
+        caches.append(c)
+        assert c.num_pages == (L + P - 1) // P and c.ptrs.tolist() == [p.data_ptr() for p in c.pages]
+    assert pool.num_pages == 1 + 1 + 2
+    b0 = kvcache.BatchedKvCache(caches)
+    for layer in range(Lyr):
+        k0 = torch.randn((sum(lens), N, 128), generator=g).to(dt)
+        v0 = torch.randn((sum(lens), N, 128), generator=g).to(dt)
+        hist.append((k0, v0))
+        kvcache.init_kv(b0, k0.to(DEV), v0.to(DEV), torch.tensor([0, 5, 21, 52], dtype=torch.int32, device=DEV), layer)
+    for c in caches:
+        c.acquire_one()                       # 16 -> 17 tokens opens a second page
+    assert [c.seqlen for c in caches] == [6, 17, 32] and caches[1].num_pages == 2
+    b1 = kvcache.BatchedKvCache(caches)
+    assert b1.indptr.tolist() == [0, 1, 3, 5] and b1.last_page_offset.tolist() == [6, 1, 16]
+    layer = 1
+    kn, vn = torch.randn((3, N, 128), generator=g).to(dt), torch.randn((3, N, 128), generator=g).to(dt)
+    q = torch.randn((3, N * G, 128), generator=g).to(dt)
+    kernels.append_kv(b1.ptrs, b1.indptr, b1.last_page_offset, kn.to(DEV), vn.to(DEV), Lyr, layer, N, P)
+    o = kvcache.batch_decode(q.to(DEV), b1, THETA, layer)
+    o_named = torch.empty_like(o)
+    kernels.batch_decode(o_named, q.to(DEV), b1.ptrs, b1.indptr, b1.last_page_offset,
+                         torch.empty(1 << 16, dtype=torch.uint8, device=DEV), Lyr, layer, N, THETA, P)
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_named)
+    # dense answer from the history of that layer
+    k0, v0 = hist[layer]
+    off, want = 0, []
+    for i, L in enumerate(lens):
+        K = torch.cat([k0[off:off + L], kn[i:i + 1]]).double()
+        V = torch.cat([v0[off:off + L], vn[i:i + 1]]).double()
+        off += L
+        qr = A.rope(q[i].double(), torch.full((N * G,), L), THETA)
+        kr = A.rope(K.permute(1, 0, 2), torch.arange(L + 1).expand(N, L + 1), THETA)
+        rows = []
+        for h in range(N * G):
+            p = torch.softmax((kr[h // G] @ qr[h]) / np.sqrt(128), dim=0)
+            rows.append(p @ V[:, h // G, :])
+        want.append(torch.stack(rows))
+    assert_close(o, torch.stack(want), what="decode step")
+    for c in caches:
+        c.release()
+    assert pool.num_pages == 0
+    with pytest.raises(RuntimeError, match="No suitable kernel"):
+        kernels.batch_decode(torch.empty((1, 6, 128), dtype=dt, device=DEV), torch.empty((1, 6, 128), dtype=dt, device=DEV),
+                             b1.ptrs[:1], b1.indptr[:2], b1.last_page_offset[:1],
+                             torch.empty(1 << 16, dtype=torch.uint8, device=DEV), Lyr, 0, 2, THETA, P)   # group 3
+
+
+def test_bad_page_table_is_reported_not_followed():
+    from loquetier_b200 import kvcache
+    P, N = 16, 2
+    pages, indptr, last = A.make_cache(61, [20, 20], 1, N, P, 128, torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    q = torch.randn((2, 8, 128), device=DEV).to(torch.bfloat16)
+    o = torch.zeros_like(q)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    bad = torch.tensor([0, 2, 9], dtype=torch.int32, device=DEV)          # reaches past the 4 pages
+    kvcache.batch_decode_into(o, q, ptrs, bad, lst, 1, 0, N, THETA, P, status_word=word)
+    torch.cuda.synchronize()
+    assert int(word.item()) & 1
+    word.zero_()
+    ptrs2 = ptrs.clone()
+    ptrs2[1] = 0                                                           # a null page
+    kvcache.batch_decode_into(o, q, ptrs2, ind, lst, 1, 0, N, THETA, P, status_word=word)
+    torch.cuda.synchronize()
+    assert int(word.item()) & 2
+
+
+@pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref/libref.so not built")
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group", [1, 4, 8])
+def test_decode_and_append_against_reference_kernels(dtype, group):
+    """Three-way: the reference's flashinfer kernels, this library, the oracle (page size 16, head dim 128)."""
+    from loquetier_b200 import kvcache
+    N, Lyr, layer, P = 2, 2, 1, 16
+    seqlens = [1, 16, 17, 250, 1031]
+    pages, indptr, last = A.make_cache(71 + group, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(72)
+    q = torch.randn((5, N * group, 128), generator=g).to(dtype)
+    kn, vn = torch.randn((5, N, 128), generator=g).to(dtype), torch.randn((5, N, 128), generator=g).to(dtype)
+    pd_ref, ptrs_ref, ind, lst = _to_dev(pages, indptr, last)
+    pd_lib, ptrs_lib, _, _ = _to_dev(pages, indptr, last)
+    ref_cuda.append_kv(ptrs_ref, ind, lst, kn.to(DEV), vn.to(DEV), Lyr, layer, N, P)
+    kvcache.append_kv_raw(ptrs_lib, ind, lst, kn.to(DEV), vn.to(DEV), Lyr, layer, N, P)
+    A.append_kv(pages, indptr, last, kn, vn, layer)
+    torch.cuda.synchronize()
+    for a, b, c in zip(pd_ref, pd_lib, pages):
+        assert torch.equal(a, b) and torch.equal(a.cpu().view(torch.int16), c.view(torch.int16))
+    o_ref = torch.zeros((5, N * group, 128), dtype=dtype, device=DEV)
+    ref_cuda.batch_decode(o_ref, q.to(DEV), ptrs_ref, ind, lst, Lyr, layer, N, THETA)
+    o_lib = _decode(q.to(DEV), ptrs_lib, ind, lst, Lyr, layer, N, P)
+    want = A.batch_decode(q, pages, indptr, last, layer, THETA)
+    assert_close(o_ref, want, what="reference kernel vs oracle")
+    assert_close(o_lib, o_ref, what="library vs reference kernel")

@@ -15,7 +15,8 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_library_loads_and_exports_every_declared_symbol():
-    hdr = open(os.path.join(ROOT, "include", "smlm_b200.h")).read()
+    hdr = "".join(open(os.path.join(ROOT, "include", f)).read() for f in sorted(os.listdir(os.path.join(ROOT, "include")))
+                  if f.endswith(".h"))
     declared = sorted(set(re.findall(r"\b(smlm_b200_\w+)\s*\(", hdr)))
     assert len(declared) >= 9
     from loquetier_b200 import cabi
