@@ -16,7 +16,6 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import assert_close
 
 
 def _problem(seed, part, h, rank, dtype, dev):
@@ -53,8 +52,8 @@ def _run_both(seed, part, h, rank, dtype, transposed, grad_fp32):
     torch.cuda.synchronize()
     plan.raise_if_failed()
     for i, (g_, w_) in enumerate(zip(got, want)):
-        s = max(1.0, float(w_.float().abs().max()))
-        assert_close(g_, w_, rtol=1e-2, atol=1e-2 * s, what=f"partition {i}")
+        # the same kernel adds the same partial sums in the same order whichever workspace it is given
+        assert torch.equal(g_, w_), f"partition {i}: built-in scratch and caller workspace disagree"
         assert not (g_ == 9.0).all() or part[i + 1] == part[i]
 
 
@@ -65,7 +64,9 @@ def test_static_scratch_matches_caller_workspace_two_calls_in_a_row():
     _run_both(11, [0, 700, 700, 733, 1500], 1024, 16, torch.bfloat16, transposed=True, grad_fp32=False)
     # straight after it, a different problem on the same shared array
     _run_both(12, [0, 5, 1300], 1536, 32, torch.float16, transposed=False, grad_fp32=True)
-    # and the first one again: leftovers of the second call must not matter
+    # rank 64 runs the tcgen05 variant of the kernel, with its own cut of the shared array
+    _run_both(13, [0, 400, 400, 690], 1024, 64, torch.bfloat16, transposed=True, grad_fp32=False)
+    # and the first one again: leftovers of the other calls must not matter
     _run_both(11, [0, 700, 700, 733, 1500], 1024, 16, torch.bfloat16, transposed=True, grad_fp32=False)
 
 
