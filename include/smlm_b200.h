@@ -233,8 +233,10 @@ int smlm_b200_bwd(void* dx, void* const* dA_table, void* const* dB_table, void* 
  * (kernel_utils.py:118-119 inside MixedLoraLinear.forward, mixed_lora.py:198).  Projections that share
  * the batch - q/k/v or gate/up of a layer, or every LoRA target when their inputs are at hand - also
  * share the segment plan, the adapter ids, the rank and the scales, so their launches can be laid end
- * to end in one grid: short launches then stop paying a set-up and a drain each.  Results are those of
- * the single-projection entry points, bit for bit.
+ * to end in one grid: short launches then stop paying a set-up and a drain each.  The function
+ * computed is that of the single-projection entry points; how a sum over the hidden dimension is cut
+ * over the CTAs of a cluster is chosen per launch, so v / dV can differ from a single-projection call
+ * in the last bit of a sum.
  *
  * `projs` is a HOST array of nproj <= SMLM_MAX_PROJ descriptors; only the fields an entry point names
  * are read.  The projections must not depend on one another: none may read or write what another

@@ -359,8 +359,9 @@ int run_fused(const FusedJobDesc* jobs, int njobs, const int32_t* ids, const flo
 // ---- wgrad ------------------------------------------------------------------
 
 template <typename T, int RT>
-int launch_wgrad(const WgradArgs& a, const WgradMaps& tm, int ncta, cudaStream_t stream) {
-  return launch(wgrad_kernel<T, RT>, dim3(ncta, 1, 1), kWgThreads, 1, WgradSmem<RT>::kTotal, stream, a, tm);
+int launch_wgrad(const WgradArgs& a, const WgradMaps& tm, int groups, cudaStream_t stream) {
+  return launch(wgrad_kernel<T, RT>, dim3(groups, a.slabs_total, 1), kWgThreads, 1, WgradSmem<RT>::kTotal, stream, a,
+                tm);
 }
 
 struct WgradJobDesc {
@@ -379,9 +380,7 @@ inline int wgrad_rt(int R) {
 
 // How a batch of T token rows in npart partitions is cut for the jobs' column counts.
 struct WgradShape {
-  int slab, slabs_total;
-  int group, groups;   // the tcgen05 kernel: pieces per CTA and CTAs per slab
-  int ncta;            // the mma.sync kernel: CTAs of the launch
+  int slab, slabs_total, group, groups;
   size_t ticket_bytes, scratch_bytes;
 };
 
@@ -400,36 +399,25 @@ WgradShape wgrad_shape(int T, int npart, int R, const int* h, int nh, bool tc) {
   for (int i = 0; i < nh; ++i)
     if (h[i] > 0) s.slabs_total += (h[i] + s.slab - 1) / s.slab;
   const int mp = std::max(1, max_pieces_of(T, npart));
-  s.group = s.groups = 1;
-  s.ncta = 1;
-  if (tc) {
-    // One CTA per SM.  The group size (pieces per CTA) that minimises  rounds of CTAs x (pieces per
-    // CTA + a fixed cost of about two pieces for set-up and closing runs).
-    long long best = -1, g = 1;
-    for (int c = 1; c <= kWgMaxGroup; ++c) {
-      const long long ctas = static_cast<long long>((mp + c - 1) / c) * s.slabs_total;
-      const long long cost = ((ctas + kNumSMs - 1) / kNumSMs) * (c + 2);
-      if (best < 0 || cost < best) {
-        best = cost;
-        g = c;
-      }
+  // CTAs that run side by side: one per SM for the tcgen05 kernel, two for the other.  The group
+  // size (pieces per CTA) that minimises  rounds of CTAs x (pieces per CTA + a fixed cost for set-up
+  // and closing runs, worth about two pieces of the tcgen05 kernel's 512-column slabs and four of the
+  // other's 256-column ones); a launch with fewer CTAs than slots takes one round.
+  const long long slots = tc ? kNumSMs : 2 * kNumSMs;
+  const int fixed = tc ? 2 : 4;
+  long long best = -1, g = 1;
+  for (int c = 1; c <= kWgMaxGroup; ++c) {
+    const long long ctas = static_cast<long long>((mp + c - 1) / c) * s.slabs_total;
+    const long long cost = ((ctas + slots - 1) / slots) * (c + fixed);
+    if (best < 0 || cost < best) {
+      best = cost;
+      g = c;
     }
-    s.group = static_cast<int>(g);
-    s.groups = (mp + s.group - 1) / s.group;
-    s.scratch_bytes = static_cast<size_t>(s.groups) * 2 * s.slabs_total * (rt * 16) * s.slab * sizeof(float);
-  } else {
-    // Two CTAs per SM.  The (slab, piece) items are dealt out evenly over whole rounds of CTAs; as many
-    // rounds as keep about a dozen items per CTA (fewer items cost more set-up and parked partial
-    // sums per byte streamed), and never more than kWgMaxGroup items per CTA.
-    const long long items = static_cast<long long>(mp) * s.slabs_total;
-    const long long slots = 2 * kNumSMs;
-    long long rounds = std::max(1LL, (items + slots * 12 - 1) / (slots * 12));
-    long long ncta = std::min(items, slots * rounds);
-    ncta = std::max(ncta, (items + kWgMaxGroup - 1) / kWgMaxGroup);
-    s.ncta = static_cast<int>(std::max(1LL, ncta));
-    s.scratch_bytes = static_cast<size_t>(s.ncta) * 2 * (rt * 16) * s.slab * sizeof(float);
   }
+  s.group = static_cast<int>(g);
+  s.groups = (mp + s.group - 1) / s.group;
   s.ticket_bytes = (static_cast<size_t>(npart) * s.slabs_total * 4 * sizeof(int) + 255) / 256 * 256;
+  s.scratch_bytes = static_cast<size_t>(s.groups) * 2 * s.slabs_total * (rt * 16) * s.slab * sizeof(float);
   return s;
 }
 
@@ -485,15 +473,15 @@ int run_wgrad(const WgradJobDesc* jobs, int njobs, const int32_t* part_indptr, c
                             a, tcm);
   }
   if (dtype == SMLM_F16) {
-    if (rt == 1) return launch_wgrad<__half, 1>(a, tm, sh.ncta, stream);
-    if (rt == 2) return launch_wgrad<__half, 2>(a, tm, sh.ncta, stream);
-    if (rt == 4) return launch_wgrad<__half, 4>(a, tm, sh.ncta, stream);
-    return launch_wgrad<__half, 8>(a, tm, sh.ncta, stream);
+    if (rt == 1) return launch_wgrad<__half, 1>(a, tm, sh.groups, stream);
+    if (rt == 2) return launch_wgrad<__half, 2>(a, tm, sh.groups, stream);
+    if (rt == 4) return launch_wgrad<__half, 4>(a, tm, sh.groups, stream);
+    return launch_wgrad<__half, 8>(a, tm, sh.groups, stream);
   }
-  if (rt == 1) return launch_wgrad<__nv_bfloat16, 1>(a, tm, sh.ncta, stream);
-  if (rt == 2) return launch_wgrad<__nv_bfloat16, 2>(a, tm, sh.ncta, stream);
-  if (rt == 4) return launch_wgrad<__nv_bfloat16, 4>(a, tm, sh.ncta, stream);
-  return launch_wgrad<__nv_bfloat16, 8>(a, tm, sh.ncta, stream);
+  if (rt == 1) return launch_wgrad<__nv_bfloat16, 1>(a, tm, sh.groups, stream);
+  if (rt == 2) return launch_wgrad<__nv_bfloat16, 2>(a, tm, sh.groups, stream);
+  if (rt == 4) return launch_wgrad<__nv_bfloat16, 4>(a, tm, sh.groups, stream);
+  return launch_wgrad<__nv_bfloat16, 8>(a, tm, sh.groups, stream);
 }
 
 // Workspace that serves either kernel variant, so that a buffer sized before a change of the

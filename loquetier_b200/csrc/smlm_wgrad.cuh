@@ -1,7 +1,7 @@
 // Per-partition weight gradients  G_p = scale * P[rows_p, :R]^T . Q[rows_p, :H]
 // with R the LoRA rank (<= 128), H a hidden size, rows_p the token rows of train
-// partition p.  One launch runs several such jobs side by side - dB and dA of one
-// projection, or of all projections of a layer.
+// partition p.  One launch runs up to two such jobs side by side, which is how
+// the backward computes dB and dA together.
 //
 // The reference has no native backward (kernel_src/csrc/loquetier_ops.cc:321-322);
 // it forms these products with torch matmuls per partition
@@ -11,12 +11,8 @@
 // transposed); the math layout swaps the two.
 //
 // Work is cut by tokens, not by partitions, so that one very long partition next
-// to many short ones still spreads evenly: a work item is one piece of the partition
-// plan (64 tokens) times one slab of Q's columns, the items of all jobs are laid out
-// slab by slab, and the launch deals them out evenly - every CTA owns one contiguous
-// run of items, so that all CTAs carry the same load whatever the number of slabs
-// and pieces (a grid of whole slabs times whole groups of pieces left up to a fifth
-// of the machine idle in its last round).  A CTA streams its
+// to many short ones still spreads evenly: a CTA owns `G` consecutive pieces of
+// the partition plan (64 tokens each) and one slab of Q's columns.  It streams its
 // Q tiles - the HBM-bound read - through a ring of shared-memory stages fed by a
 // producer warp with TMA ([16 tokens x 64 columns] tiled tensor copies with the
 // 128-byte swizzle, issued so that each token row's consecutive chunks are requested
@@ -28,7 +24,7 @@
 // a run that holds a whole partition is written out directly; otherwise the warp
 // parks its fp32 partial sums in the caller's workspace and takes a ticket; the
 // warp that draws the last ticket of a (partition, slab) adds all parked partials
-// in CTA order - a fixed order, so results are deterministic - and writes G.
+// in group order - a fixed order, so results are deterministic - and writes G.
 // Nobody waits on anybody: there is no spin loop and no atomic on data.
 #pragma once
 #include <cuda.h>
@@ -56,7 +52,7 @@ struct WgradSmem {
   static constexpr int kStage = kQBytes + kPBytes;
   static constexpr int kRing = kWgStages * kStage;
   static constexpr int kStageOff = kRing;                      // per warp [KP][CW] fp32
-  // Piece[kWgMaxGroup], int2 bounds[kWgMaxGroup], void* gout[kWgMaxGroup], float scale[kWgMaxGroup], int slab[kWgMaxGroup]
+  // Piece[kWgMaxGroup], int2 bounds[kWgMaxGroup], void* gout[kWgMaxGroup], float scale[kWgMaxGroup]
   static constexpr int kPieceOff = kStageOff + KP * SLAB * 4;
   static constexpr int kBarOff = kPieceOff + kWgMaxGroup * 40;
   static constexpr int kTotal = kBarOff + 2 * kWgStages * 8 + 1024;
@@ -82,13 +78,12 @@ struct WgradArgs {
   const float* scale;          // per partition (ids == null) or per adapter, or null
   const int32_t* ids;          // per-partition adapter index for `scale`, or null
   int* plan;                   // plan built on part_indptr: header + pieces
-  int* tickets;                // [npart][slabs of all jobs][4 warps], zero between launches
-  float* scratch;              // parked partial sums: wgrad_kernel [CTAs][2][KP * SLAB],
-                               // wgrad_tc_kernel [groups][2][slabs of all jobs][KP * SLAB]
+  int* tickets;                // [npart][slabs of both jobs][4 warps], zero between launches
+  float* scratch;              // [groups][2][slabs of both jobs][KP * SLAB]
   int n_table;
   int npart, T;
   int R;
-  int group;                   // wgrad_tc_kernel: pieces per CTA (G)
+  int group;                   // pieces per CTA (G)
   int accumulate;              // G += instead of G =
   int out_fp32;                // G holds fp32 instead of the operand type
   int independent;             // 1: reads nothing the previous kernel of the stream wrote, and
@@ -98,11 +93,6 @@ struct WgradArgs {
 struct WgradMaps {
   CUtensorMap q[kWgMaxJobs];  // Q of every job: boxes of 16 tokens x 64 columns
 };
-
-// Which CTA of a balanced launch handles work item i: CTA c owns items [c * total / ncta, (c + 1) * total / ncta).
-__device__ __forceinline__ int wg_cta_of(long long item, int ncta, long long total) {
-  return static_cast<int>(((item + 1) * ncta + total - 1) / total) - 1;
-}
 
 template <typename T, int RT>
 __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant__ WgradArgs a,
@@ -117,23 +107,31 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int cta = blockIdx.x;
-  const int ncta = gridDim.x;
+  const int G = a.group;
+  const int grp = blockIdx.x;
   const int slabs_total = a.slabs_total;
+  const int slab_global = blockIdx.y;
+  int ji = 0;
+  for (int j = 1; j < a.njobs; ++j)
+    if (slab_global >= a.job[j].slab_begin) ji = j;
+  const WgradJob& jb = a.job[ji];
+  void* const* g_table = jb.g_table;
+  const T* P = static_cast<const T*>(jb.p);
+  const int H = jb.H;
+  const int transposed = jb.transposed;
+  const int use_scale = jb.use_scale;
+  const int col0 = (slab_global - jb.slab_begin) * SLAB;
   const int R = a.R;
+  const int ncols = min(SLAB, H - col0);
   int* err = a.plan + 1;
 
   // dependent launches wait for their predecessor here; independent ones overlap with it and
   // wait just before they exit, so that completion stays in stream order
   if (!a.independent) pdl_wait();
   pdl_trigger();
-  // Work items are (slab, piece) pairs in slab-major order; the launch deals them out evenly, so a
-  // CTA's share is one contiguous run of items - usually part of one slab, sometimes the end of one
-  // and the start of the next.
   const int count = a.plan[0];
-  const long long total = static_cast<long long>(slabs_total) * count;
-  const long long ibeg = total * cta / ncta;
-  const int np = static_cast<int>(min(static_cast<long long>(kWgMaxGroup), total * (cta + 1) / ncta - ibeg));
+  const int pbeg = grp * G;
+  const int np = max(0, min(count, pbeg + G) - pbeg);  // pieces of this CTA
 
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -142,60 +140,39 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
   int2* bounds = reinterpret_cast<int2*>(smem + SM::kPieceOff + kWgMaxGroup * 16);
   void** gouts = reinterpret_cast<void**>(smem + SM::kPieceOff + kWgMaxGroup * 24);
   float* scales = reinterpret_cast<float*>(smem + SM::kPieceOff + kWgMaxGroup * 32);
-  int* slabof = reinterpret_cast<int*>(smem + SM::kPieceOff + kWgMaxGroup * 36);   // slab | job << 24
   const uint32_t full0 = base + SM::kBarOff;
   const uint32_t empty0 = full0 + S * 8;
 
-  auto job_of = [&](int slab) {
-    int ji = 0;
-    for (int j = 1; j < a.njobs; ++j)
-      if (slab >= a.job[j].slab_begin) ji = j;
-    return ji;
-  };
-
-  // gradients of partitions without tokens own no piece: the first CTAs clear them, slab by slab
-  if (!a.accumulate) {
-    for (int slab = cta; slab < slabs_total; slab += ncta) {
-      const WgradJob& jb = a.job[job_of(slab)];
-      const int col0 = (slab - jb.slab_begin) * SLAB;
-      const int ncols = min(SLAB, jb.H - col0);
-      for (int p = warp; p < a.npart; p += kWgThreads / 32) {
-        const int ra = a.part_indptr[p], rb = a.part_indptr[p + 1];
-        void* gout = jb.g_table[p];
-        if (rb != ra || gout == nullptr) continue;
-        for (int e = lane; e < R * ncols; e += 32) {
-          int r, c;
-          if (jb.transposed) { c = e / R; r = e - c * R; } else { r = e / ncols; c = e - r * ncols; }
-          const size_t off = jb.transposed ? static_cast<size_t>(col0 + c) * R + r
-                                           : static_cast<size_t>(r) * jb.H + col0 + c;
-          if (a.out_fp32) static_cast<float*>(gout)[off] = 0.f;
-          else static_cast<T*>(gout)[off] = static_cast<T>(0.f);
-        }
+  // the first group also clears the gradients of partitions without tokens (they own no piece)
+  if (grp == 0 && !a.accumulate) {
+    for (int p = warp; p < a.npart; p += kWgThreads / 32) {
+      const int ra = a.part_indptr[p], rb = a.part_indptr[p + 1];
+      void* gout = g_table[p];
+      if (rb != ra || gout == nullptr) continue;
+      for (int e = lane; e < R * ncols; e += 32) {
+        int r, c;
+        if (transposed) { c = e / R; r = e - c * R; } else { r = e / ncols; c = e - r * ncols; }
+        const size_t off = transposed ? static_cast<size_t>(col0 + c) * R + r : static_cast<size_t>(r) * H + col0 + c;
+        if (a.out_fp32) static_cast<float*>(gout)[off] = 0.f;
+        else static_cast<T*>(gout)[off] = static_cast<T>(0.f);
       }
     }
   }
-  if (np <= 0) {
+  if (np == 0) {
     if (a.independent) pdl_wait();
     return;
   }
 
   if (tid < np) {
-    const long long item = ibeg + tid;
-    const int slab = static_cast<int>(item / count);
-    const int piece = static_cast<int>(item - static_cast<long long>(slab) * count);
-    const int ji = job_of(slab);
-    const WgradJob& jb = a.job[ji];
-    Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[piece];
+    Piece pc = reinterpret_cast<const Piece*>(a.plan + kPlanHeaderInts)[pbeg + tid];
     if (pc.pad != 0) {  // a gather piece of a grouped plan: not a row range of one partition
       atomicOr(err, kErrGrouped);
       pc.row0 = 0; pc.nrows = 0; pc.seg = 0;
     }
-    pc.pad = piece;   // the field is free from here on: the piece's index in the plan
     pcs[tid] = pc;
     bounds[tid] = make_int2(a.part_indptr[pc.seg], a.part_indptr[pc.seg + 1]);
-    gouts[tid] = jb.g_table[pc.seg];
-    scales[tid] = jb.use_scale ? adapter_scale(a.scale, a.ids, a.n_table, pc.seg) : 1.0f;
-    slabof[tid] = slab | (ji << 24);
+    gouts[tid] = g_table[pc.seg];
+    scales[tid] = use_scale ? adapter_scale(a.scale, a.ids, a.n_table, pc.seg) : 1.0f;
   }
   if (tid == 0) {
 #pragma unroll
@@ -208,19 +185,15 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
   __syncthreads();
 
   bool dead = false;
+  const int nch = (ncols + 63) >> 6;
 
   if (warp == 4) {
-    // ---------------- producer: one stage per item ----------------
+    // ---------------- producer: one stage per piece ----------------
     for (int it = 0; it < np; ++it) {
       const int slot = it % S;
       const int t0 = pcs[it].row0;
       const int ntok = pcs[it].nrows;
       const int nblk = (ntok + 15) >> 4;
-      const int slab = slabof[it] & 0xffffff, ji = slabof[it] >> 24;
-      const WgradJob& jb = a.job[ji];
-      const int col0 = (slab - jb.slab_begin) * SLAB;
-      const int nch = (min(SLAB, jb.H - col0) + 63) >> 6;
-      const T* P = static_cast<const T*>(jb.p);
       const uint32_t qs = base + slot * SM::kStage;
       const uint32_t ps = qs + SM::kQBytes;
       const uint32_t fb = full0 + slot * 8;
@@ -228,7 +201,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
       const uint32_t pbytes = static_cast<uint32_t>(ntok) * R * 2;
       if (lane == 0) {
         mbar_expect_tx(fb, 2048u * nblk * nch + pbytes);
-        if (pbytes > 0) bulk_load(ps, P + static_cast<size_t>(t0) * R, pbytes, fb);
+        bulk_load(ps, P + static_cast<size_t>(t0) * R, pbytes, fb);
       }
       __syncwarp();
       for (int i = lane; i < nblk * nch; i += 32) {
@@ -243,6 +216,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
   const int wcol = warp * CW;
   const int ch = wcol >> 6;          // 64-column chunk holding this warp's columns
   const int c0 = (wcol & 63) >> 3;   // first 16-byte chunk inside it
+  const bool active = wcol < ncols;
 
   float acc[RT][NTW][4];
 #pragma unroll
@@ -254,6 +228,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
   // everything after (output, parking, adding parked partials) runs as short plain loops
   float* st = reinterpret_cast<float*>(smem + SM::kStageOff) + warp * (SM::KP * CW);
   constexpr int kWarpFloats = SM::KP * CW;
+  const int cwv = min(CW, ncols - wcol);  // this warp's columns that exist
 
   auto stage_acc = [&]() {
     const int g = lane >> 2, t = lane & 3;
@@ -269,40 +244,21 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
     __syncwarp();
   };
 
-  // the run's place: job, first column, columns that exist, this warp's share of them
-  struct RunGeo {
-    int H, transposed, col0, ncols, cwv;
-    bool active;
-  };
-  auto geo_of = [&](int i) {
-    RunGeo g;
-    const int slab = slabof[i] & 0xffffff;
-    const WgradJob& jb = a.job[slabof[i] >> 24];
-    g.H = jb.H;
-    g.transposed = jb.transposed;
-    g.col0 = (slab - jb.slab_begin) * SLAB;
-    g.ncols = min(SLAB, jb.H - g.col0);
-    g.active = wcol < g.ncols;
-    g.cwv = min(CW, g.ncols - wcol);
-    return g;
-  };
-
   // writes this warp's columns of G from the staging block; i0 = a piece of the partition
-  auto emit = [&](int i0, const RunGeo& geo) {
+  auto emit = [&](int i0) {
     void* gout = gouts[i0];
     if (gout == nullptr || (reinterpret_cast<uintptr_t>(gout) & 15) != 0) {
       if (lane == 0) atomicOr(err, kErrBadPointer);
       return;
     }
     const float sc = scales[i0];
-    const int H = geo.H, col0 = geo.col0, cwv = geo.cwv;
     // eight consecutive output elements per lane and step: 16-byte (or 2 x 16-byte fp32) stores
     const int r8 = R >> 3, c8 = (cwv + 7) >> 3;
-    const int total_e = geo.transposed ? cwv * r8 : R * c8;
-    for (int e = lane; e < total_e; e += 32) {
+    const int total = transposed ? cwv * r8 : R * c8;
+    for (int e = lane; e < total; e += 32) {
       float v[8];
       size_t off;
-      if (geo.transposed) {  // G[H][R]: column c, ranks rh*8 .. rh*8+7
+      if (transposed) {  // G[H][R]: column c, ranks rh*8 .. rh*8+7
         const int c = e / r8, rh = e - c * r8;
 #pragma unroll
         for (int k = 0; k < 8; ++k) v[k] = st[(rh * 8 + k) * CW + c] * sc;
@@ -337,38 +293,34 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
     }
   };
 
-  // closes the run of items [i0, i1] (indices inside this CTA): one partition, one slab
+  // closes the run of pieces [i0, i1] (indices inside this CTA), all of partition p
   auto close_run = [&](int i0, int i1) {
-    const RunGeo geo = geo_of(i0);
     const int p = pcs[i0].seg;
     const int ra = bounds[i0].x, rb = bounds[i0].y;
     const bool starts = pcs[i0].row0 == ra;
     const bool ends = pcs[i1].row0 + pcs[i1].nrows == rb;
     stage_acc();
-    if (!geo.active) return;
+    if (!active) return;
     if (starts && ends) {
-      emit(i0, geo);
+      emit(i0);
     } else {
-      // the partition's pieces are consecutive in the plan, hence its items in this slab are too;
-      // which CTAs hold them?
+      // the partition's pieces are consecutive in the plan; which groups hold them?
       const int bm = a.plan[3];
-      const int slab = slabof[i0] & 0xffffff;
-      const int first_piece = pcs[i0].pad - (pcs[i0].row0 - ra) / bm;
+      const int first_piece = pbeg + i0 - (pcs[i0].row0 - ra) / bm;
       const int last_piece = first_piece + (rb - ra + bm - 1) / bm - 1;
-      const long long sbase = static_cast<long long>(slab) * count;
-      const int first_c = wg_cta_of(sbase + first_piece, ncta, total);
-      const int last_c = wg_cta_of(sbase + last_piece, ncta, total);
-      float* mine = a.scratch + static_cast<size_t>(cta * 2 + (starts ? 1 : 0)) * SM::kPartialFloats + warp * kWarpFloats;
+      const int first_g = first_piece / G, last_g = last_piece / G;
+      float* mine = a.scratch + (static_cast<size_t>(grp * 2 + (starts ? 1 : 0)) * slabs_total + slab_global) *
+                                    SM::kPartialFloats + warp * kWarpFloats;
       for (int e = lane * 4; e < kWarpFloats; e += 128)
         *reinterpret_cast<float4*>(mine + e) = *reinterpret_cast<const float4*>(st + e);
       __threadfence();
       __syncwarp();
-      int* ticket = a.tickets + (static_cast<size_t>(p) * slabs_total + slab) * 4 + warp;
+      int* ticket = a.tickets + (static_cast<size_t>(p) * slabs_total + slab_global) * 4 + warp;
       int old = 0;
       if (lane == 0) old = atomicAdd(ticket, 1);
       old = __shfl_sync(0xffffffffu, old, 0);
-      if (old == last_c - first_c) {
-        // last contributor: add every CTA's partial in CTA order (loads of one CTA's partial are
+      if (old == last_g - first_g) {
+        // last contributor: add every group's partial in group order (loads of one group are
         // independent of each other and overlap)
         __threadfence();
         constexpr int NV = kWarpFloats / 128;
@@ -376,9 +328,9 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
 #pragma unroll
         for (int q = 0; q < NV; ++q) s4[q] = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 2
-        for (int cc = first_c; cc <= last_c; ++cc) {
-          const float* src = a.scratch + static_cast<size_t>(cc * 2 + (cc == first_c ? 1 : 0)) * SM::kPartialFloats +
-                             warp * kWarpFloats + lane * 4;
+        for (int gg = first_g; gg <= last_g; ++gg) {
+          const float* src = a.scratch + (static_cast<size_t>(gg * 2 + (gg == first_g ? 1 : 0)) * slabs_total +
+                                          slab_global) * SM::kPartialFloats + warp * kWarpFloats + lane * 4;
           float4 v[NV];
 #pragma unroll
           for (int q = 0; q < NV; ++q) v[q] = __ldcg(reinterpret_cast<const float4*>(src + q * 128));
@@ -393,7 +345,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
 #pragma unroll
         for (int q = 0; q < NV; ++q) *reinterpret_cast<float4*>(st + q * 128 + lane * 4) = s4[q];
         __syncwarp();
-        emit(i0, geo);
+        emit(i0);
         if (lane == 0) *ticket = 0;  // leave the workspace ready for the next launch
       }
     }
@@ -406,7 +358,6 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
     const uint32_t qs = base + slot * SM::kStage;
     const uint32_t ps = qs + SM::kQBytes;
     mbar_wait(full0 + slot * 8, (it / S) & 1, err, dead);
-    const bool active = geo_of(it).active;
     if (active) {
       const int ntok = pcs[it].nrows;
       const int kmax = (ntok + 15) >> 4;
@@ -460,7 +411,7 @@ __global__ void __launch_bounds__(kWgThreads) wgrad_kernel(const __grid_constant
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + slot * 8);
-    if (it + 1 == np || pcs[it + 1].seg != pcs[it].seg || slabof[it + 1] != slabof[it]) {
+    if (it + 1 == np || pcs[it + 1].seg != pcs[it].seg) {
       close_run(run0, it);
       run0 = it + 1;
     }
