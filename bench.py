@@ -1079,6 +1079,7 @@ def main():
     ap.add_argument("--only", default="", help="comma-separated projection names: restrict the workload "
                                                "(for profiler captures of one shape)")
     ap.add_argument("--no-group", action="store_true", help="plan without grouping short segments by adapter")
+    ap.add_argument("--ks", type=int, default=0, help="force the cluster split of the fused kernel (measurements)")
     ap.add_argument("--seg-len", type=int, default=0, help="c5 only: tokens per segment instead of 2048 "
                                                           "(a smaller footprint for profiler captures)")
     a = ap.parse_args()
@@ -1178,6 +1179,9 @@ def main():
             print(json.dumps(line))
         return
 
+    if a.ks:
+        from loquetier_b200 import ops as _ops
+        _ops.set_cluster_split(a.ks)
     wl = Workload(spec, dev)
     wl.overlap = not a.no_overlap
     wl.grouped = not a.no_group

@@ -80,6 +80,13 @@ int smlm_b200_piece_rows(int T);
  * accumulation, V rounded to the storage type between the products). */
 int smlm_b200_set_tensor_core_mode(int mode);
 
+/* Tuning knob of the mma.sync fused kernel, for measurements: a piece (up to 64 rows of one segment)
+ * is served by a cluster of 1..4 CTAs that split the hidden dimension; 0 (default) lets the library
+ * choose per launch from the batch shape, 1..4 forces the split.  No reference counterpart.
+ * Process-wide; returns the previous setting.  Results are the same function either way (sums over
+ * the hidden dimension are cut differently). */
+int smlm_b200_set_cluster_split(int split);
+
 /* Bytes of the plan buffer for a batch of T token rows in nseg segments. */
 size_t smlm_b200_plan_bytes(int T, int nseg);
 

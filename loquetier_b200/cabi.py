@@ -41,6 +41,7 @@ SIGNATURES = {
     "smlm_b200_merge_segments": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "smlm_b200_piece_rows": (c_int, [c_int]),
     "smlm_b200_set_tensor_core_mode": (c_int, [c_int]),
+    "smlm_b200_set_cluster_split": (c_int, [c_int]),
     "smlm_b200_plan_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_plan": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p]),
     "smlm_b200_plan_grouped": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

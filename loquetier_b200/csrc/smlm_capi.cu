@@ -210,6 +210,8 @@ int dispatch_fused_r(const FusedArgs& a, const FusedMapsN& tm, int ctas, bool gr
 // ---- the tcgen05 variant for ranks above 32 ----------------------------------
 // 0: chosen by shape, 1: wherever the kernel applies, -1: never
 std::atomic<int> g_tensor_core_mode{0};
+// 0: the cluster split of the fused kernel is chosen by the cost model; 1..4: forced
+std::atomic<int> g_cluster_split{0};
 
 template <typename T, int R16, bool RM>
 int launch_tc(const TcArgs& a, const TcMaps& tm, int max_tall, cudaStream_t stream) {
@@ -315,10 +317,29 @@ int run_fused(const FusedJobDesc* jobs, int njobs, const int32_t* ids, const flo
         ks = k;
       }
     }
+    {
+      const int forced = g_cluster_split.load(std::memory_order_relaxed);
+      if (forced > 0) ks = forced;
+    }
     FusedArgs a;
     FusedMapsN tm;
     a.ids = ids; a.scale = scale; a.plan = static_cast<int*>(plan);
-    a.n_table = n_table; a.R = R; a.ksplit = ks; a.ctas_per_job = mp * ks; a.scale_mid = scale_mid;
+    a.n_table = n_table; a.R = R; a.ksplit = ks; a.scale_mid = scale_mid;
+    // groups: runs of jobs with the same K1 + N2 (the caller sorted the jobs by it)
+    a.ngroups = 0;
+    for (int j = 0; j < nj; ++j) {
+      const FusedJobDesc& d = jobs[j0 + j];
+      if (j == 0 || static_cast<long long>(d.K1) + d.N2 !=
+                        static_cast<long long>(jobs[j0 + j - 1].K1) + jobs[j0 + j - 1].N2) {
+        a.grp_job_begin[a.ngroups] = j;
+        a.grp_cta_begin[a.ngroups] = j * mp * ks;
+        ++a.ngroups;
+      }
+    }
+    for (int g = a.ngroups; g <= kFusedMaxJobs; ++g) {
+      a.grp_job_begin[g] = nj;
+      a.grp_cta_begin[g] = nj * mp * ks;
+    }
     a.independent = (independent || j0 > 0) ? 1 : 0;
     a.mode = mode;
     for (int j = 0; j < kFusedMaxJobs; ++j) {
@@ -775,6 +796,11 @@ int smlm_b200_gemm(void* y, const void* x, const void* const* w_table, const int
   const FusedJobDesc job = {y, const_cast<void*>(x), nullptr, nullptr, w_table, 64, d_out, accumulate};
   return run_fused(&job, 1, seg_ids, seg_scale, plan, n_table, T, nseg, d_in, dtype, is_row_major, 0, 0,
                    kFusedExpandOnly, grouped, st);
+}
+
+int smlm_b200_set_cluster_split(int split) {
+  const int v = split < 0 ? 0 : (split > 4 ? 4 : split);
+  return g_cluster_split.exchange(v, std::memory_order_relaxed);
 }
 
 int smlm_b200_set_tensor_core_mode(int mode) {

@@ -135,7 +135,14 @@ struct FusedArgs {
   int n_table;
   int R;
   int ksplit;
-  int ctas_per_job;             // CTAs of the grid per job (plan capacity x ksplit)
+  // The grid is cut into groups of jobs of the same size; inside a group the jobs' pieces alternate
+  // (cluster c of a group of n jobs serves job c % n, piece c / n), so that CTAs resident side by
+  // side belong to different jobs - a projection that mostly writes next to one that mostly reads -
+  // and both directions of HBM stay busy.  Groups are ordered longest job first, so that the launch
+  // ends on its shortest CTAs.
+  int ngroups;
+  int grp_cta_begin[kFusedMaxJobs + 1];   // first CTA of every group (and the end of the grid)
+  int grp_job_begin[kFusedMaxJobs + 1];   // first job of every group (and the number of jobs)
   int scale_mid;                // 1: the scale multiplies MID (backward); 0: it multiplies OUT (forward)
   int independent;              // 1: see smlm_b200_fwd in include/smlm_b200.h
   int mode;                     // kFusedBoth, or one half only (one reference operator call):
@@ -179,11 +186,16 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
   const int lane = tid & 31;
   const int warp = tid >> 5;
   const int KS = a.ksplit;
-  // the grid is the jobs' grids laid end to end; a cluster never straddles two jobs
-  const int jidx = blockIdx.x / a.ctas_per_job;
-  const int local = blockIdx.x - jidx * a.ctas_per_job;
-  const int piece_idx = local / KS;
-  const int z = local - piece_idx * KS;
+  // the grid is the groups' grids laid end to end; a cluster never straddles two pieces
+  int grp = 0;
+  for (int i = 1; i < a.ngroups; ++i)
+    if (static_cast<int>(blockIdx.x) >= a.grp_cta_begin[i]) grp = i;
+  const int local = blockIdx.x - a.grp_cta_begin[grp];
+  const int gjobs = a.grp_job_begin[grp + 1] - a.grp_job_begin[grp];
+  const int cl = local / KS;
+  const int z = local - cl * KS;
+  const int jidx = a.grp_job_begin[grp] + cl % gjobs;
+  const int piece_idx = cl / gjobs;
   const FusedJob& jb = a.job[jidx];
   const FusedMaps& tm = tmn.m[jidx];
 

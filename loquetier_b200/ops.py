@@ -85,6 +85,12 @@ def set_tensor_core_mode(mode: int) -> int:
     return int(lib.smlm_b200_set_tensor_core_mode(int(mode)))
 
 
+def set_cluster_split(split: int) -> int:
+    """Measurement knob of the mma.sync fused kernel: 0 lets the library choose how many CTAs share a
+    piece, 1..4 forces it.  Returns the previous setting."""
+    return int(lib.smlm_b200_set_cluster_split(int(split)))
+
+
 def gemm(y, x, w_table, plan: Plan, is_row_major=False, seg_ids=None, seg_scale=None, accumulate=False):
     """One segmented GEMM (one reference operator call)."""
     with torch.cuda.device(x.device):

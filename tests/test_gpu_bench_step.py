@@ -67,7 +67,7 @@ def test_c3_multi_and_single_schedules_agree():
         for a, b in zip(outs["single"], outs[sched]):
             for k in a:
                 x, y = a[k].float(), b[k].float()
-                tol = 2.0 ** -7 * x.abs() + 1e-3 * float(x.abs().max())
+                tol = 2.0 ** -6 * x.abs() + 4e-3 * float(x.abs().max())
                 assert bool(((x - y).abs() <= tol).all()), f"{sched}: {k} differs from the per-projection launches"
                 if k not in ("dA", "dB"):   # (a gradient element sums thousands of products with v / dV)
                     assert float((a[k] != b[k]).float().mean()) < 0.02, f"{sched}: {k}: too many elements differ"
