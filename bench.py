@@ -222,9 +222,15 @@ class Workload:
             self.plan = None
         else:
             g = self.grouped and wants_grouped_plan(lens, ids)
+            self.iplan = None
+            if self.tl and self.sched != "single":
+                # both plans of the step from one launch
+                self.plan, self.pplan = self.ops.plan_pair(self.seg, self.T, self.part, self.tl,
+                                                           seg_ids_a=self.ids if g else None,
+                                                           n_table_a=self.spec["n_adapters"])
+                return
             self.plan = self.ops.Plan(self.seg, self.T, seg_ids=self.ids if g else None,
                                       n_table=self.spec["n_adapters"])
-            self.iplan = None
         if self.tl:
             self.pplan = self.ops.Plan(self.part, self.tl)
 
@@ -235,11 +241,11 @@ class Workload:
     def launches_per_step(self):
         """Kernels of this library launched per step: the plans, then per class one launch (multi / split)
         or one per projection (single)."""
-        nplan = 1 + (1 if self.tl else 0)
+        nplan = 1 + (1 if self.tl and (self.sched in ("single", "split", "split2") or self.pset is None) else 0)
         if self.sched == "single" or self.pset is None:
             return nplan + len(self.proj) * (1 + (2 if self.tl else 0))
         if self.sched in ("split", "split2") and self.iseg is not None and self.tl:
-            return nplan + 1 + 4
+            return nplan + 4
         return nplan + 1 + (2 if self.tl else 0)
 
     def step(self):

@@ -111,6 +111,13 @@ int smlm_b200_plan(void* plan, size_t plan_bytes, const int32_t* seg_indptr, int
 int smlm_b200_plan_grouped(void* plan, size_t plan_bytes, const int32_t* seg_indptr, const int32_t* seg_ids,
                            int nseg, int n_table, int T, void* stream);
 
+/* Two plans in one launch: plan A as smlm_b200_plan_grouped builds it (ids_a may be NULL for an ordinary
+ * plan), plan B as smlm_b200_plan builds it - typically the plan of all segments and the plan of the train
+ * partitions of one step, which would otherwise cost two launches back to back. */
+int smlm_b200_plan_pair(void* plan_a, size_t plan_a_bytes, const int32_t* indptr_a, const int32_t* ids_a, int nseg_a,
+                        int n_table_a, int T_a, void* plan_b, size_t plan_b_bytes, const int32_t* indptr_b,
+                        int nseg_b, int T_b, void* stream);
+
 /* Synchronises the stream and reports what the device recorded in a plan: number
  * of pieces and SMLM_OK or one of the SMLM_ERR_BAD_* codes.  For tests and
  * debugging; the compute entry points never synchronise. */

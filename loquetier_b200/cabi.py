@@ -45,6 +45,8 @@ SIGNATURES = {
     "smlm_b200_plan_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_plan": (c_int, [c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p]),
     "smlm_b200_plan_grouped": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "smlm_b200_plan_pair": (c_int, [c_void_p, c_size_t, c_void_p, c_void_p, c_int, c_int, c_int,
+                                    c_void_p, c_size_t, c_void_p, c_int, c_int, c_void_p]),
     "smlm_b200_plan_status": (c_int, [c_void_p, ctypes.POINTER(c_int), c_void_p]),
     "smlm_b200_gemm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -32,11 +32,26 @@ namespace smlm {
 
 constexpr int kPlanThreads = 1024;
 
-__global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(int* __restrict__ plan,
-                                                                   const int32_t* __restrict__ indptr, int nseg,
-                                                                   int T, int max_pieces, int bm, int max_pieces2,
-                                                                   int bm2, const int32_t* __restrict__ ids,
-                                                                   int n_table) {
+// One plan to build: CTA i of the launch builds job i, so the plans of a step (all segments, train
+// partitions) cost one launch.
+struct PlanJob {
+  int* plan;
+  const int32_t* indptr;
+  const int32_t* ids;
+  int nseg, T, max_pieces, bm, max_pieces2, bm2, n_table;
+};
+constexpr int kPlanMaxJobs = 4;
+struct PlanJobs {
+  PlanJob job[kPlanMaxJobs];
+};
+
+__global__ void __launch_bounds__(kPlanThreads) plan_pieces_kernel(const __grid_constant__ PlanJobs jobs) {
+  const PlanJob& J = jobs.job[blockIdx.x];
+  int* plan = J.plan;
+  const int32_t* __restrict__ indptr = J.indptr;
+  const int32_t* __restrict__ ids = J.ids;
+  const int nseg = J.nseg, T = J.T, max_pieces2 = J.max_pieces2, bm2 = J.bm2, n_table = J.n_table;
+  int max_pieces = J.max_pieces, bm = J.bm;
   __shared__ int s_off[kPlanThreads + 1];
   __shared__ int s_warp[32];
   __shared__ int s_base;

@@ -42,12 +42,14 @@ class Plan:
     """Work list of one batch: built on the device from the segment index pointer,
     shared by every SMLM call of the batch (all projections, shrink and expand)."""
 
-    __slots__ = ("buf", "indptr", "nseg", "T", "seg_ids", "n_table")
+    __slots__ = ("buf", "indptr", "nseg", "T", "seg_ids", "n_table", "nbytes")
 
-    def __init__(self, indptr: torch.Tensor, T: int, seg_ids: Optional[torch.Tensor] = None, n_table: int = 0):
+    def __init__(self, indptr: torch.Tensor, T: int, seg_ids: Optional[torch.Tensor] = None, n_table: int = 0,
+                 launch: bool = True):
         """``seg_ids`` (int32 per segment) and ``n_table`` make it a grouped plan: short segments
         (decode tokens) are grouped by adapter for the forward calls that pass the same ``seg_ids``
-        and an adapter table of ``n_table`` entries.  Weight gradients need a plan without them."""
+        and an adapter table of ``n_table`` entries.  Weight gradients need a plan without them.
+        ``launch=False`` only allocates the buffer (for ``plan_pair``)."""
         _chk_cuda_contig(indptr, "s", 1)
         if indptr.dtype != torch.int32:
             raise RuntimeError("s must be int32")
@@ -62,6 +64,9 @@ class Plan:
                 raise RuntimeError("seg_ids must hold one int32 adapter index per segment")
         nbytes = lib.smlm_b200_plan_bytes(self.T, max(self.nseg, 0))
         self.buf = torch.empty((nbytes + 3) // 4, dtype=torch.int32, device=indptr.device)
+        self.nbytes = nbytes
+        if not launch:
+            return
         with torch.cuda.device(indptr.device):
             check(lib.smlm_b200_plan_grouped(self.buf.data_ptr(), nbytes, indptr.data_ptr(), _p(seg_ids), self.nseg,
                                              self.n_table, self.T, _stream(indptr)), "smlm_b200_plan")
@@ -77,6 +82,19 @@ class Plan:
     def raise_if_failed(self):
         _, rc = self.status()
         check(rc, "smlm plan")
+
+
+def plan_pair(indptr_a: torch.Tensor, T_a: int, indptr_b: torch.Tensor, T_b: int,
+              seg_ids_a: Optional[torch.Tensor] = None, n_table_a: int = 0):
+    """The two plans of a step - all segments (grouped when ``seg_ids_a`` is given) and the train
+    partitions - built by one launch.  Returns (plan_a, plan_b)."""
+    a = Plan(indptr_a, T_a, seg_ids=seg_ids_a, n_table=n_table_a, launch=False)
+    b = Plan(indptr_b, T_b, launch=False)
+    with torch.cuda.device(indptr_a.device):
+        check(lib.smlm_b200_plan_pair(a.buf.data_ptr(), a.nbytes, indptr_a.data_ptr(), _p(seg_ids_a), a.nseg,
+                                      a.n_table, a.T, b.buf.data_ptr(), b.nbytes, indptr_b.data_ptr(), b.nseg, b.T,
+                                      _stream(indptr_a)), "smlm_b200_plan_pair")
+    return a, b
 
 
 def set_tensor_core_mode(mode: int) -> int:

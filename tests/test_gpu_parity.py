@@ -424,3 +424,24 @@ def test_backward_literal_tolerance_at_reference_rounding_points(dtype, rank):
             worst = max(worst, float(err.max()) / max(float(w.abs().max()), 1e-30))
     assert worst < 1e-2
     print(f"observed max|err|/max|ref| over dA, dB: {worst:.3e}; largest share outside the literal tolerance: {share:.3e}")
+
+
+def test_plan_pair_builds_the_same_two_plans_in_one_launch():
+    from loquetier_b200 import ops
+    rng = np.random.default_rng(3)
+    lens = [int(v) for v in rng.integers(0, 90, size=200)]
+    ids = torch.tensor(rng.integers(0, 16, size=200), dtype=torch.int32, device="cuda")
+    seg = torch.tensor(np.concatenate([[0], np.cumsum(lens)]).astype(np.int32), device="cuda")
+    T = int(seg[-1])
+    part = seg[:9].contiguous()
+    tl = int(part[-1])
+    a0 = ops.Plan(seg, T, seg_ids=ids, n_table=16)
+    b0 = ops.Plan(part, tl)
+    a1, b1 = ops.plan_pair(seg, T, part, tl, seg_ids_a=ids, n_table_a=16)
+    torch.cuda.synchronize()
+    assert a1.status() == a0.status() and b1.status() == b0.status() and a0.status()[1] == 0
+
+    def used(p):   # header + the pieces that were written
+        n = p.status()[0]
+        return p.buf[:4 + 4 * n]
+    assert torch.equal(used(a0), used(a1)) and torch.equal(used(b0), used(b1))
