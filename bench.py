@@ -910,7 +910,8 @@ def run_c5(a, rank, world, local, torch, dist, blocks, steps):
     if a.seg_len > 0:
         spec["lens"] = [a.seg_len] * len(spec["lens"])
     wl = Workload(spec, torch.device("cuda", local))
-    dp = DataParallelStep(wl, torch, dist if world > 1 else None, chunks=a.chunks)
+    # one rank alone exchanges nothing: its weight gradients stay one launch per projection
+    dp = DataParallelStep(wl, torch, dist if world > 1 else None, chunks=a.chunks if world > 1 else 1)
     T = wl.T
     dp.step()
     torch.cuda.synchronize()
