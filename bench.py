@@ -875,14 +875,21 @@ class DataParallelStep:
                 if self.exchange:
                     b.reduce_slots(i, 0, b.n_slots)
             else:
+                # the plans of all ranges first: the launches after the first one do not wait for their
+                # predecessors, so nothing they read may be written in between
+                subs = [self._sub(*parts) if parts is not None else None for (_, _, parts) in self.ranges]
+                launched = 0
                 for c, (s0, s1, parts) in enumerate(self.ranges):
                     if parts is not None:
                         p0, p1 = parts
-                        d = self._sub(p0, p1)
+                        d = subs[c]
+                        # the ranges touch different partitions, outputs and workspaces: each launch after
+                        # the first may start while its predecessor drains
                         ops.wgrad_pair(p["dA_t"][p0:p1], p["dB_t"][p0:p1], p["dv"], p["x"], p["v"], p["go"], d["part"],
                                        d["plan"], r, part_ids=d["ids"], part_scale=wl.scale, n_table=n_ad,
                                        workspace=ops.wgrad_workspace(wl.dev, wl.tl, wl.npart, r, p["h_out"], p["h_in"],
-                                                                     slot=100 + c))
+                                                                     slot=100 + c), independent=launched > 0)
+                        launched += 1
                     if self.exchange:
                         b.reduce_slots(i, s0, s1)
         b.finish()
