@@ -9,35 +9,24 @@
 // seq_len - 1 (:489-494).
 //
 //   append_kv_kernel   one new token per request   (AppendPagedKVCacheDecodeKernel, page.cuh:368-396)
-//   init_kv_kernel     a run of tokens per request (AppendPagedKVCachePrefillKernel, page.cuh:411-444)
+//                      or a run of tokens per request (AppendPagedKVCachePrefillKernel, page.cuh:411-444)
 //   paged_decode_kernel  o = softmax(rope(q) . rope(K)^T / sqrt(d)) . V per request and head
 //                        (BatchDecodeWithPagedKVCacheKernel, decode.cuh:451-620)
 //
-// Decode is HBM-bound: every K and V page of a (request, kv head) is read exactly once, whatever the
-// number of query heads that share the kv head (they are all served by the CTA that streams the
-// pages).  A CTA owns one (request, kv head, split): it streams its pages through a ring of shared-
-// memory stages (16-byte cp.async, several pages in flight), rotates each key once and dots it with
-// the rotated queries of the group, and keeps a running softmax per head.  Rotation angles advance by
-// a fixed stride per thread, so they are carried by the angle-addition recurrence (FMA pipe) and
-// re-seeded with an accurate evaluation from time to time instead of costing 16 special-function operations
-// per key.  Long sequences of small batches are cut into `splits` page ranges so that the machine is
-// filled; the partial softmax states go through a workspace and the CTA that finishes last (a
-// ticket, no waiting) merges them in split order - a fixed order, so the result does not depend on
-// scheduling.
+// Decode is HBM-bound: every K and V entry of a (request, kv head) is read exactly once, whatever the
+// number of query heads that share the kv head - they are the rows of one tensor-core tile.  Long
+// sequences of small batches are cut into `splits` ranges of key tiles so that the machine is filled; the
+// partial softmax states go through a workspace and the CTA that finishes last (a ticket, no waiting)
+// merges them in range order - a fixed order, so the result does not depend on scheduling.
 #pragma once
 #include "smlm_common.cuh"
 
 namespace smlm {
 
 constexpr int kPdDim = 128;          // head dimension served
-constexpr int kPdStages = 6;         // pages in flight per CTA
-constexpr int kPdEntryLanes = 8;     // keys of a page processed side by side
+constexpr int kPdStages = 3;         // tiles of 16 keys in flight per warp
 constexpr int kPdMaxSplits = 16;
-constexpr int kPdReseed = 64;        // keys between two accurate evaluations of the rotation
 constexpr int kPdRec = kPdDim + 4;   // floats of a parked softmax state: m, d, two unused, then o[128] (16-byte aligned)
-
-__host__ __device__ constexpr int pd_heads_per_thread(int g) { return g < 4 ? g : 4; }
-__host__ __device__ constexpr int pd_threads(int g) { return 128 * (g / pd_heads_per_thread(g)); }
 
 struct PdArgs {
   void* o;                        // [B, Nq, 128]
@@ -117,43 +106,47 @@ __global__ void __launch_bounds__(128) append_kv_kernel(const AppendArgs a) {
 // decode
 // ---------------------------------------------------------------------------------------------
 
-template <typename T>
-__device__ __forceinline__ void load8(float (&f)[8], const T* p) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
-  const float2 a = unpack2<T>(u.x), b = unpack2<T>(u.y), c = unpack2<T>(u.z), d = unpack2<T>(u.w);
-  f[0] = a.x; f[1] = a.y; f[2] = b.x; f[3] = b.y; f[4] = c.x; f[5] = c.y; f[6] = d.x; f[7] = d.y;
-}
-
-// online-softmax state merge in the base-2 domain: (m, d, o) <- (m, d, o) + (m2, d2, o2)
-__device__ __forceinline__ void pd_merge(float& m, float& d, float (&o)[8], float m2, float d2, const float (&o2)[8]) {
+// online-softmax state merge in the base-2 domain for N values: (m, d, o) <- (m, d, o) + (m2, d2, o2)
+template <int N>
+__device__ __forceinline__ void pd_merge(float& m, float& d, float (&o)[N], float m2, float d2, const float (&o2)[N]) {
   if (d2 == 0.f) return;             // an empty state carries no information (and its m may be -inf)
   if (d == 0.f) {
     m = m2; d = d2;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] = o2[i];
+    for (int i = 0; i < N; ++i) o[i] = o2[i];
     return;
   }
   const float mn = fmaxf(m, m2);
   const float s1 = exp2f(m - mn), s2 = exp2f(m2 - mn);
   d = d * s1 + d2 * s2;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) o[i] = o[i] * s1 + o2[i] * s2;
+  for (int i = 0; i < N; ++i) o[i] = o[i] * s1 + o2[i] * s2;
   m = mn;
 }
 
+constexpr int kPdWarps = 4;                          // each warp streams its own tiles of 16 keys
+constexpr int kPdTile = 16;
+constexpr int kPdTileBytes = kPdTile * kPdDim * 2;   // one tile of K (or V) of one head: 4 KB
+constexpr int kPdWarpRing = kPdStages * 2 * kPdTileBytes;
+constexpr int kPdQOff = kPdWarps * kPdWarpRing;      // rotated queries [8 rows][128], then 16 bytes of zeros
+constexpr int kPdSmem = kPdQOff + 8 * kPdDim * 2 + 64;
+
+// One CTA = one (request, kv head, range of key tiles).  The G query heads that share the kv head are the
+// rows of a 16-row MMA tile (rows G..15 are zero), so every key and value is read once for all of them:
+//   S[heads, 16 keys] = Q . K^T  and  O[heads, 128] += P . V  with mma.sync m16n8k16, fp32 accumulation.
+// Each warp owns every fourth tile of the range and a private ring of shared-memory stages filled with
+// 16-byte cp.async copies (no CTA-wide barrier in the loop).  A tile's keys are rotated where they lie in
+// shared memory before the MMA reads them: lane l owns the frequency pair (2l, 2l+1) and walks the 16
+// positions of the tile with the angle-addition recurrence, re-seeded exactly at every tile.  The rotated
+// keys are rounded to the storage type - what a cache that stores rotated keys holds anyway.
 template <typename T, int G>
-__global__ void __launch_bounds__(pd_threads(G)) paged_decode_kernel(const PdArgs a) {
-  constexpr int HPT = pd_heads_per_thread(G);   // query heads per thread
-  constexpr int NT = pd_threads(G);
-  extern __shared__ unsigned char pd_smem[];
+__global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArgs a) {
+  extern __shared__ __align__(128) unsigned char pd_smem[];
   __shared__ int s_last;
   const int tid = threadIdx.x;
   const int lane = tid & 31;
   const int warp = tid >> 5;
-  const int tx = lane & 15;                     // dims tx*8 .. tx*8+7
-  const int ty = warp >> 2;                     // head block of this thread
-  const int ez = ((warp & 3) << 1) | (lane >> 4);   // entry lane 0..7
-  const unsigned hmask = (lane & 16) ? 0xffff0000u : 0x0000ffffu;
+  const int g = lane >> 2, t = lane & 3;       // MMA fragment coordinates: row (head) g, column pair t
 
   const int S = a.splits;
   const int s = blockIdx.x % S;
@@ -162,7 +155,7 @@ __global__ void __launch_bounds__(pd_threads(G)) paged_decode_kernel(const PdArg
   const int b = bh / a.num_kv_heads;
   const int Nq = a.num_kv_heads * G;
   const int P = a.page_size;
-  const int head0 = kvh * G + ty * HPT;
+  const int head0 = kvh * G;
 
   pdl_wait();
   int p0 = a.kv_indptr[b], p1 = a.kv_indptr[b + 1];
@@ -177,56 +170,86 @@ __global__ void __launch_bounds__(pd_threads(G)) paged_decode_kernel(const PdArg
     last_valid = 0;
   }
   const int seq_len = npages > 0 ? (npages - 1) * P + last_valid : 0;
-  const int per = (npages + S - 1) / S;
-  const int pg0 = s * per;
-  const int npg = max(0, min(npages, pg0 + per) - pg0);   // pages of this split
+  const int ntiles = (seq_len + kPdTile - 1) / kPdTile;
+  const int per = (ntiles + S - 1) / S;
+  const int tile0 = s * per;
+  const int ntl = max(0, min(ntiles, tile0 + per) - tile0);   // tiles of this CTA
+  const int ntw = ntl > warp ? (ntl - warp + kPdWarps - 1) / kPdWarps : 0;   // tiles of this warp
 
-  // ---- rotation frequencies and the rotated, pre-scaled queries ----
-  float freq[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int dm = (tx * 8 + i) & 63;
-    // angles are kept in half-turns (angle / pi): sincospif reduces its argument exactly, whereas the
-    // library is built with fast math, under which sincosf loses accuracy at the large angles long
-    // sequences reach
-    freq[i] = exp2f(-a.log2_theta * static_cast<float>(2 * dm) * (1.0f / kPdDim)) * 0.31830988618379067f;
-  }
-  const float sgn = tx < 8 ? -1.f : 1.f;       // first half: x cos - partner sin; second: x cos + partner sin
-  float qv[HPT][8];
+  // ---- the rotated, pre-scaled queries as the A operand: [8 rows][128] in shared memory ----
+  // Angles are kept in half-turns (angle / pi): sincospif reduces its argument exactly, whereas the
+  // library is built with fast math, under which sincosf loses accuracy at the angles long sequences reach.
+  const uint32_t sbase = smem_u32(pd_smem);
+  const uint32_t qs = sbase + kPdQOff;
   {
-    const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
-    const T* Q = static_cast<const T*>(a.q);
-    float cq[8], sq[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) sincospif(static_cast<float>(max(seq_len - 1, 0)) * freq[i], &sq[i], &cq[i]);
-#pragma unroll
-    for (int g = 0; g < HPT; ++g) {
-      const T* qp = Q + (static_cast<size_t>(b) * Nq + head0 + g) * kPdDim;
-      float own[8], par[8];
-      load8<T>(own, qp + tx * 8);
-      load8<T>(par, qp + ((tx * 8 + 64) & 127));
-#pragma unroll
-      for (int i = 0; i < 8; ++i) qv[g][i] = (own[i] * cq[i] + sgn * par[i] * sq[i]) * qscale;
+    const int row = tid >> 4;                 // 8 rows x 16 threads
+    const int d0 = (tid & 15) * 4;            // dims d0..d0+3 and their partners d0+64..
+    float own[4] = {0.f, 0.f, 0.f, 0.f}, par[4] = {0.f, 0.f, 0.f, 0.f};
+    if (row < G) {
+      const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(b) * Nq + head0 + row) * kPdDim;
+      const uint2 uo = *reinterpret_cast<const uint2*>(qp + d0);
+      const uint2 up = *reinterpret_cast<const uint2*>(qp + d0 + 64);
+      const float2 o0 = unpack2<T>(uo.x), o1 = unpack2<T>(uo.y), q0 = unpack2<T>(up.x), q1 = unpack2<T>(up.y);
+      own[0] = o0.x; own[1] = o0.y; own[2] = o1.x; own[3] = o1.y;
+      par[0] = q0.x; par[1] = q0.y; par[2] = q1.x; par[3] = q1.y;
     }
+    const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
+    float ro[4], rp[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
+      float sn, cs;
+      sincospif(static_cast<float>(max(seq_len - 1, 0)) * f, &sn, &cs);
+      ro[i] = (own[i] * cs - par[i] * sn) * qscale;
+      rp[i] = (par[i] * cs + own[i] * sn) * qscale;
+    }
+    const int c_own = d0 >> 3, c_par = (d0 + 64) >> 3;
+    const uint32_t off = (d0 & 7) * 2;
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(qs + row * 256 + ((c_own ^ row) << 4) + off),
+                 "r"(pack2<T>(ro[0], ro[1])), "r"(pack2<T>(ro[2], ro[3])) : "memory");
+    asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(qs + row * 256 + ((c_par ^ row) << 4) + off),
+                 "r"(pack2<T>(rp[0], rp[1])), "r"(pack2<T>(rp[2], rp[3])) : "memory");
+    if (tid < 4) asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(qs + 8 * 256 + tid * 4), "r"(0) : "memory");
+  }
+  __syncthreads();
+  uint32_t qf[8][4];
+#pragma unroll
+  for (int ks = 0; ks < 8; ++ks) {
+    // matrices: (rows 0-7, k lo), (rows 8-15, k lo), (rows 0-7, k hi), (rows 8-15, k hi); rows 8-15 are zeros
+    const int m = lane >> 3, r = lane & 7;
+    const int chunk = ks * 2 + (m >> 1);
+    const uint32_t addr = (m & 1) ? qs + 8 * 256 : qs + r * 256 + ((chunk ^ r) << 4);
+    ldsm_x4(qf[ks], addr);
   }
 
-  // ---- stream the pages ----
-  const int stage_bytes = 2 * P * kPdDim * static_cast<int>(sizeof(T));
-  const uint32_t ring = smem_u32(pd_smem);
+  // ---- this warp's ring and its loader ----
+  const uint32_t ring = sbase + warp * kPdWarpRing;
   const size_t head_off = (static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + kvh) * P * kPdDim;
   const size_t kv_delta = static_cast<size_t>(a.num_kv_heads) * P * kPdDim;
-  const int chunks = P * 16;   // 16-byte chunks per K (or V) page of one head
   bool bad_ptr = false;
-  auto issue = [&](int j) {
-    if (j < npg) {
-      const T* page = static_cast<const T*>(a.kv_ptrs[p0 + pg0 + j]);
-      const bool ok = page != nullptr && (reinterpret_cast<uintptr_t>(page) & 15) == 0;
-      if (!ok) bad_ptr = true;
-      const T* kp = ok ? page + head_off : nullptr;
-      const uint32_t dst = ring + (j % kPdStages) * stage_bytes;
-      for (int c = tid; c < 2 * chunks; c += NT) {
-        const T* src = c < chunks ? kp + c * 8 : kp + kv_delta + (c - chunks) * 8;
-        cp_async16(dst + c * 16, ok ? src : static_cast<const T*>(a.q), ok);   // a bad page reads as zeros
+  auto issue = [&](int j) {   // j-th tile of this warp
+    if (j < ntw) {
+      const int key0 = (tile0 + warp + j * kPdWarps) * kPdTile;
+      const uint32_t kst = ring + (j % kPdStages) * (2 * kPdTileBytes);
+      const int cch = lane & 15;
+#pragma unroll 4
+      for (int k = 0; k < kPdTile / 2; ++k) {
+        const int key = 2 * k + (lane >> 4);
+        const int gk = key0 + key;
+        bool ok = gk < seq_len;
+        const T* src = static_cast<const T*>(a.q);
+        if (ok) {
+          const T* page = static_cast<const T*>(a.kv_ptrs[p0 + gk / P]);
+          if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) {
+            bad_ptr = true;
+            ok = false;
+          } else {
+            src = page + head_off + static_cast<size_t>(gk % P) * kPdDim + cch * 8;
+          }
+        }
+        const uint32_t dst = kst + key * 256 + ((cch ^ (key & 7)) << 4);
+        cp_async16(dst, src, ok);                                             // keys past the end read as zeros
+        cp_async16(dst + kPdTileBytes, ok ? src + kv_delta : src, ok);
       }
     }
     cp_async_commit();
@@ -234,149 +257,166 @@ __global__ void __launch_bounds__(pd_threads(G)) paged_decode_kernel(const PdArg
 #pragma unroll
   for (int j = 0; j < kPdStages - 1; ++j) issue(j);
 
-  float m[HPT], d[HPT], o[HPT][8];
+  // ---- rotation state of this lane: frequencies 2l and 2l + 1 ----
+  float fr[2], c1[2], s1[2];
 #pragma unroll
-  for (int g = 0; g < HPT; ++g) {
-    m[g] = -INFINITY;
-    d[g] = 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[g][i] = 0.f;
+  for (int i = 0; i < 2; ++i) {
+    fr[i] = exp2f(-a.log2_theta * static_cast<float>(2 * (2 * lane + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
+    sincospif(fr[i], &s1[i], &c1[i]);
   }
-  // rotation of the key this thread handles next: position pos, then pos + 8, pos + 16, ...
-  float c8[8], s8[8], cc[8], ss[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) sincospif(8.f * freq[i], &s8[i], &c8[i]);
-  int pos = pg0 * P + ez;
-  int since_seed = kPdReseed;
 
-  for (int it = 0; it < npg; ++it) {
-    issue(it + kPdStages - 1);
+  float m_run = -INFINITY, l_run = 0.f;   // row g; l_run is this lane's share of the row sum
+  float o[16][4];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f;
+
+  for (int j = 0; j < ntw; ++j) {
+    issue(j + kPdStages - 1);
     cp_async_wait<kPdStages - 1>();
-    __syncthreads();
-    const unsigned char* st = pd_smem + (it % kPdStages) * stage_bytes;
-    const T* ks = reinterpret_cast<const T*>(st);
-    const T* vs = ks + P * kPdDim;
-    const int valid = (pg0 + it == npages - 1) ? last_valid : P;
-    for (int e = ez; e < valid; e += kPdEntryLanes) {
-      if (since_seed >= kPdReseed) {
+    __syncwarp();
+    const int key0 = (tile0 + warp + j * kPdWarps) * kPdTile;
+    const uint32_t kst = ring + (j % kPdStages) * (2 * kPdTileBytes);
+    const uint32_t vst = kst + kPdTileBytes;
+    // rotate the 16 keys in place
+    {
+      float cc[2], ss[2];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sincospif(static_cast<float>(pos) * freq[i], &ss[i], &cc[i]);
-        since_seed = 0;
+      for (int i = 0; i < 2; ++i) sincospif(static_cast<float>(key0) * fr[i], &ss[i], &cc[i]);
+#pragma unroll 4
+      for (int e = 0; e < kPdTile; ++e) {
+        const uint32_t ao = kst + e * 256 + ((((lane >> 2) ^ (e & 7))) << 4) + (lane & 3) * 4;
+        uint32_t wo, wp;
+        asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wo) : "r"(ao));
+        asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wp) : "r"(ao + 128));
+        const float2 ko = unpack2<T>(wo), kp = unpack2<T>(wp);
+        const uint32_t no = pack2<T>(ko.x * cc[0] - kp.x * ss[0], ko.y * cc[1] - kp.y * ss[1]);
+        const uint32_t np = pack2<T>(kp.x * cc[0] + ko.x * ss[0], kp.y * cc[1] + ko.y * ss[1]);
+        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao), "r"(no) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao + 128), "r"(np) : "memory");
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float cn = cc[i] * c1[i] - ss[i] * s1[i];
+          ss[i] = ss[i] * c1[i] + cc[i] * s1[i];
+          cc[i] = cn;
+        }
       }
-      float own[8], par[8], kr[8];
-      load8<T>(own, ks + e * kPdDim + tx * 8);
-      load8<T>(par, ks + e * kPdDim + ((tx * 8 + 64) & 127));
-#pragma unroll
-      for (int i = 0; i < 8; ++i) kr[i] = own[i] * cc[i] + sgn * par[i] * ss[i];
-      float x[HPT];
-#pragma unroll
-      for (int g = 0; g < HPT; ++g) {
-        float acc = 0.f;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc = fmaf(qv[g][i], kr[i], acc);
-        x[g] = acc;
-      }
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1)
-#pragma unroll
-        for (int g = 0; g < HPT; ++g) x[g] += __shfl_xor_sync(hmask, x[g], off);
-      float vv[8];
-      load8<T>(vv, vs + e * kPdDim + tx * 8);
-#pragma unroll
-      for (int g = 0; g < HPT; ++g) {
-        const float mn = fmaxf(m[g], x[g]);
-        const float sc = exp2f(m[g] - mn);   // exp2f(-inf) = 0 on the first key
-        const float p = exp2f(x[g] - mn);
-        d[g] = d[g] * sc + p;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o[g][i] = fmaf(p, vv[i], o[g][i] * sc);
-        m[g] = mn;
-      }
-      // advance the rotation by eight positions
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const float cn = cc[i] * c8[i] - ss[i] * s8[i];
-        ss[i] = ss[i] * c8[i] + cc[i] * s8[i];
-        cc[i] = cn;
-      }
-      pos += kPdEntryLanes;
-      ++since_seed;
     }
-    // a page with fewer valid entries than lanes leaves some lanes behind: keep every lane's position
-    // in step with the pages (only the request's last page can be short, so this runs at most once)
-    if (valid < P) {
-      const int done = ez < valid ? (valid - 1 - ez) / kPdEntryLanes + 1 : 0;
-      pos += (P / kPdEntryLanes - done) * kPdEntryLanes;
-      since_seed = kPdReseed;
+    __syncwarp();
+    // S = Q . K^T
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      uint32_t bf[4];
+      const int m = lane >> 3;
+      const int key = (m >> 1) * 8 + (lane & 7);
+      const int chunk = ks * 2 + (m & 1);
+      ldsm_x4(bf, kst + key * 256 + ((chunk ^ (key & 7)) << 4));
+      mma16816<T>(sc[0], qf[ks], bf[0], bf[1]);
+      mma16816<T>(sc[1], qf[ks], bf[2], bf[3]);
     }
-    __syncthreads();
+    // running softmax of row g over this lane's keys 2t, 2t+1, 8+2t, 9+2t
+    float x[4] = {sc[0][0], sc[0][1], sc[1][0], sc[1][1]};
+    const int kb = key0 + 2 * t;
+    if (kb >= seq_len) x[0] = -INFINITY;
+    if (kb + 1 >= seq_len) x[1] = -INFINITY;
+    if (kb + 8 >= seq_len) x[2] = -INFINITY;
+    if (kb + 9 >= seq_len) x[3] = -INFINITY;
+    float mx = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float mn = fmaxf(m_run, mx);          // finite: every tile holds at least one valid key
+    const float rescale = exp2f(m_run - mn);    // exp2f(-inf) = 0 on the first tile
+    float pr[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pr[i] = exp2f(x[i] - mn);
+    l_run = l_run * rescale + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+    m_run = mn;
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn) {
+      o[jn][0] *= rescale;
+      o[jn][1] *= rescale;
+    }
+    // O += P . V ; P is the A operand straight from the registers (rows 8-15 zero)
+    uint32_t pa[4] = {pack2<T>(pr[0], pr[1]), 0u, pack2<T>(pr[2], pr[3]), 0u};
+#pragma unroll
+    for (int jn = 0; jn < 16; jn += 2) {
+      uint32_t bf[4];
+      const int m = lane >> 3;
+      const int key = (m & 1) * 8 + (lane & 7);
+      const int chunk = jn + (m >> 1);
+      ldsm_x4_t(bf, vst + key * 256 + ((chunk ^ (key & 7)) << 4));
+      mma16816<T>(o[jn], pa, bf[0], bf[1]);
+      mma16816<T>(o[jn + 1], pa, bf[2], bf[3]);
+    }
+    __syncwarp();   // the stage is free for the copy issued two iterations from now
   }
   cp_async_wait<0>();
-  __syncthreads();
-  if (bad_ptr && tid == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
+  if (__any_sync(0xffffffffu, bad_ptr) && lane == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+  l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+  __syncthreads();   // every warp is done with its ring: it becomes the merge area
 
-  // ---- merge the entry lanes in lane order (a fixed order) ----
-  // per (ty, ez, g): m, d, then o[128]
+  // ---- merge the warps in warp order (a fixed order): per (warp, row) m, d, 2 unused, o[128] ----
   float* red = reinterpret_cast<float*>(pd_smem);
   constexpr int REC = kPdRec;
-  {
+  float ov[32];
 #pragma unroll
-    for (int g = 0; g < HPT; ++g) {
-      float* r = red + ((ty * kPdEntryLanes + ez) * HPT + g) * REC;
-      if (tx == 0) {
-        r[0] = m[g];
-        r[1] = d[g];
-      }
-#pragma unroll
-      for (int i = 0; i < 8; ++i) r[4 + tx * 8 + i] = o[g][i];
+  for (int jn = 0; jn < 16; ++jn) {
+    ov[2 * jn] = o[jn][0];
+    ov[2 * jn + 1] = o[jn][1];
+  }
+  if (warp > 0) {
+    float* r = red + (warp * 8 + g) * REC;
+    if (t == 0) {
+      r[0] = m_run;
+      r[1] = l_run;
     }
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn) *reinterpret_cast<float2*>(r + 4 + jn * 8 + 2 * t) = make_float2(ov[2 * jn], ov[2 * jn + 1]);
   }
   __syncthreads();
-  const bool merger = ez == 0;   // the first half-warp of each head block
-  if (merger) {
+  if (warp != 0) {
+    if (S == 1) return;
+  } else {
+    for (int w = 1; w < kPdWarps; ++w) {
+      const float* r = red + (w * 8 + g) * REC;
+      float o2[32];
 #pragma unroll
-    for (int g = 0; g < HPT; ++g) {
-      for (int z = 1; z < kPdEntryLanes; ++z) {
-        const float* r = red + ((ty * kPdEntryLanes + z) * HPT + g) * REC;
-        float o2[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o2[i] = r[4 + tx * 8 + i];
-        pd_merge(m[g], d[g], o[g], r[0], r[1], o2);
+      for (int jn = 0; jn < 16; ++jn) {
+        const float2 v2 = *reinterpret_cast<const float2*>(r + 4 + jn * 8 + 2 * t);
+        o2[2 * jn] = v2.x;
+        o2[2 * jn + 1] = v2.y;
       }
+      pd_merge<32>(m_run, l_run, ov, r[0], r[1], o2);
     }
   }
 
   T* O = static_cast<T*>(a.o);
-  auto store_out = [&](int g) {
-    const float inv = d[g] > 0.f ? 1.0f / d[g] : 0.f;   // a request without keys gives zeros
-    uint4 u;
-    u.x = pack2<T>(o[g][0] * inv, o[g][1] * inv);
-    u.y = pack2<T>(o[g][2] * inv, o[g][3] * inv);
-    u.z = pack2<T>(o[g][4] * inv, o[g][5] * inv);
-    u.w = pack2<T>(o[g][6] * inv, o[g][7] * inv);
-    *reinterpret_cast<uint4*>(O + (static_cast<size_t>(b) * Nq + head0 + g) * kPdDim + tx * 8) = u;
+  auto store_out = [&]() {   // warp 0: row g = head, this lane's 32 columns
+    if (g >= G) return;
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;   // a request without keys gives zeros
+    T* op = O + (static_cast<size_t>(b) * Nq + head0 + g) * kPdDim;
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn)
+      *reinterpret_cast<uint32_t*>(op + jn * 8 + 2 * t) = pack2<T>(ov[2 * jn] * inv, ov[2 * jn + 1] * inv);
   };
 
   if (S == 1) {
-    if (merger) {
-#pragma unroll
-      for (int g = 0; g < HPT; ++g) store_out(g);
-    }
+    if (warp == 0) store_out();
     return;
   }
 
-  // ---- several splits: park the partial state, the last CTA of the (request, kv head) merges ----
-  if (merger) {
-#pragma unroll
-    for (int g = 0; g < HPT; ++g) {
-      float* r = a.partial + ((static_cast<size_t>(b) * Nq + head0 + g) * S + s) * REC;
-      if (tx == 0) {
-        r[0] = m[g];
-        r[1] = d[g];
-      }
-      *reinterpret_cast<float4*>(r + 4 + tx * 8) = make_float4(o[g][0], o[g][1], o[g][2], o[g][3]);
-      *reinterpret_cast<float4*>(r + 4 + tx * 8 + 4) = make_float4(o[g][4], o[g][5], o[g][6], o[g][7]);
+  // ---- several ranges: park the partial state, the last CTA of the (request, kv head) merges ----
+  if (warp == 0 && g < G) {
+    float* r = a.partial + ((static_cast<size_t>(b) * Nq + head0 + g) * S + s) * REC;
+    if (t == 0) {
+      r[0] = m_run;
+      r[1] = l_run;
     }
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn) *reinterpret_cast<float2*>(r + 4 + jn * 8 + 2 * t) = make_float2(ov[2 * jn], ov[2 * jn + 1]);
     __threadfence();
   }
   __syncthreads();
@@ -386,25 +426,25 @@ __global__ void __launch_bounds__(pd_threads(G)) paged_decode_kernel(const PdArg
     if (old == S - 1) a.tickets[bh] = 0;   // leave the workspace ready for the next launch
   }
   __syncthreads();
-  if (!s_last || !merger) return;
+  if (!s_last || warp != 0 || g >= G) return;
   __threadfence();
+  m_run = -INFINITY;
+  l_run = 0.f;
 #pragma unroll
-  for (int g = 0; g < HPT; ++g) {
-    float mm = -INFINITY, dd = 0.f, oo[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    for (int z = 0; z < S; ++z) {
-      const float* r = a.partial + ((static_cast<size_t>(b) * Nq + head0 + g) * S + z) * REC;
-      const float m2 = __ldcg(r), d2 = __ldcg(r + 1);
-      const float4 lo = __ldcg(reinterpret_cast<const float4*>(r + 4 + tx * 8));
-      const float4 hi = __ldcg(reinterpret_cast<const float4*>(r + 4 + tx * 8 + 4));
-      const float o2[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
-      pd_merge(mm, dd, oo, m2, d2, o2);
+  for (int i = 0; i < 32; ++i) ov[i] = 0.f;
+  for (int z = 0; z < S; ++z) {
+    const float* r = a.partial + ((static_cast<size_t>(b) * Nq + head0 + g) * S + z) * REC;
+    const float m2 = __ldcg(r), d2 = __ldcg(r + 1);
+    float o2[32];
+#pragma unroll
+    for (int jn = 0; jn < 16; ++jn) {
+      const float2 v2 = __ldcg(reinterpret_cast<const float2*>(r + 4 + jn * 8 + 2 * t));
+      o2[2 * jn] = v2.x;
+      o2[2 * jn + 1] = v2.y;
     }
-    m[g] = mm;
-    d[g] = dd;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[g][i] = oo[i];
-    store_out(g);
+    pd_merge<32>(m_run, l_run, ov, m2, d2, o2);
   }
+  store_out();
 }
 
 }  // namespace smlm

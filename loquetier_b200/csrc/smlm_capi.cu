@@ -630,10 +630,7 @@ inline size_t decode_ticket_bytes(int batch, int num_kv_heads) {
 
 template <typename T, int G>
 int launch_decode(const PdArgs& a, cudaStream_t stream) {
-  const int stage = 2 * a.page_size * kPdDim * static_cast<int>(sizeof(T));
-  constexpr int kRed = (G / pd_heads_per_thread(G)) * kPdEntryLanes * pd_heads_per_thread(G) * kPdRec * 4;
-  const int smem = std::max(kPdStages * stage, kRed);
-  return launch(paged_decode_kernel<T, G>, dim3(a.batch * a.num_kv_heads * a.splits, 1, 1), pd_threads(G), 1, smem,
+  return launch(paged_decode_kernel<T, G>, dim3(a.batch * a.num_kv_heads * a.splits, 1, 1), kPdWarps * 32, 1, kPdSmem,
                 stream, a);
 }
 
