@@ -13,7 +13,7 @@
  * (BatchedKvCache, kvcache.py:143-165).  A request's sequence length is
  * (pages - 1) * page_size + last_page_offset.  Keys are stored as projected, not rotated.
  *
- * Shapes served: head_dim 128; page_size a multiple of 8 up to 64; num_qo_heads / num_kv_heads in
+ * Shapes served: head_dim 128; page_size 8, 16, 32 or 64; num_qo_heads / num_kv_heads in
  * {1, 2, 4, 8}; fp16 and bf16.  Anything else is SMLM_ERR_NO_KERNEL, the reference's
  * "No suitable kernel." (kernel_src/csrc/loquetier_ops.cc:157-159).
  *

@@ -227,33 +227,46 @@ __global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArg
   const size_t head_off = (static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + kvh) * P * kPdDim;
   const size_t kv_delta = static_cast<size_t>(a.num_kv_heads) * P * kPdDim;
   bool bad_ptr = false;
-  auto issue = [&](int j) {   // j-th tile of this warp
+  const int lp = 31 - __clz(P);   // the page size is a power of two (checked by the host)
+  // The two halves of a tile (keys 0-7 and 8-15) each lie inside one page (pages hold a multiple of 8
+  // entries).  Their addresses are looked up one tile ahead, so that the loads of the page table are
+  // in flight while the previous tile is being computed and never sit in front of the copies.
+  const T* half_ptr[2] = {nullptr, nullptr};
+  auto lookup = [&](int j) {
+    half_ptr[0] = half_ptr[1] = nullptr;
+    if (j < ntw) {
+      const int key0 = (tile0 + warp + j * kPdWarps) * kPdTile;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int gk = key0 + 8 * h;
+        if (gk < seq_len) {
+          const T* page = static_cast<const T*>(a.kv_ptrs[p0 + (gk >> lp)]);
+          if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) bad_ptr = true;
+          else half_ptr[h] = page + head_off + static_cast<size_t>(gk & (P - 1)) * kPdDim;
+        }
+      }
+    }
+  };
+  auto issue = [&](int j) {   // j-th tile of this warp; its addresses were looked up before
     if (j < ntw) {
       const int key0 = (tile0 + warp + j * kPdWarps) * kPdTile;
       const uint32_t kst = ring + (j % kPdStages) * (2 * kPdTileBytes);
       const int cch = lane & 15;
-#pragma unroll 4
+#pragma unroll
       for (int k = 0; k < kPdTile / 2; ++k) {
         const int key = 2 * k + (lane >> 4);
-        const int gk = key0 + key;
-        bool ok = gk < seq_len;
-        const T* src = static_cast<const T*>(a.q);
-        if (ok) {
-          const T* page = static_cast<const T*>(a.kv_ptrs[p0 + gk / P]);
-          if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) {
-            bad_ptr = true;
-            ok = false;
-          } else {
-            src = page + head_off + static_cast<size_t>(gk % P) * kPdDim + cch * 8;
-          }
-        }
+        const T* hp = half_ptr[k >> 2];
+        const bool ok = hp != nullptr && key0 + key < seq_len;
+        const T* src = ok ? hp + (key & 7) * kPdDim + cch * 8 : static_cast<const T*>(a.q);
         const uint32_t dst = kst + key * 256 + ((cch ^ (key & 7)) << 4);
         cp_async16(dst, src, ok);                                             // keys past the end read as zeros
         cp_async16(dst + kPdTileBytes, ok ? src + kv_delta : src, ok);
       }
     }
     cp_async_commit();
+    lookup(j + 1);
   };
+  lookup(0);
 #pragma unroll
   for (int j = 0; j < kPdStages - 1; ++j) issue(j);
 
@@ -282,7 +295,7 @@ __global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArg
       float cc[2], ss[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) sincospif(static_cast<float>(key0) * fr[i], &ss[i], &cc[i]);
-#pragma unroll 4
+#pragma unroll
       for (int e = 0; e < kPdTile; ++e) {
         const uint32_t ao = kst + e * 256 + ((((lane >> 2) ^ (e & 7))) << 4) + (lane & 3) * 4;
         uint32_t wo, wp;
@@ -303,9 +316,10 @@ __global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArg
     }
     __syncwarp();
     // S = Q . K^T
-    float sc[2][4];
+    // (even and odd k steps accumulate separately: two shorter chains of dependent MMAs)
+    float sc[4][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    for (int n = 0; n < 4; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < 8; ++ks) {
       uint32_t bf[4];
@@ -313,11 +327,11 @@ __global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArg
       const int key = (m >> 1) * 8 + (lane & 7);
       const int chunk = ks * 2 + (m & 1);
       ldsm_x4(bf, kst + key * 256 + ((chunk ^ (key & 7)) << 4));
-      mma16816<T>(sc[0], qf[ks], bf[0], bf[1]);
-      mma16816<T>(sc[1], qf[ks], bf[2], bf[3]);
+      mma16816<T>(sc[(ks & 1) * 2], qf[ks], bf[0], bf[1]);
+      mma16816<T>(sc[(ks & 1) * 2 + 1], qf[ks], bf[2], bf[3]);
     }
     // running softmax of row g over this lane's keys 2t, 2t+1, 8+2t, 9+2t
-    float x[4] = {sc[0][0], sc[0][1], sc[1][0], sc[1][1]};
+    float x[4] = {sc[0][0] + sc[2][0], sc[0][1] + sc[2][1], sc[1][0] + sc[3][0], sc[1][1] + sc[3][1]};
     const int kb = key0 + 2 * t;
     if (kb >= seq_len) x[0] = -INFINITY;
     if (kb + 1 >= seq_len) x[1] = -INFINITY;

@@ -646,7 +646,7 @@ int dispatch_decode(const PdArgs& a, int group, cudaStream_t stream) {
 }
 
 inline bool kv_shape_ok(int head_dim, int page_size) {
-  return head_dim == kPdDim && page_size >= 8 && page_size <= 64 && page_size % 8 == 0;
+  return head_dim == kPdDim && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
 
 int run_append(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset, const void* k,
