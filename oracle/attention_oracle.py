@@ -16,6 +16,8 @@ What it restates (paths inside the reference checkout):
   ``(seq_len - 1) % page_size`` of page ``(seq_len - 1) // page_size``.
 * ``init_kv``    - AppendPagedKVCachePrefillKernel, page.cuh:411-444: the run of new tokens fills the
   LAST ``n`` positions of the sequence.
+* ``batch_prefill`` - BatchPrefillWithPagedKVCacheKernel, prefill.cuh:904-1060 (causal; query i of a request
+  at position ``kv_len - qo_len + i``); same rotation, scale and softmax as below.
 * ``batch_decode`` - BatchDecodeWithPagedKVCacheKernel, decode.cuh:451-620, with the settings of
   FlashInferBatchDecodeKernel (kernel_src/csrc/flashinfer_adapter/flashinfer_all.cu:85-108): Llama
   rotary mode, rope scale 1, ``sm_scale = 1 / sqrt(head_dim)`` (decode.cuh:1052); the query is rotated
@@ -119,6 +121,37 @@ def batch_decode(q: torch.Tensor, pages: Sequence[torch.Tensor], indptr: Sequenc
             logits = (kr[h // G] @ qr[h]) / np.sqrt(D)
             p = torch.softmax(logits, dim=0)
             out[b, h] = p @ V[:, h // G, :]
+    return out.to(q.dtype)
+
+
+def batch_prefill(q: torch.Tensor, qo_indptr: Sequence[int], pages: Sequence[torch.Tensor], indptr: Sequence[int],
+                  last_page_offset: Sequence[int], layer_idx: int, rope_theta: float) -> torch.Tensor:
+    """Causal self-attention of a ragged batch of prompts over their paged caches
+    (BatchPrefillWithPagedKVCacheKernel, prefill.cuh:904-1060, with the settings of
+    FlashInferBatchPrefillKernel, flashinfer_all.cu:48-83: causal, Llama rotary mode, rope scale 1).
+    ``q [sum(qo_len), Nq, D]``; request b owns rows ``qo_indptr[b] .. qo_indptr[b + 1]``; its cache already
+    holds all ``kv_len >= qo_len`` keys (init_kv ran before).  Query i of a request sits at position
+    ``kv_len - qo_len + i`` (prefill.cuh:262) and sees the keys at positions up to its own (:397)."""
+    Tq, Nq, D = q.shape
+    N = pages[0].shape[2]
+    G = Nq // N
+    out = torch.zeros((Tq, Nq, D), dtype=torch.float64)
+    for b in range(len(qo_indptr) - 1):
+        a0, a1 = qo_indptr[b], qo_indptr[b + 1]
+        n = a1 - a0
+        if n <= 0:
+            continue
+        K, V = gather_kv(pages, indptr[b], indptr[b + 1], last_page_offset[b], layer_idx)
+        L = K.shape[0]
+        pos_q = torch.arange(L - n, L)
+        qr = rope(q[a0:a1].to(torch.float64).permute(1, 0, 2), pos_q.expand(Nq, n), rope_theta)    # [Nq, n, D]
+        kr = rope(K.permute(1, 0, 2), torch.arange(L).expand(N, L), rope_theta)                     # [N, L, D]
+        mask = torch.arange(L).unsqueeze(0) > pos_q.unsqueeze(1)                                     # [n, L]
+        for h in range(Nq):
+            logits = (qr[h] @ kr[h // G].t()) / np.sqrt(D)
+            logits = logits.masked_fill(mask, float("-inf"))
+            p = torch.softmax(logits, dim=1)
+            out[a0:a1, h] = p @ V[:, h // G, :]
     return out.to(q.dtype)
 
 

@@ -71,3 +71,25 @@ def test_append_and_init_fill_the_last_positions():
         K0, _ = A.gather_kv(before, indptr[b], indptr[b + 1], last[b], 0)
         assert torch.equal(K[:L - runs[b]], K0[:L - runs[b]])
     assert A.last_page_offset_of(16, 16) == 16 and A.last_page_offset_of(17, 16) == 1
+
+
+def test_paged_prefill_equals_dense_causal_attention_and_decode_of_its_last_row():
+    P, N, G, D = 16, 2, 4, 128
+    seqlens = [5, 16, 40]          # keys in the cache
+    qlens = [5, 9, 40]             # the last qlens[b] positions are the prompt being prefilled
+    pages, indptr, last = A.make_cache(7, seqlens, 1, N, P, D, torch.float32)
+    g = torch.Generator().manual_seed(8)
+    qind = [0] + list(np.cumsum(qlens))
+    q = torch.randn((qind[-1], N * G, D), generator=g)
+    o = A.batch_prefill(q, qind, pages, indptr, last, 0, 10000.0)
+    for b, (L, n) in enumerate(zip(seqlens, qlens)):
+        K, V = A.gather_kv(pages, indptr[b], indptr[b + 1], last[b], 0)
+        for i in range(n):
+            pos = L - n + i
+            want = _dense(q[qind[b] + i].double().numpy(), K.numpy()[:pos + 1], V.numpy()[:pos + 1], 10000.0)
+            assert np.allclose(o[qind[b] + i].double().numpy(), want, rtol=1e-5, atol=1e-6)
+    # the last query of every prompt sees the whole cache: it is a decode step
+    last_q = torch.stack([q[qind[b + 1] - 1] for b in range(3)])
+    od = A.batch_decode(last_q, pages, indptr, last, 0, 10000.0)
+    for b in range(3):
+        assert torch.allclose(od[b], o[qind[b + 1] - 1], rtol=1e-5, atol=1e-6)
