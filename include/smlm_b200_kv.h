@@ -52,6 +52,23 @@ int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, c
                            int batch_size, int total_pages, int num_qo_heads, int num_kv_heads, int head_dim,
                            int num_layers, int layer_idx, int page_size, float rope_theta, int dtype, void* stream);
 
+/* Causal self-attention of a ragged batch of prompts over their paged caches.  Request b owns the rows
+ * qo_indptr[b] .. qo_indptr[b + 1] of q and o ([total_q, num_qo_heads, head_dim], 16-byte aligned); its cache
+ * already holds all L_b >= n_b keys (init_kv ran before).  Query i of the request stands at position
+ * L_b - n_b + i and attends to the keys 0 .. its own position:
+ *   o[i, h] = softmax( rope(q[i, h], pos_i) . rope(K_b[0..pos_i, h / group])^T / sqrt(head_dim) ) . V_b[0..pos_i]
+ * Replaces batch_prefill (kernel_src/csrc/loquetier_ops.cc:90-136; FlashInferBatchPrefillKernel,
+ * kernel_src/csrc/flashinfer_adapter/flashinfer_all.cu:48-83; BatchPrefillWithPagedKVCacheKernel,
+ * kernel_src/third_party/flashinfer/include/flashinfer/prefill.cuh:904-1060), without the reference's 64 MiB
+ * `tmpbuf` and without its copy of qo_indptr to the host: no workspace, no synchronisation.  A request with
+ * more queries than keys sets bit 1 of the status word; its rows that see no key are zeros.  Status value 8: a
+ * bounded wait inside the kernel gave up (the output is then not valid). */
+int smlm_b200_batch_prefill(void* o, const void* q, const int32_t* qo_indptr, const void* const* kv_ptrs,
+                            const int32_t* kv_indptr, const int32_t* last_page_offset, int* status_word,
+                            int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
+                            int head_dim, int num_layers, int layer_idx, int page_size, float rope_theta, int dtype,
+                            void* stream);
+
 /* Writes the key and value of ONE new token per request into the last valid entry of its cache
  * (the pages must already account for the token).  k, v: [batch, num_kv_heads, head_dim].  Replaces
  * append_kv (loquetier_ops.cc:230-273; AppendPagedKVCacheDecodeKernel, page.cuh:368-396), without its

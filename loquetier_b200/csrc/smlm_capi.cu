@@ -13,6 +13,7 @@
 #include "../../include/smlm_b200.h"
 #include "../../include/smlm_b200_kv.h"
 #include "paged_kv.cuh"
+#include "paged_prefill.cuh"
 #include "rms_norm.cuh"
 #include "smlm_fused.cuh"
 #include "smlm_fused_tc.cuh"
@@ -645,6 +646,20 @@ int dispatch_decode(const PdArgs& a, int group, cudaStream_t stream) {
   }
 }
 
+template <typename T>
+int dispatch_prefill(const PfArgs& a, int group, cudaStream_t stream) {
+  // query tiles: sum over requests of ceil(len / positions per tile) <= total_q / positions per tile + batch
+  const int ppt = kPfRows / group;
+  const dim3 grid((a.total_q / ppt + a.batch) * a.num_kv_heads, 1, 1);
+  switch (group) {
+    case 1: return launch(paged_prefill_kernel<T, 1>, grid, kPfThreads, 1, kPfSmem, stream, a);
+    case 2: return launch(paged_prefill_kernel<T, 2>, grid, kPfThreads, 1, kPfSmem, stream, a);
+    case 4: return launch(paged_prefill_kernel<T, 4>, grid, kPfThreads, 1, kPfSmem, stream, a);
+    case 8: return launch(paged_prefill_kernel<T, 8>, grid, kPfThreads, 1, kPfSmem, stream, a);
+    default: return SMLM_ERR_NO_KERNEL;
+  }
+}
+
 inline bool kv_shape_ok(int head_dim, int page_size) {
   return head_dim == kPdDim && (page_size == 8 || page_size == 16 || page_size == 32 || page_size == 64);
 }
@@ -1096,6 +1111,33 @@ int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, c
   a.log2_theta = std::log2(rope_theta);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return dtype == SMLM_F16 ? dispatch_decode<__half>(a, group, st) : dispatch_decode<__nv_bfloat16>(a, group, st);
+}
+
+int smlm_b200_batch_prefill(void* o, const void* q, const int32_t* qo_indptr, const void* const* kv_ptrs,
+                            const int32_t* kv_indptr, const int32_t* last_page_offset, int* status_word,
+                            int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
+                            int head_dim, int num_layers, int layer_idx, int page_size, float rope_theta, int dtype,
+                            void* stream) {
+  if (batch_size < 0 || total_q < 0 || total_pages < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_layers <= 0 ||
+      layer_idx < 0 || layer_idx >= num_layers || !(rope_theta > 0.f))
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
+  if (num_qo_heads % num_kv_heads != 0 || !kv_shape_ok(head_dim, page_size)) return SMLM_ERR_NO_KERNEL;
+  const int group = num_qo_heads / num_kv_heads;
+  if (group != 1 && group != 2 && group != 4 && group != 8) return SMLM_ERR_NO_KERNEL;
+  if (batch_size == 0 || total_q == 0) return SMLM_OK;
+  if (o == nullptr || q == nullptr || qo_indptr == nullptr || kv_ptrs == nullptr || kv_indptr == nullptr ||
+      last_page_offset == nullptr)
+    return SMLM_ERR_INVALID_ARGUMENT;
+  if (!aligned16(o) || !aligned16(q)) return SMLM_ERR_MISALIGNED;
+  PfArgs a;
+  a.o = o; a.q = q; a.qo_indptr = qo_indptr; a.kv_ptrs = kv_ptrs; a.kv_indptr = kv_indptr;
+  a.last_page_offset = last_page_offset; a.err = status_word;
+  a.batch = batch_size; a.num_kv_heads = num_kv_heads; a.num_layers = num_layers; a.layer_idx = layer_idx;
+  a.page_size = page_size; a.total_pages = total_pages; a.total_q = total_q;
+  a.log2_theta = std::log2(rope_theta);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  return dtype == SMLM_F16 ? dispatch_prefill<__half>(a, group, st) : dispatch_prefill<__nv_bfloat16>(a, group, st);
 }
 
 int smlm_b200_append_kv(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset,

@@ -98,6 +98,38 @@ def _no_kernel(e, q, page_size, group_size):
     return e
 
 
+def batch_prefill(o: torch.Tensor, q: torch.Tensor, qo_indptr: torch.Tensor, kv_ptrs: torch.Tensor,
+                  kv_indptr: torch.Tensor, last_page_offset: torch.Tensor, tmpbuf: torch.Tensor, num_layers: int,
+                  layer_idx: int, num_kv_heads: int, base: float, page_size: int) -> None:
+    """Causal prefill attention over the paged cache with the arguments and checks of the reference's
+    binding (batch_prefill, loquetier_ops.cc:90-136).  ``tmpbuf`` is accepted for compatibility and not
+    used (the reference wants 64 MiB of it and copies ``qo_indptr`` to the host).  Does not synchronise."""
+    from . import kvcache
+    for t, name in ((o, "o"), (q, "q")):
+        ops._chk_cuda_contig(t, name, 3)
+    ops._chk_cuda_contig(qo_indptr, "qo_indptr", 1)
+    if o.shape != q.shape:
+        raise RuntimeError("CHECK_SHAPE(o, q) failed")
+    batch_size = int(last_page_offset.size(0)) if last_page_offset.dim() == 1 else 0
+    num_qo_heads = int(o.size(1))
+    group_size = num_qo_heads // max(int(num_kv_heads), 1)
+    if num_qo_heads != group_size * num_kv_heads:
+        raise RuntimeError(f"CHECK_EQ(num_qo_heads, group_size * num_kv_heads) failed. "
+                           f"{num_qo_heads} vs {group_size * num_kv_heads}")
+    _chk_kv(kv_ptrs, kv_indptr, last_page_offset, batch_size)
+    if qo_indptr.dtype != torch.int32:
+        raise RuntimeError("expected scalar type Int but found " + str(qo_indptr.dtype))
+    if qo_indptr.size(0) != batch_size + 1:
+        raise RuntimeError(f"CHECK_EQ(qo_indptr.size(0), batch_size + 1) failed. {qo_indptr.size(0)} vs {batch_size + 1}")
+    if tmpbuf.numel() * tmpbuf.element_size() < 4 * (4 * batch_size + 1):
+        raise RuntimeError("CHECK_GE(tmpbuf.nbytes(), sizeof(int32_t) * (4 * batch_size + 1)) failed")
+    try:
+        kvcache.batch_prefill_into(o, q, qo_indptr, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx,
+                                   num_kv_heads, base, page_size)
+    except RuntimeError as e:
+        raise _no_kernel(e, q, page_size, group_size) from None
+
+
 def batch_decode(o: torch.Tensor, q: torch.Tensor, kv_ptrs: torch.Tensor, kv_indptr: torch.Tensor,
                  last_page_offset: torch.Tensor, tmpbuf: torch.Tensor, num_layers: int, layer_idx: int,
                  num_kv_heads: int, base: float, page_size: int) -> None:

@@ -1,7 +1,7 @@
 """Paged key-value cache of the decode path: the mirror of ``KvPool``, ``KvCache`` and
 ``BatchedKvCache`` of the reference (kernel_src/src/loquetier/utils/kvcache.py:7-50, 87-141, 143-165)
 with the same constructors, properties and methods, plus the three attention-side operators
-``batch_decode``, ``init_kv`` and ``append_kv`` of kernel_src/src/loquetier/ops/__init__.py:60-170
+``batch_prefill``, ``batch_decode``, ``init_kv`` and ``append_kv`` of kernel_src/src/loquetier/ops/__init__.py:18-170
 on the B200 kernels.
 
 A page is one tensor ``[num_layers, 2, num_heads, page_len, head_dim]``, as in the reference.  The pool
@@ -197,6 +197,31 @@ def batch_decode(q: torch.Tensor, kv: BatchedKvCache, base: float, layer_idx: in
     o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
     return batch_decode_into(o, q, kv.ptrs, kv.indptr, kv.last_page_offset, kv.pool.num_layers, layer_idx,
                              kv.pool.num_heads, base, kv.pool.page_len)
+
+
+def batch_prefill_into(o, q, qo_indptr, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx, num_kv_heads,
+                       base, page_size, status_word=None):
+    with torch.cuda.device(q.device):
+        check(lib.smlm_b200_batch_prefill(o.data_ptr(), q.data_ptr(), qo_indptr.data_ptr(), kv_ptrs.data_ptr(),
+                                          kv_indptr.data_ptr(), last_page_offset.data_ptr(),
+                                          None if status_word is None else status_word.data_ptr(),
+                                          int(last_page_offset.numel()), int(q.size(0)), int(kv_ptrs.numel()),
+                                          int(q.size(1)), int(num_kv_heads), int(q.size(2)), int(num_layers),
+                                          int(layer_idx), int(page_size), float(base), _dtype_code(q), _stream(q)),
+              "smlm_b200_batch_prefill")
+    return o
+
+
+def batch_prefill(q: torch.Tensor, qo_indptr: torch.Tensor, kv: BatchedKvCache, base: float,
+                  layer_idx: int) -> torch.Tensor:
+    """Causal self-attention with rotary position encoding for each prompt of the batch
+    (batch_prefill, kernel_src/src/loquetier/ops/__init__.py:18-57).  ``q``
+    ``[sum(seqlen), num_heads, head_dim]`` and the keys in ``kv`` are NOT position encoded; request b owns
+    rows ``qo_indptr[b] .. qo_indptr[b + 1]`` (int32, on the device).  Returns the attention output in the
+    shape of ``q``."""
+    o = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    return batch_prefill_into(o, q, qo_indptr, kv.ptrs, kv.indptr, kv.last_page_offset, kv.pool.num_layers,
+                              layer_idx, kv.pool.num_heads, base, kv.pool.page_len)
 
 
 def init_kv_raw(kv_ptrs, kv_indptr, last_page_offset, k, v, seqlen_indptr, num_layers, layer_idx, num_kv_heads,

@@ -29,6 +29,8 @@ def lib():
         L.ref_rms_norm.argtypes = [c_void_p] * 4 + [c_int, c_int, c_float, c_int, c_void_p]
         L.ref_batch_decode.restype = c_int
         L.ref_batch_decode.argtypes = [c_void_p] * 6 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]
+        L.ref_batch_prefill.restype = c_int
+        L.ref_batch_prefill.argtypes = [c_void_p] * 8 + [c_int] * 4 + [c_float, c_int, c_int, c_void_p]
         L.ref_append_kv.restype = c_int
         L.ref_append_kv.argtypes = [c_void_p] * 6 + [c_int] * 6 + [c_void_p]
         _lib = L
@@ -75,6 +77,25 @@ def batch_decode(o, q, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_i
                                 last_page_offset.data_ptr(), aux.data_ptr(), int(num_layers), int(layer_idx),
                                 int(q.size(1)) // int(num_kv_heads), int(num_kv_heads), float(base), B, _code(q),
                                 torch.cuda.current_stream(q.device).cuda_stream)
+    torch.cuda.synchronize()
+    if not ok:
+        raise RuntimeError("No suitable kernel.")
+    return o
+
+
+def batch_prefill(o, q, qo_indptr, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx, num_kv_heads, base):
+    """The reference's prefill attention (flashinfer's BatchPrefillWithPagedKVCacheKernel with the adapter's
+    settings: causal, Llama rotary mode); page size 16, head dim 128, group size 1, 4 or 8.  The dispatcher
+    reads ``qo_indptr`` back to the host and synchronises."""
+    B = int(last_page_offset.numel())
+    aux = torch.zeros(4 * (B + 1), dtype=torch.int32, device=q.device)
+    tmp = torch.zeros(1024, dtype=torch.float32, device=q.device)   # handed to the kernel, which never reads it
+    torch.cuda.synchronize()
+    ok = lib().ref_batch_prefill(o.data_ptr(), q.data_ptr(), qo_indptr.data_ptr(), kv_ptrs.data_ptr(),
+                                 kv_indptr.data_ptr(), last_page_offset.data_ptr(), aux.data_ptr(), tmp.data_ptr(),
+                                 int(num_layers), int(layer_idx), int(q.size(1)) // int(num_kv_heads),
+                                 int(num_kv_heads), float(base), B, _code(q),
+                                 torch.cuda.current_stream(q.device).cuda_stream)
     torch.cuda.synchronize()
     if not ok:
         raise RuntimeError("No suitable kernel.")

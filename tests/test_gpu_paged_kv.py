@@ -1,5 +1,5 @@
-"""The paged key-value cache on the GPU through the C ABI: appending keys/values (bit-exact) and batch
-decode attention (rtol = atol = 1e-2 for 16-bit storage with fp32 arithmetic) against the CPU oracle,
+"""The paged key-value cache on the GPU through the C ABI: appending keys/values (bit-exact), batch
+decode and causal prefill attention (rtol = atol = 1e-2 for 16-bit storage with fp32 arithmetic) against the CPU oracle,
 and - where oracle/_ref/libref.so has been built - against the reference's own kernels."""
 import numpy as np
 import pytest
@@ -201,5 +201,146 @@ def test_decode_and_append_against_reference_kernels(dtype, group):
     ref_cuda.batch_decode(o_ref, q.to(DEV), ptrs_ref, ind, lst, Lyr, layer, N, THETA)
     o_lib = _decode(q.to(DEV), ptrs_lib, ind, lst, Lyr, layer, N, P)
     want = A.batch_decode(q, pages, indptr, last, layer, THETA)
+    assert_close(o_ref, want, what="reference kernel vs oracle")
+    assert_close(o_lib, o_ref, what="library vs reference kernel")
+
+
+# ---------------------------------------------------------------------------------------------
+# prefill
+# ---------------------------------------------------------------------------------------------
+
+def _prefill(q, qind, ptrs, ind, last, Lyr, layer, N, P, expect_word=0):
+    from loquetier_b200 import kvcache
+    o = torch.full(q.shape, 7.0, dtype=q.dtype, device=DEV)
+    word = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kvcache.batch_prefill_into(o, q, qind, ptrs, ind, last, Lyr, layer, N, THETA, P, status_word=word)
+    torch.cuda.synchronize()
+    assert int(word.item()) == expect_word, f"fault bits {int(word.item())}"
+    return o
+
+
+def _qind(qlens):
+    return [0] + [int(v) for v in np.cumsum(qlens)]
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group,P", [(1, 16), (2, 8), (4, 16), (8, 16), (4, 32), (1, 64)])
+def test_prefill_matches_oracle(dtype, group, P):
+    """Ragged prompts: shorter than a key tile, exactly a tile, ragged query tiles, several query tiles, an
+    empty request, and one whose cache already held a prefix (queries are the last positions)."""
+    N, Lyr, layer = 2, 2, 1
+    seqlens = [1, 5, 64, 65, 130, 300, 0, 200]
+    qlens = [1, 5, 64, 65, 130, 300, 0, 77]
+    pages, indptr, last = A.make_cache(31 + group + P, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(group * 17 + P)
+    qind = _qind(qlens)
+    q = torch.randn((qind[-1], N * group, 128), generator=g).to(dtype)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    want = A.batch_prefill(q, qind, pages, indptr, last, layer, THETA)
+    assert_close(o, want, what=f"prefill group {group} page {P}")
+    o2 = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    assert torch.equal(o, o2)
+
+
+def test_prefill_long_prompt_and_last_row_is_a_decode_step():
+    """2500 positions (40 key tiles, 20 query tiles per head): the running-maximum policy and the barrier
+    phases go through many rounds; the last query of a prompt must agree with the decode kernel."""
+    N, group, P, Lyr = 2, 4, 16, 1
+    seqlens, qlens = [2500, 700], [2500, 700]
+    pages, indptr, last = A.make_cache(91, seqlens, Lyr, N, P, 128, torch.bfloat16)
+    g = torch.Generator().manual_seed(92)
+    qind = _qind(qlens)
+    q = (torch.randn((qind[-1], N * group, 128), generator=g) * 1.5).to(torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, 0, N, P)
+    sel = list(range(0, 2500, 97)) + [2499, 2500, 2500 + 699]
+    want = A.batch_prefill(q, qind, pages, indptr, last, 0, THETA)
+    assert_close(o[sel], want[sel], what="long prompt rows")
+    assert_close(o, want, what="long prompt")
+    last_q = torch.stack([q[qind[1] - 1], q[qind[2] - 1]]).to(DEV)
+    od = _decode(last_q, ptrs, ind, lst, Lyr, 0, N, P)
+    assert_close(torch.stack([o[qind[1] - 1], o[qind[2] - 1]]), od.cpu(), what="prefill last row vs decode")
+
+
+def test_prefill_large_scores_raise_the_running_maximum():
+    """Scores that grow along the sequence (keys scaled up with their index): every row's maximum is raised
+    again and again, so the accumulator in tensor memory is rescaled many times."""
+    N, group, P, Lyr = 1, 2, 16, 1
+    L = 700
+    pages, indptr, last = A.make_cache(55, [L], Lyr, N, P, 128, torch.float16)
+    for i, pg in enumerate(pages):
+        pg[:, 0] *= 1.0 + 0.1 * i        # keys of later pages are larger
+    g = torch.Generator().manual_seed(56)
+    q = (torch.randn((L, N * group, 128), generator=g) * 1.5).to(torch.float16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor([0, L], dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, 0, N, P)
+    want = A.batch_prefill(q, [0, L], pages, indptr, last, 0, THETA)
+    assert_close(o, want, what="raised maxima")
+
+
+def test_prefill_named_operator_and_cache_classes():
+    """init_kv then batch_prefill through the mirrored classes and through the reference's binding names."""
+    from loquetier_b200 import kernels, kvcache
+    N, group, P, Lyr, layer = 2, 4, 16, 2, 1
+    pool = kvcache.KvPool(num_layers=Lyr, num_heads=N, head_dim=128, page_len=P, dtype=torch.bfloat16, device=DEV)
+    lens = [40, 129]
+    caches = [kvcache.KvCache(pool, n) for n in lens]
+    bkv = kvcache.BatchedKvCache(caches)
+    g = torch.Generator().manual_seed(3)
+    T = sum(lens)
+    k = torch.randn((T, N, 128), generator=g).to(torch.bfloat16)
+    v = torch.randn((T, N, 128), generator=g).to(torch.bfloat16)
+    q = torch.randn((T, N * group, 128), generator=g).to(torch.bfloat16)
+    qind = torch.tensor([0, 40, 169], dtype=torch.int32, device=DEV)
+    kvcache.init_kv(bkv, k.to(DEV), v.to(DEV), qind, layer)
+    o = kvcache.batch_prefill(q.to(DEV), qind, bkv, THETA, layer)
+    o_named = torch.empty_like(o)
+    kernels.batch_prefill(o_named, q.to(DEV), qind, bkv.ptrs, bkv.indptr, bkv.last_page_offset,
+                          torch.empty(64, dtype=torch.uint8, device=DEV), Lyr, layer, N, THETA, P)
+    torch.cuda.synchronize()
+    assert torch.equal(o, o_named)
+    # dense causal attention of the same k, v
+    pages, indptr, last = A.make_cache(0, lens, Lyr, N, P, 128, torch.bfloat16)
+    A.init_kv(pages, indptr, last, k, v, [0, 40, 169], layer)
+    want = A.batch_prefill(q, [0, 40, 169], pages, indptr, last, layer, THETA)
+    assert_close(o, want, what="classes")
+    with pytest.raises(RuntimeError, match="No suitable kernel"):
+        kernels.batch_prefill(torch.empty((4, 6, 128), dtype=torch.bfloat16, device=DEV),
+                              torch.empty((4, 6, 128), dtype=torch.bfloat16, device=DEV),
+                              torch.tensor([0, 4], dtype=torch.int32, device=DEV), bkv.ptrs[:1], bkv.indptr[:2],
+                              bkv.last_page_offset[:1], torch.empty(64, dtype=torch.uint8, device=DEV), Lyr, layer, 2,
+                              THETA, P)   # 6 query heads on 2 kv heads: a group of 3
+
+
+def test_prefill_more_queries_than_keys_is_reported_not_faulted():
+    N, group, P, Lyr = 1, 1, 16, 1
+    pages, indptr, last = A.make_cache(8, [10], Lyr, N, P, 128, torch.bfloat16)
+    q = torch.randn((20, 1, 128)).to(torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor([0, 20], dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, 0, N, P,
+                 expect_word=1)
+    assert torch.isfinite(o.float()).all()
+    assert float(o[:10].float().abs().max()) == 0.0     # positions -10 .. -1 see no key
+
+
+@pytest.mark.skipif(not ref_cuda.available(), reason="oracle/_ref/libref.so not built")
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("group", [1, 4, 8])
+def test_prefill_against_reference_kernel(dtype, group):
+    """Three-way: the reference's flashinfer prefill kernel, this library, the oracle (page 16, head dim 128)."""
+    N, Lyr, layer, P = 2, 2, 1, 16
+    seqlens = [3, 64, 100, 517]
+    qlens = [3, 64, 100, 517]
+    pages, indptr, last = A.make_cache(171 + group, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(172)
+    qind = _qind(qlens)
+    q = torch.randn((qind[-1], N * group, 128), generator=g).to(dtype)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    qi = torch.tensor(qind, dtype=torch.int32, device=DEV)
+    o_ref = torch.zeros(q.shape, dtype=dtype, device=DEV)
+    ref_cuda.batch_prefill(o_ref, q.to(DEV), qi, ptrs, ind, lst, Lyr, layer, N, THETA)
+    o_lib = _prefill(q.to(DEV), qi, ptrs, ind, lst, Lyr, layer, N, P)
+    want = A.batch_prefill(q, qind, pages, indptr, last, layer, THETA)
     assert_close(o_ref, want, what="reference kernel vs oracle")
     assert_close(o_lib, o_ref, what="library vs reference kernel")
