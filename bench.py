@@ -1026,6 +1026,80 @@ def run_decode(a, rank, world, local, torch, dist, blocks, steps):
     return rec
 
 
+def tensor_peak():
+    try:
+        return float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        return 1590.0, "fallback"
+
+
+def run_prefill(a, rank, world, local, torch, dist, blocks, steps):
+    """Causal prefill attention over the paged key-value cache with the copy of the prompts' keys/values
+    into the pages in front of it (init_kv): Llama-3-8B heads (32 query, 8 kv, dim 128), page size 16, one
+    layer's pages, 32 prompts with lengths uniform in [256, 2048].  Prompts shard over ranks with no
+    collective.  The bound is the tensor cores: 4 * head_dim flops per (query, visible key, query head),
+    visible keys = positions up to the query's own."""
+    from loquetier_b200 import kvcache
+    dev = torch.device("cuda", local)
+    B, N, G, P, D = 32, 8, 4, 16, 128
+    rng = np.random.default_rng(9100 + rank)
+    seqlens = [int(v) for v in rng.integers(256, 2049, size=B)]
+    T = sum(seqlens)
+    pool = kvcache.KvPool(1, N, D, P, torch.bfloat16, dev, pages_per_slab=4096)
+    caches = [kvcache.KvCache(pool, L) for L in seqlens]
+    bkv = kvcache.BatchedKvCache(caches)
+    g = torch.Generator(device=dev).manual_seed(9100 + rank)
+    q = torch.randn((T, N * G, D), generator=g, device=dev).to(torch.bfloat16)
+    k = torch.randn((T, N, D), generator=g, device=dev).to(torch.bfloat16)
+    v = torch.randn((T, N, D), generator=g, device=dev).to(torch.bfloat16)
+    o = torch.empty_like(q)
+    qind_h = np.concatenate([[0], np.cumsum(seqlens)]).astype(np.int32)
+    qind = torch.tensor(qind_h, device=dev)
+    word = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def step():
+        kvcache.init_kv_raw(bkv.ptrs, bkv.indptr, bkv.last_page_offset, k, v, qind, 1, 0, N, P, status_word=word)
+        kvcache.batch_prefill_into(o, q, qind, bkv.ptrs, bkv.indptr, bkv.last_page_offset, 1, 0, N, 500000.0, P,
+                                   status_word=word)
+
+    step()
+    torch.cuda.synchronize()
+    assert int(word.item()) == 0, "the kernels recorded a fault"
+    fn = capture(step, torch) if not a.no_graph else step
+    ms, per = timed(fn, steps, max(3, a.warmup), torch, dist, None, blocks)
+    flops = float(sum(4 * D * N * G * (L * (L + 1) // 2) for L in seqlens))
+    nbytes = 2 * (2 * T * N * G * D + 4 * T * N * D)    # q, o; k, v read and written into the pages
+    peak, which = tensor_peak()
+    name = ("prefill: paged-KV causal prefill attention + init_kv, bf16, 32 prompts of 256..2048 tokens, "
+            "32 query / 8 kv heads of dim 128, page size 16")
+    rec = dict(workload=name, metric="prefill attention tokens/s", value=T * world / (ms * 1e-3), unit="tokens/s",
+               n_gpus=world, ms_per_step=ms, ms_per_step_min=min(per), ms_per_step_max=max(per), blocks=len(per),
+               prompt_tokens=T, pages=int(bkv.ptrs.numel()),
+               l2="%.0f MB of q, o, k, v per step (> 126 MB L2)" % (nbytes / 1e6),
+               roofline=dict(bound="tensor", achieved=flops / (ms * 1e-3) / 1e12, peak=peak, unit="TFLOP/s",
+                             frac=flops / (ms * 1e-3) / 1e12 / peak, peak_source=which, traffic=None,
+                             algorithmic_flops=flops,
+                             note="causal flops only (visible keys); the step also holds the init_kv copy"),
+               launch_mode="eager" if a.no_graph else "cuda graph replay", gpu_launches_per_step=2)
+    if a.check and rank == 0:
+        from oracle import attention_oracle as AO
+        sel = [int(i) for i in np.argsort(seqlens)[[0, B // 2]]]   # the shortest and the median prompt
+        pages, ind, last, qi, rows = [], [0], [], [0], []
+        for i in sel:
+            c = caches[i]
+            pages += [pg.cpu() for pg in c.pages]
+            ind.append(ind[-1] + c.num_pages)
+            last.append(AO.last_page_offset_of(c.seqlen, P))
+            qi.append(qi[-1] + seqlens[i])
+            rows += list(range(int(qind_h[i]), int(qind_h[i + 1])))
+        want = AO.batch_prefill(q[rows].cpu(), qi, pages, ind, last, 0, 500000.0)
+        err = (o[rows].cpu().float() - want.float()).abs()
+        assert bool((err <= 1e-2 + 1e-2 * want.float().abs()).all()), "prefill differs from the oracle"
+        rec["parity_checked"] = True
+        rec["parity_max_abs_err"] = float(err.max())
+    return rec
+
+
 def run_linear_host(a, local, torch):
     """Host time of one eager MixedLoraLinear.forward - what a model pays per LoRA linear and step on top
     of the kernels: wall clock around many forwards without a synchronisation in between, for the segment
@@ -1073,7 +1147,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear", "decode"])
+    ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear", "decode", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps; the median is reported")
     ap.add_argument("--sched", default="multi", choices=["multi", "multi_f", "split", "split2", "single"],
@@ -1110,7 +1184,7 @@ def main():
         if line is not None and rank == 0:
             print(json.dumps(line))
         return
-    if a.workload == "decode":
+    if a.workload in ("decode", "prefill"):
         assert torch.cuda.is_available(), "bench.py needs a CUDA device (there is no CPU fallback)"
         torch.cuda.set_device(local)
         dist = None
@@ -1118,7 +1192,8 @@ def main():
             import torch.distributed as dist_mod
             dist_mod.init_process_group("nccl", device_id=torch.device("cuda", local))
             dist = dist_mod
-        rec = run_decode(a, rank, world, local, torch, dist, a.blocks, a.steps)
+        rec = (run_decode if a.workload == "decode" else run_prefill)(a, rank, world, local, torch, dist, a.blocks,
+                                                                     a.steps)
         if dist is not None:
             dist.barrier()
             dist.destroy_process_group()
@@ -1281,6 +1356,10 @@ def main():
         dec = run_decode(sub, rank, world, local, torch, dist, max(3, a.blocks // 5), max(5, min(a.steps, 20)))
         if rank == 0:
             line["attention_decode"] = dec
+        torch.cuda.empty_cache()
+        pre = run_prefill(sub, rank, world, local, torch, dist, max(3, a.blocks // 5), max(5, min(a.steps, 20)))
+        if rank == 0:
+            line["attention_prefill"] = pre
     if rank == 0 and world == 1 and not a.no_cpu:
         base, _ = run_cpu(spec, torch)
         line["cpu_baseline"] = base

@@ -141,12 +141,42 @@ def decode_case():
                 library_ms=t_lib, reference_gbs=nbytes / t_ref / 1e6, library_gbs=nbytes / t_lib / 1e6)
 
 
+def prefill_case():
+    B, N, G, P, D = 32, 8, 4, 16, 128
+    rng = np.random.default_rng(9100)
+    seqlens = [int(v) for v in rng.integers(256, 2049, size=B)]
+    T = sum(seqlens)
+    pool = kvcache.KvPool(1, N, D, P, torch.bfloat16, DEV, pages_per_slab=4096)
+    caches = [kvcache.KvCache(pool, L) for L in seqlens]
+    bkv = kvcache.BatchedKvCache(caches)
+    g = torch.Generator(device=DEV).manual_seed(3)
+    q = torch.randn((T, N * G, D), generator=g, device=DEV).to(torch.bfloat16)
+    k = torch.randn((T, N, D), generator=g, device=DEV).to(torch.bfloat16)
+    v = torch.randn((T, N, D), generator=g, device=DEV).to(torch.bfloat16)
+    o_ref, o_lib = torch.empty_like(q), torch.empty_like(q)
+    qind = torch.tensor(np.concatenate([[0], np.cumsum(seqlens)]).astype(np.int32), device=DEV)
+    flops = float(sum(4 * D * N * G * (L * (L + 1) // 2) for L in seqlens))
+
+    def ref():
+        ref_cuda.append_kv(bkv.ptrs, bkv.indptr, bkv.last_page_offset, k, v, 1, 0, N, P, seqlen_indptr=qind)
+        ref_cuda.batch_prefill(o_ref, q, qind, bkv.ptrs, bkv.indptr, bkv.last_page_offset, 1, 0, N, 500000.0)
+
+    def lib():
+        kvcache.init_kv(bkv, k, v, qind, 0)
+        kvcache.batch_prefill_into(o_lib, q, qind, bkv.ptrs, bkv.indptr, bkv.last_page_offset, 1, 0, N, 500000.0, P)
+
+    t_ref, t_lib = _wall(ref), _events(lib)
+    err = float((o_ref.float() - o_lib.float()).abs().max())
+    return dict(prompts=B, prompt_tokens=T, causal_tflop=flops / 1e12, reference_ms=t_ref, library_ms=t_lib,
+                reference_tflops=flops / t_ref / 1e9, library_tflops=flops / t_lib / 1e9, max_abs_difference=err)
+
+
 def main():
     assert ref_cuda.available(), "build oracle/_ref/libref.so first (python oracle/build_ref.py --reference ...)"
     res = dict(gpu=torch.cuda.get_device_name(0),
                smlm_forward=dict(c2=smlm_case("c2"), c3=smlm_case("c3", only=("q_proj", "gate_proj")),
                                  c4=smlm_case("c4")),
-               rms_norm_forward=rms_case(), decode_attention=decode_case())
+               rms_norm_forward=rms_case(), decode_attention=decode_case(), prefill_attention=prefill_case())
     print(json.dumps(res, indent=1))
 
 
