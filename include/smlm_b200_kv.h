@@ -52,6 +52,11 @@ int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, c
                            int batch_size, int total_pages, int num_qo_heads, int num_kv_heads, int head_dim,
                            int num_layers, int layer_idx, int page_size, float rope_theta, int dtype, void* stream);
 
+/* Bytes of the workspace of smlm_b200_batch_prefill: one dense copy of the batch's keys (rotated) and values,
+ * total_pages * page_size * 2 * num_kv_heads * head_dim elements of the storage type.  Its contents need not
+ * survive between calls. */
+size_t smlm_b200_batch_prefill_workspace_bytes(int total_pages, int page_size, int num_kv_heads);
+
 /* Causal self-attention of a ragged batch of prompts over their paged caches.  Request b owns the rows
  * qo_indptr[b] .. qo_indptr[b + 1] of q and o ([total_q, num_qo_heads, head_dim], 16-byte aligned); its cache
  * already holds all L_b >= n_b keys (init_kv ran before).  Query i of the request stands at position
@@ -59,13 +64,15 @@ int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, c
  *   o[i, h] = softmax( rope(q[i, h], pos_i) . rope(K_b[0..pos_i, h / group])^T / sqrt(head_dim) ) . V_b[0..pos_i]
  * Replaces batch_prefill (kernel_src/csrc/loquetier_ops.cc:90-136; FlashInferBatchPrefillKernel,
  * kernel_src/csrc/flashinfer_adapter/flashinfer_all.cu:48-83; BatchPrefillWithPagedKVCacheKernel,
- * kernel_src/third_party/flashinfer/include/flashinfer/prefill.cuh:904-1060), without the reference's 64 MiB
- * `tmpbuf` and without its copy of qo_indptr to the host: no workspace, no synchronisation.  A request with
- * more queries than keys sets bit 1 of the status word; its rows that see no key are zeros.  Status value 8: a
- * bounded wait inside the kernel gave up (the output is then not valid). */
+ * kernel_src/third_party/flashinfer/include/flashinfer/prefill.cuh:904-1060), without its copy of qo_indptr
+ * to the host and its synchronisation.  Two launches: the pages are gathered once into the workspace (128-byte
+ * aligned, sized by the function above; the reference asks for a 64 MiB `tmpbuf` instead) with the keys rotated
+ * for their positions, then the attention kernel streams tiles of it with TMA.  A request with more queries
+ * than keys sets bit 1 of the status word; its rows that see no key are zeros.  Status value 8: a bounded wait
+ * inside the kernel gave up (the output is then not valid). */
 int smlm_b200_batch_prefill(void* o, const void* q, const int32_t* qo_indptr, const void* const* kv_ptrs,
-                            const int32_t* kv_indptr, const int32_t* last_page_offset, int* status_word,
-                            int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
+                            const int32_t* kv_indptr, const int32_t* last_page_offset, void* workspace,
+                            size_t workspace_bytes, int* status_word, int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
                             int head_dim, int num_layers, int layer_idx, int page_size, float rope_theta, int dtype,
                             void* stream);
 

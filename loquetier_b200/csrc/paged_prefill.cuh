@@ -4,31 +4,40 @@
 // FlashInferBatchPrefillKernel, kernel_src/csrc/flashinfer_adapter/flashinfer_all.cu:48-83: causal,
 // Llama rotary embedding applied to q and to the keys as they are read, rope scale 1).
 //
-// One CTA owns 128 rows of one (request, kv head): 128 / G consecutive query positions times the G query
-// heads that share the kv head (row = position * G + head, the reference's fusion of the group into the
-// row dimension, prefill.cuh:938-943), and walks the keys 0 .. its last position in tiles of 64:
+// Two launches.
 //
-//   S[128, 64]   = Q . K_tile^T      tcgen05.mma, A = Q and B = K both K-major in shared memory,
-//                                    fp32 accumulator in tensor memory (two buffers: the product of the
-//                                    next tile runs under the softmax of this one)
+// prefill_gather_kernel   reads every page of the batch once and writes the keys - rotated for their
+//                         position, rounded to the storage type - and the values into a dense scratch
+//                         [page slot = page * page_size + entry][K of all kv heads | V of all kv heads].  A
+//                         request's slots are consecutive, so a tile of 64 keys of one head is a box of a 2-D
+//                         tensor map: the attention kernel needs no address arithmetic, no page table and
+//                         no rotation in its loop.  Unused entries of a request's last page become zeros.
+//
+// paged_prefill_kernel    one CTA owns 128 rows of one (request, kv head): 128 / G consecutive query
+//                         positions times the G query heads that share the kv head (row = position * G +
+//                         head, the reference's fusion of the group into the row dimension,
+//                         prefill.cuh:938-943), and walks the keys 0 .. its last position in tiles of 64:
+//
+//   S[128, 64]   = Q . K_tile^T      tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32
+//                                    accumulator in tensor memory (two buffers: the product of the next
+//                                    tile runs under the softmax of this one)
 //   P            = exp2(S - m)       thread i owns row i (tensor-memory lane i): no shuffles
 //   O[128, 128] += P . V_tile        A = P (written to shared memory as 16-bit), B = V MN-major, i.e.
 //                                    exactly as the cache stores it; the accumulator stays in tensor
 //                                    memory for the whole walk
+//
+// Warp roles: warps 0-3 softmax (and the rotation of Q in the prologue), warp 4 the TMA producer of K and V
+// tiles (two-stage rings each: a K stage is free as soon as S is formed, V is held until P . V has been
+// read), warp 5 issues the MMAs.  All hand-offs are mbarriers; every wait is bounded.
 //
 // The running maximum of a row is only raised when the new one exceeds it by more than 2^8: until then P
 // is formed against the old maximum (values up to 256, exact in fp32 sums and harmless in 16 bits), and
 // the accumulator needs no rescaling.  When a row of a warp does cross the limit the warp rescales its 32
 // rows in tensor memory (tcgen05.ld / tcgen05.st).  The result O / l does not depend on which maximum was
 // used.
-//
-// Keys are stored unrotated, so every tile of K is rotated where it lies in shared memory before the MMA
-// reads it (the position of a key is its index in the sequence, prefill.cuh:262,1000); the rotated keys
-// are rounded to the storage type.  K and V tiles arrive with 16-byte cp.async copies straight from the
-// pages into the 128-byte-swizzled layout that the MMA descriptors name; K and V have their own two-stage
-// rings, because a K stage is free as soon as S is formed while V is held until P . V has been read.
-// Every wait on an mbarrier is bounded.
 #pragma once
+#include <cuda.h>
+
 #include "paged_kv.cuh"
 #include "smlm_fused_tc.cuh"
 
@@ -36,14 +45,14 @@ namespace smlm {
 
 constexpr int kPfRows = 128;                      // rows of a query tile
 constexpr int kPfKeys = 64;                       // keys of a tile
-constexpr int kPfThreads = 128;
+constexpr int kPfThreads = 192;
 constexpr int kPfQBytes = 2 * kPfRows * 128;      // two 64-dim panels of [128 rows][128 B]
 constexpr int kPfKvBytes = 2 * kPfKeys * 128;     // two 64-dim panels of [64 keys][128 B]
 constexpr int kPfKOff = kPfQBytes;                // K ring: 2 stages
 constexpr int kPfVOff = kPfKOff + 2 * kPfKvBytes; // V ring: 2 stages
 constexpr int kPfPOff = kPfVOff + 2 * kPfKvBytes; // P: [128 rows][128 B]
 constexpr int kPfBarOff = kPfPOff + kPfRows * 128;
-constexpr int kPfSmem = kPfBarOff + 64;           // 3 mbarriers, the tensor-memory address
+constexpr int kPfSmem = kPfBarOff + 128;          // 15 mbarriers, the tensor-memory address
 constexpr int kPfTmemCols = 256;                  // S: 2 x 64 columns, O: 128 columns
 constexpr float kPfRaise = 8.0f;                  // a row's maximum is raised when exceeded by this much (log2)
 static_assert(2 * (kPfSmem + 1024) <= 228 * 1024, "two CTAs per SM");
@@ -55,6 +64,7 @@ struct PfArgs {
   const void* const* kv_ptrs;
   const int32_t* kv_indptr;       // [B + 1]
   const int32_t* last_page_offset;  // [B]
+  void* scratch;                  // [total_pages * page_size][2 * Nkv * 128]: rotated K | V
   int* err;                       // error word, may be null
   int batch, num_kv_heads, num_layers, layer_idx, page_size, total_pages, total_q;
   float log2_theta;
@@ -81,10 +91,89 @@ __device__ __forceinline__ void pf_wait(uint32_t bar, uint32_t parity, int* err,
   if (err != nullptr) atomicOr(err, kErrTimeout);
 }
 
+// ---------------------------------------------------------------------------------------------
+// gather: pages -> dense scratch, keys rotated
+// ---------------------------------------------------------------------------------------------
+
+// grid: one CTA per page of the batch.  Thread = (entry of the page, 8-dim chunk c and its partner c + 8):
+// the sines and cosines of its eight frequencies at the entry's position serve all kv heads.
+template <typename T>
+__global__ void __launch_bounds__(128) prefill_gather_kernel(const PfArgs a) {
+  const int pg = blockIdx.x;
+  const int P = a.page_size;
+  pdl_wait();
+  // the request that owns page pg: the last b with kv_indptr[b] <= pg
+  int lo = 0, hi = a.batch;   // invariant: kv_indptr[lo] <= pg < kv_indptr[hi] (if the table is sound)
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (a.kv_indptr[mid] <= pg) lo = mid; else hi = mid;
+  }
+  const int b = lo;
+  const int p0 = a.kv_indptr[b], p1 = a.kv_indptr[b + 1];
+  T* rowbase = static_cast<T*>(a.scratch) + static_cast<size_t>(pg) * P * (2 * a.num_kv_heads * kPdDim);
+  const int row_elems = 2 * a.num_kv_heads * kPdDim;
+  const T* page = static_cast<const T*>(a.kv_ptrs[pg]);
+  int valid = 0;   // entries of this page that hold tokens
+  if (pg >= p0 && pg < p1 && p0 >= 0 && p1 <= a.total_pages) {
+    const int lv = a.last_page_offset[b];
+    valid = pg == p1 - 1 ? min(max(lv, 0), P) : P;
+  }
+  if (valid > 0 && (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0)) {
+    if (threadIdx.x == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
+    valid = 0;
+  }
+  const size_t kv_delta = static_cast<size_t>(a.num_kv_heads) * P * kPdDim;
+  for (int idx = threadIdx.x; idx < P * 8; idx += blockDim.x) {
+    const int e = idx >> 3, c = idx & 7;
+    T* dst = rowbase + static_cast<size_t>(e) * row_elems;
+    if (e >= valid) {   // zeros: nothing that is not a number may sit where a tile can reach
+      for (int h = 0; h < a.num_kv_heads; ++h) {
+        *reinterpret_cast<uint4*>(dst + h * kPdDim + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dst + h * kPdDim + 64 + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dst + (a.num_kv_heads + h) * kPdDim + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+        *reinterpret_cast<uint4*>(dst + (a.num_kv_heads + h) * kPdDim + 64 + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      continue;
+    }
+    const float pos = static_cast<float>((pg - p0) * P + e);
+    float cs[8], sn[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (c * 8 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
+      sincospif(pos * f, &sn[i], &cs[i]);
+    }
+    for (int h = 0; h < a.num_kv_heads; ++h) {
+      const T* src = page + ((static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + h) * P + e) * kPdDim + c * 8;
+      const uint4 ko = *reinterpret_cast<const uint4*>(src);
+      const uint4 kp = *reinterpret_cast<const uint4*>(src + 64);
+      const uint4 vo = *reinterpret_cast<const uint4*>(src + kv_delta);
+      const uint4 vp = *reinterpret_cast<const uint4*>(src + kv_delta + 64);
+      const uint32_t wo[4] = {ko.x, ko.y, ko.z, ko.w}, wp[4] = {kp.x, kp.y, kp.z, kp.w};
+      uint32_t ro[4], rp[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = unpack2<T>(wo[i]), y = unpack2<T>(wp[i]);
+        ro[i] = pack2<T>(x.x * cs[2 * i] - y.x * sn[2 * i], x.y * cs[2 * i + 1] - y.y * sn[2 * i + 1]);
+        rp[i] = pack2<T>(y.x * cs[2 * i] + x.x * sn[2 * i], y.y * cs[2 * i + 1] + x.y * sn[2 * i + 1]);
+      }
+      *reinterpret_cast<uint4*>(dst + h * kPdDim + c * 8) = make_uint4(ro[0], ro[1], ro[2], ro[3]);
+      *reinterpret_cast<uint4*>(dst + h * kPdDim + 64 + c * 8) = make_uint4(rp[0], rp[1], rp[2], rp[3]);
+      *reinterpret_cast<uint4*>(dst + (a.num_kv_heads + h) * kPdDim + c * 8) = vo;
+      *reinterpret_cast<uint4*>(dst + (a.num_kv_heads + h) * kPdDim + 64 + c * 8) = vp;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// attention
+// ---------------------------------------------------------------------------------------------
+
 // grid: (upper bound of query tiles over all requests) * Nkv; a CTA finds its request and tile itself,
-// because the query lengths live on the device.
+// because the query lengths live on the device.  kvmap: the scratch as [slots][2 * Nkv * 128], boxes of 64
+// slots x 64 columns with the 128-byte swizzle.
 template <typename T, int G>
-__global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfArgs a) {
+__global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfArgs a,
+                                                                      const __grid_constant__ CUtensorMap kvmap) {
   extern __shared__ __align__(1024) unsigned char pf_smem[];
   constexpr int PPT = kPfRows / G;   // query positions per tile
   const int tid = threadIdx.x;
@@ -158,21 +247,17 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   const uint32_t ks0 = sbase + kPfKOff;
   const uint32_t vs0 = sbase + kPfVOff;
   const uint32_t ps = sbase + kPfPOff;
-  const uint32_t bar_s0 = sbase + kPfBarOff;      // two barriers: S buffers
-  const uint32_t bar_o = bar_s0 + 16;
-  const uint32_t tmem_slot = bar_s0 + 32;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 32);
+  const uint32_t bars = sbase + kPfBarOff;
+  const uint32_t k_full = bars, k_empty = bars + 16, v_full = bars + 32, v_empty = bars + 48;   // two each
+  const uint32_t s_full = bars + 64, s_empty = bars + 80;                                        // two each
+  const uint32_t p_full = bars + 96, o_done = bars + 104, q_full = bars + 112;
+  const uint32_t tmem_slot = bars + 120;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 120);
 
   T* O = static_cast<T*>(a.o);
-  // this thread's row
-  const int my_qi = qi0 + tid / G;
-  const int my_head = kvh * G + tid % G;
-  const bool my_valid = tid / G < nq;
-  const int my_pos = my_valid ? pos0 + my_qi : last_pos;   // rows past the end behave like the last one
-
   if (ntiles == 0) {   // no key is visible: zeros
-    if (my_valid) {
-      uint4* op = reinterpret_cast<uint4*>(O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim);
+    if (tid < kPfRows && tid / G < nq) {
+      uint4* op = reinterpret_cast<uint4*>(O + (static_cast<size_t>(qo0 + qi0 + tid / G) * Nq + kvh * G + tid % G) * kPdDim);
 #pragma unroll
       for (int i = 0; i < 16; ++i) op[i] = make_uint4(0u, 0u, 0u, 0u);
     }
@@ -180,275 +265,250 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   }
 
   if (tid == 0) {
-    mbar_init(bar_s0, 1);
-    mbar_init(bar_s0 + 8, 1);
-    mbar_init(bar_o, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(k_full + i * 8, 1);
+      mbar_init(k_empty + i * 8, 1);
+      mbar_init(v_full + i * 8, 1);
+      mbar_init(v_empty + i * 8, 1);
+      mbar_init(s_full + i * 8, 1);
+      mbar_init(s_empty + i * 8, kPfRows);
+    }
+    mbar_init(p_full, kPfRows);
+    mbar_init(o_done, 1);
+    mbar_init(q_full, kPfRows);
     fence_mbar_init();
   }
-  if (warp == 0) {
+  if (warp == 5) {
     tc_alloc(tmem_slot, kPfTmemCols);
     tc_relinquish();
   }
-
-  // ---- loader of K and V tiles: thread = 16-byte column c16 of the 256-byte rows, keys (tid>>4) + 8 i ----
-  const size_t head_off = (static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + kvh) * P * kPdDim;
-  const size_t kv_delta = static_cast<size_t>(a.num_kv_heads) * P * kPdDim;
-  const int lp = 31 - __clz(P);
-  bool bad_ptr = false;
-  const int c16 = tid & 15;
-  const uint32_t ld_off = (c16 >> 3) * (kPfKeys * 128);
-  auto load_tile = [&](int j, uint32_t stage, bool value) {
-    if (j < ntiles) {
-      const int key0 = j * kPfKeys;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int key = (tid >> 4) + 8 * i;
-        const int gk = key0 + key;
-        const T* src = static_cast<const T*>(a.q);
-        bool ok = gk < nkeys;
-        if (ok) {
-          const T* page = static_cast<const T*>(a.kv_ptrs[p0 + (gk >> lp)]);
-          if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) {
-            bad_ptr = true;
-            ok = false;
-          } else {
-            src = page + head_off + (value ? kv_delta : 0) + static_cast<size_t>(gk & (P - 1)) * kPdDim + c16 * 8;
-          }
-        }
-        cp_async16(stage + ld_off + key * 128 + (((c16 & 7) ^ (key & 7)) << 4), src, ok);   // past the end: zeros
-      }
-    }
-    cp_async_commit();
-  };
-  load_tile(0, ks0, false);
-  load_tile(0, vs0, true);
-  load_tile(1, ks0 + kPfKvBytes, false);
-  load_tile(1, vs0 + kPfKvBytes, true);
-
-  // ---- the rotated, pre-scaled queries: A operand, K-major ----
-  {
-    const int d0 = (tid & 15) * 4;            // dims d0..d0+3 and their partners d0+64..
-    float fr[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      fr[i] = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
-    const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
-    for (int r = tid >> 4; r < kPfRows; r += 8) {
-      const int qi = qi0 + r / G;
-      float ro[4] = {0.f, 0.f, 0.f, 0.f}, rp[4] = {0.f, 0.f, 0.f, 0.f};
-      if (r / G < nq) {
-        const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi) * Nq + kvh * G + r % G) * kPdDim;
-        const uint2 uo = *reinterpret_cast<const uint2*>(qp + d0);
-        const uint2 up = *reinterpret_cast<const uint2*>(qp + d0 + 64);
-        const float2 o0 = unpack2<T>(uo.x), o1 = unpack2<T>(uo.y), q0 = unpack2<T>(up.x), q1 = unpack2<T>(up.y);
-        const float own[4] = {o0.x, o0.y, o1.x, o1.y}, par[4] = {q0.x, q0.y, q1.x, q1.y};
-        const float pos = static_cast<float>(max(pos0 + qi, 0));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float sn, cs;
-          sincospif(pos * fr[i], &sn, &cs);
-          ro[i] = (own[i] * cs - par[i] * sn) * qscale;
-          rp[i] = (par[i] * cs + own[i] * sn) * qscale;
-        }
-      }
-      const uint32_t addr = qs + r * 128 + (((d0 >> 3) ^ (r & 7)) << 4) + (d0 & 7) * 2;
-      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(pack2<T>(ro[0], ro[1])),
-                   "r"(pack2<T>(ro[2], ro[3])) : "memory");
-      asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr + kPfRows * 128), "r"(pack2<T>(rp[0], rp[1])),
-                   "r"(pack2<T>(rp[2], rp[3])) : "memory");
-    }
-  }
-
-  // ---- rotation of a K tile in place: warp w owns keys 16 w .. 16 w + 15, lane l the frequencies 2l, 2l+1 ----
-  float fr[2], c1[2], s1[2];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    fr[i] = exp2f(-a.log2_theta * static_cast<float>(2 * (2 * lane + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
-    sincospif(fr[i], &s1[i], &c1[i]);
-  }
-  auto rotate_tile = [&](int j, uint32_t kst) {
-    const int kbase = j * kPfKeys + warp * 16;
-    float cc[2], ss[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) sincospif(static_cast<float>(kbase) * fr[i], &ss[i], &cc[i]);
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      const int key = warp * 16 + e;
-      const uint32_t ao = kst + key * 128 + ((((lane >> 2) ^ (key & 7))) << 4) + (lane & 3) * 4;
-      uint32_t wo, wp;
-      asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wo) : "r"(ao));
-      asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wp) : "r"(ao + kPfKeys * 128));
-      const float2 ko = unpack2<T>(wo), kp = unpack2<T>(wp);
-      const uint32_t no = pack2<T>(ko.x * cc[0] - kp.x * ss[0], ko.y * cc[1] - kp.y * ss[1]);
-      const uint32_t np = pack2<T>(kp.x * cc[0] + ko.x * ss[0], kp.y * cc[1] + ko.y * ss[1]);
-      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao), "r"(no) : "memory");
-      asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao + kPfKeys * 128), "r"(np) : "memory");
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float cn = cc[i] * c1[i] - ss[i] * s1[i];
-        ss[i] = ss[i] * c1[i] + cc[i] * s1[i];
-        cc[i] = cn;
-      }
-    }
-  };
-
   tc_fence_before();
-  __syncthreads();   // barriers, the tensor-memory address and Q are visible
+  __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
-  const uint32_t my_tmem = tmem + (static_cast<uint32_t>(warp * 32) << 16);
-  const uint32_t idesc_s = tc_idesc<T>(kPfKeys, false);
-  const uint32_t idesc_o = tc_idesc<T>(kPdDim, true);
   bool dead = false;
 
-  auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
-    const uint32_t kst = ks0 + (j & 1) * kPfKvBytes;
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) {
-      const uint64_t ad = desc_kmajor(qs + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
-      const uint64_t bd = desc_kmajor(kst + (kk >> 2) * (kPfKeys * 128) + (kk & 3) * 32);
-      tc_mma(tmem + (j & 1) * kPfKeys, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
-    }
-    tc_commit(bar_s0 + (j & 1) * 8);
-  };
-
-  // first tile of K
-  cp_async_wait<3>();
-  __syncthreads();
-  rotate_tile(0, ks0);
-  fence_proxy_async();
-  __syncthreads();
-  if (tid == 0) {
-    tc_fence_after();
-    issue_s(0);
-  }
-
-  float m_ref = -INFINITY, l_run = 0.f;
-  for (int j = 0; j < ntiles; ++j) {
-    // A. the next tile's S runs on the tensor cores while this tile's softmax is computed
-    if (j + 1 < ntiles) {
-      cp_async_wait<1>();
-      __syncthreads();
-      rotate_tile(j + 1, ks0 + ((j + 1) & 1) * kPfKvBytes);
-      fence_proxy_async();
-      __syncthreads();
-      if (tid == 0) {
-        tc_fence_after();
-        issue_s(j + 1);
+  if (warp == 4) {
+    // ---------------- producer: K and V tiles by TMA ----------------
+    if (lane == 0) {
+      const int row0 = p0 * P;                    // the request's first slot of the scratch
+      const int xk = kvh * kPdDim, xv = (a.num_kv_heads + kvh) * kPdDim;
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j & 1, use = j >> 1;
+        const int y = row0 + j * kPfKeys;
+        if (use > 0) pf_wait(k_empty + st * 8, (use - 1) & 1, a.err, dead);
+        if (dead) break;   // nothing new is put in flight once a wait has given up
+        mbar_expect_tx(k_full + st * 8, kPfKvBytes);
+        tma_load_2d(ks0 + st * kPfKvBytes, &kvmap, xk, y, k_full + st * 8);
+        tma_load_2d(ks0 + st * kPfKvBytes + kPfKeys * 128, &kvmap, xk + 64, y, k_full + st * 8);
+        if (use > 0) pf_wait(v_empty + st * 8, (use - 1) & 1, a.err, dead);
+        if (dead) break;
+        mbar_expect_tx(v_full + st * 8, kPfKvBytes);
+        tma_load_2d(vs0 + st * kPfKvBytes, &kvmap, xv, y, v_full + st * 8);
+        tma_load_2d(vs0 + st * kPfKvBytes + kPfKeys * 128, &kvmap, xv + 64, y, v_full + st * 8);
       }
     }
-    // B. S(j)
-    pf_wait(bar_s0 + (j & 1) * 8, (j >> 1) & 1, a.err, dead);
-    tc_fence_after();
-    uint32_t sv[2][32];
-    tc_ld32(my_tmem + (j & 1) * kPfKeys, sv[0]);
-    tc_ld32(my_tmem + (j & 1) * kPfKeys + 32, sv[1]);
-    tc_wait_ld();
-    load_tile(j + 2, ks0 + (j & 1) * kPfKvBytes, false);   // the K stage of tile j is free
-    // C. softmax of this thread's row
-    const int lim = my_pos - j * kPfKeys;   // columns above lim are later keys
-    float mx = -INFINITY;
-    if (lim < kPfKeys - 1) {
+  } else if (warp == 5) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      const uint32_t idesc_s = tc_idesc<T>(kPfKeys, false);
+      const uint32_t idesc_o = tc_idesc<T>(kPdDim, true);
+      auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
+        const int st = j & 1, use = j >> 1;
+        pf_wait(k_full + st * 8, use & 1, a.err, dead);
+        if (use > 0) pf_wait(s_empty + st * 8, (use - 1) & 1, a.err, dead);
+        tc_fence_after();
+        if (!dead) {
+          const uint32_t kst = ks0 + st * kPfKvBytes;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const uint64_t ad = desc_kmajor(qs + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
+            const uint64_t bd = desc_kmajor(kst + (kk >> 2) * (kPfKeys * 128) + (kk & 3) * 32);
+            tc_mma(tmem + st * kPfKeys, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+          }
+        }
+        tc_commit(k_empty + st * 8);
+        tc_commit(s_full + st * 8);
+      };
+      pf_wait(q_full, 0, a.err, dead);
+      issue_s(0);
+      for (int j = 0; j < ntiles; ++j) {
+        if (j + 1 < ntiles) issue_s(j + 1);
+        const int st = j & 1;
+        pf_wait(v_full + st * 8, (j >> 1) & 1, a.err, dead);
+        pf_wait(p_full, j & 1, a.err, dead);
+        tc_fence_after();
+        if (!dead) {
+          const uint32_t vst = vs0 + st * kPfKvBytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t ad = desc_kmajor(ps + kk * 32);
+            const uint64_t bd = desc_mnmajor(vst + kk * 2048, kPfKeys * 128);
+            tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+          }
+        }
+        tc_commit(v_empty + st * 8);
+        tc_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------- softmax warps: thread = row ----------------
+    const int my_qi = qi0 + tid / G;
+    const int my_head = kvh * G + tid % G;
+    const bool my_valid = tid / G < nq;
+    const int my_pos = my_valid ? pos0 + my_qi : last_pos;   // rows past the end behave like the last one
+    const uint32_t my_tmem = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+
+    // the rotated, pre-scaled queries: A operand, K-major.  16 threads per row (4 dims and their partners
+    // each), 8 rows per pass; the position advances by 8 / G per pass, so the angle is stepped, not recomputed
+    {
+      const int d0 = (tid & 15) * 4;
+      const int rg = tid >> 4;
+      constexpr int STEP = 8 / G;
+      const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
+      float cc[4], ss[4], c1[4], s1[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
+        sincospif(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
+        sincospif(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
+      }
+#pragma unroll 4
+      for (int it = 0; it < kPfRows / 8; ++it) {
+        const int r = rg + 8 * it;
+        const int qi = qi0 + r / G;
+        uint32_t wo0 = 0u, wo1 = 0u, wp0 = 0u, wp1 = 0u;
+        if (r / G < nq) {
+          const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi) * Nq + kvh * G + r % G) * kPdDim;
+          const uint2 uo = *reinterpret_cast<const uint2*>(qp + d0);
+          const uint2 up = *reinterpret_cast<const uint2*>(qp + d0 + 64);
+          const float2 o0 = unpack2<T>(uo.x), o1 = unpack2<T>(uo.y), q0 = unpack2<T>(up.x), q1 = unpack2<T>(up.y);
+          const float own[4] = {o0.x, o0.y, o1.x, o1.y}, par[4] = {q0.x, q0.y, q1.x, q1.y};
+          float ro[4], rp[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ro[i] = (own[i] * cc[i] - par[i] * ss[i]) * qscale;
+            rp[i] = (par[i] * cc[i] + own[i] * ss[i]) * qscale;
+          }
+          wo0 = pack2<T>(ro[0], ro[1]); wo1 = pack2<T>(ro[2], ro[3]);
+          wp0 = pack2<T>(rp[0], rp[1]); wp1 = pack2<T>(rp[2], rp[3]);
+        }
+        const uint32_t addr = qs + r * 128 + (((d0 >> 3) ^ (r & 7)) << 4) + (d0 & 7) * 2;
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(wo0), "r"(wo1) : "memory");
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr + kPfRows * 128), "r"(wp0), "r"(wp1) : "memory");
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float cn = cc[i] * c1[i] - ss[i] * s1[i];
+          ss[i] = ss[i] * c1[i] + cc[i] * s1[i];
+          cc[i] = cn;
+        }
+      }
+      fence_proxy_async();   // the MMA reads Q through the async proxy
+      mbar_arrive(q_full);
+    }
+
+    float m_ref = -INFINITY, l_run = 0.f;
+    for (int j = 0; j < ntiles; ++j) {
+      const int st = j & 1;
+      pf_wait(s_full + st * 8, (j >> 1) & 1, a.err, dead);
+      tc_fence_after();
+      uint32_t sv[2][32];
+      tc_ld32(my_tmem + st * kPfKeys, sv[0]);
+      tc_ld32(my_tmem + st * kPfKeys + 32, sv[1]);
+      tc_wait_ld();
+      tc_fence_before();
+      mbar_arrive(s_empty + st * 8);   // the S buffer may be overwritten by the tile after next
+      const int lim = my_pos - j * kPfKeys;   // columns above lim are later keys
+      if (lim < kPfKeys - 1) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (h * 32 + i > lim) sv[h][i] = __float_as_uint(-INFINITY);
+      }
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        mx0 = fmaxf(mx0, __uint_as_float(sv[0][i]));
+        mx1 = fmaxf(mx1, __uint_as_float(sv[1][i]));
+      }
+      const float mx = fmaxf(mx0, mx1);
+      float rescale = 1.0f;
+      bool raise = false;
+      if (mx > m_ref + kPfRaise || m_ref == -INFINITY) {   // (-inf + 8 = -inf: the first visible key always raises)
+        if (mx != -INFINITY) {
+          raise = m_ref != -INFINITY;
+          rescale = exp2f(m_ref - mx);   // 0 when nothing was accumulated yet
+          m_ref = mx;
+        }
+      }
+      const float mm = m_ref == -INFINITY ? 0.f : m_ref;
+      float sum0 = 0.f, sum1 = 0.f;
+      uint32_t pw[32];
 #pragma unroll
       for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (h * 32 + i > lim) sv[h][i] = __float_as_uint(-INFINITY);
-    }
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sv[h][i]));
-    float rescale = 1.0f;
-    bool raise = false;
-    if (mx > m_ref + kPfRaise || m_ref == -INFINITY) {   // (-inf + 8 = -inf: the first visible key always raises)
-      if (mx != -INFINITY) {
-        raise = m_ref != -INFINITY;
-        rescale = exp2f(m_ref - mx);   // 0 when nothing was accumulated yet
-        m_ref = mx;
-      }
-    }
-    const float mm = m_ref == -INFINITY ? 0.f : m_ref;
-    float sum = 0.f;
-    uint32_t pw[32];
-#pragma unroll
-    for (int h = 0; h < 2; ++h)
-#pragma unroll
-      for (int i = 0; i < 32; i += 2) {
-        const float e0 = exp2f(__uint_as_float(sv[h][i]) - mm), e1 = exp2f(__uint_as_float(sv[h][i + 1]) - mm);
-        sum += e0 + e1;
-        pw[h * 16 + (i >> 1)] = pack2<T>(e0, e1);
-      }
-    l_run = l_run * rescale + sum;
-    // D. P . V of the previous tile has been read: P, O and its V stage are free
-    if (j > 0) {
-      pf_wait(bar_o, (j - 1) & 1, a.err, dead);
-      tc_fence_after();
-      load_tile(j + 1, vs0 + ((j + 1) & 1) * kPfKvBytes, true);
-      if (__any_sync(0xffffffffu, raise)) {
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t ov[32];
-          tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
-          tc_wait_ld();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * rescale);
-          tc_st32(my_tmem + 2 * kPfKeys + c * 32, ov);
+        for (int i = 0; i < 32; i += 2) {
+          const float e0 = exp2f(__uint_as_float(sv[h][i]) - mm), e1 = exp2f(__uint_as_float(sv[h][i + 1]) - mm);
+          sum0 += e0;
+          sum1 += e1;
+          pw[h * 16 + (i >> 1)] = pack2<T>(e0, e1);
         }
-        tc_wait_st();
-      }
-    } else {
-      cp_async_commit();   // keeps the count of copy groups the same in every iteration
-    }
-    // E. P as the A operand, then O += P . V(j)
-#pragma unroll
-    for (int c = 0; c < 8; ++c)
-      asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(ps + tid * 128 + ((c ^ (tid & 7)) << 4)),
-                   "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
-    cp_async_wait<2>();   // V(j) has landed (this thread's part)
-    fence_proxy_async();
-    tc_fence_before();
-    __syncthreads();
-    if (tid == 0) {
-      tc_fence_after();
-      const uint32_t vst = vs0 + (j & 1) * kPfKvBytes;
-#pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {
-        const uint64_t ad = desc_kmajor(ps + kk * 32);
-        const uint64_t bd = desc_mnmajor(vst + kk * 2048, kPfKeys * 128);
-        tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-      }
-      tc_commit(bar_o);
-    }
-  }
-  cp_async_wait<0>();
-  if (__any_sync(0xffffffffu, bad_ptr) && lane == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
-
-  // ---- the result: O / l ----
-  pf_wait(bar_o, (ntiles - 1) & 1, a.err, dead);
-  tc_fence_after();
-  const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-  T* op = O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim;
+      l_run = l_run * rescale + (sum0 + sum1);
+      // P . V of the previous tile has been read: P and O are free
+      if (j > 0) {
+        pf_wait(o_done, (j - 1) & 1, a.err, dead);
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-  for (int c = 0; c < 4; ++c) {
-    uint32_t ov[32];
-    tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
-    tc_wait_ld();
-    if (my_valid && !dead) {
+          for (int c = 0; c < 4; ++c) {
+            uint32_t ov[32];
+            tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
+            tc_wait_ld();
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint32_t w[4];
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * rescale);
+            tc_st32(my_tmem + 2 * kPfKeys + c * 32, ov);
+          }
+          tc_wait_st();
+        }
+      }
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          w[k] = pack2<T>(__uint_as_float(ov[i * 8 + 2 * k]) * inv, __uint_as_float(ov[i * 8 + 2 * k + 1]) * inv);
-        *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+      for (int c = 0; c < 8; ++c)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(ps + tid * 128 + ((c ^ (tid & 7)) << 4)),
+                     "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
+      tc_fence_before();
+      fence_proxy_async();   // the MMA reads P through the async proxy
+      mbar_arrive(p_full);
+    }
+
+    // ---- the result: O / l ----
+    pf_wait(o_done, (ntiles - 1) & 1, a.err, dead);
+    tc_fence_after();
+    const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+    T* op = O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim;
+#pragma unroll 1
+    for (int c = 0; c < 4; ++c) {
+      uint32_t ov[32];
+      tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
+      tc_wait_ld();
+      if (my_valid && !dead) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t w[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            w[k] = pack2<T>(__uint_as_float(ov[i * 8 + 2 * k]) * inv, __uint_as_float(ov[i * 8 + 2 * k + 1]) * inv);
+          *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
       }
     }
   }
+
+  // everyone is done with tensor memory: hand it back
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 0) tc_dealloc(tmem, kPfTmemCols);
+  if (warp == 5) tc_dealloc(tmem, kPfTmemCols);
 }
 
 }  // namespace smlm

@@ -647,15 +647,17 @@ int dispatch_decode(const PdArgs& a, int group, cudaStream_t stream) {
 }
 
 template <typename T>
-int dispatch_prefill(const PfArgs& a, int group, cudaStream_t stream) {
+int dispatch_prefill(const PfArgs& a, const CUtensorMap& kvmap, int group, cudaStream_t stream) {
+  int rc = launch(prefill_gather_kernel<T>, dim3(a.total_pages, 1, 1), 128, 1, 0, stream, a);
+  if (rc != SMLM_OK) return rc;
   // query tiles: sum over requests of ceil(len / positions per tile) <= total_q / positions per tile + batch
   const int ppt = kPfRows / group;
   const dim3 grid((a.total_q / ppt + a.batch) * a.num_kv_heads, 1, 1);
   switch (group) {
-    case 1: return launch(paged_prefill_kernel<T, 1>, grid, kPfThreads, 1, kPfSmem, stream, a);
-    case 2: return launch(paged_prefill_kernel<T, 2>, grid, kPfThreads, 1, kPfSmem, stream, a);
-    case 4: return launch(paged_prefill_kernel<T, 4>, grid, kPfThreads, 1, kPfSmem, stream, a);
-    case 8: return launch(paged_prefill_kernel<T, 8>, grid, kPfThreads, 1, kPfSmem, stream, a);
+    case 1: return launch(paged_prefill_kernel<T, 1>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);
+    case 2: return launch(paged_prefill_kernel<T, 2>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);
+    case 4: return launch(paged_prefill_kernel<T, 4>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);
+    case 8: return launch(paged_prefill_kernel<T, 8>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);
     default: return SMLM_ERR_NO_KERNEL;
   }
 }
@@ -1113,9 +1115,14 @@ int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, c
   return dtype == SMLM_F16 ? dispatch_decode<__half>(a, group, st) : dispatch_decode<__nv_bfloat16>(a, group, st);
 }
 
+size_t smlm_b200_batch_prefill_workspace_bytes(int total_pages, int page_size, int num_kv_heads) {
+  if (total_pages <= 0 || page_size <= 0 || num_kv_heads <= 0) return 0;
+  return static_cast<size_t>(total_pages) * page_size * 2 * num_kv_heads * kPdDim * 2;
+}
+
 int smlm_b200_batch_prefill(void* o, const void* q, const int32_t* qo_indptr, const void* const* kv_ptrs,
-                            const int32_t* kv_indptr, const int32_t* last_page_offset, int* status_word,
-                            int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
+                            const int32_t* kv_indptr, const int32_t* last_page_offset, void* workspace,
+                            size_t workspace_bytes, int* status_word, int batch_size, int total_q, int total_pages, int num_qo_heads, int num_kv_heads,
                             int head_dim, int num_layers, int layer_idx, int page_size, float rope_theta, int dtype,
                             void* stream) {
   if (batch_size < 0 || total_q < 0 || total_pages < 0 || num_qo_heads <= 0 || num_kv_heads <= 0 || num_layers <= 0 ||
@@ -1130,14 +1137,25 @@ int smlm_b200_batch_prefill(void* o, const void* q, const int32_t* qo_indptr, co
       last_page_offset == nullptr)
     return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(o) || !aligned16(q)) return SMLM_ERR_MISALIGNED;
+  if (total_pages == 0) return SMLM_ERR_INVALID_ARGUMENT;   // queries without a single page of keys
+  if (workspace == nullptr ||
+      workspace_bytes < smlm_b200_batch_prefill_workspace_bytes(total_pages, page_size, num_kv_heads))
+    return SMLM_ERR_WORKSPACE;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 127) != 0) return SMLM_ERR_MISALIGNED;
+  if (static_cast<long long>(total_pages) * page_size > 0x7fffffffLL) return SMLM_ERR_INVALID_ARGUMENT;
+  CUtensorMap kvmap;
+  if (!make_map_2d(&kvmap, workspace, total_pages * page_size, 2 * num_kv_heads * kPdDim, kPfKeys, dtype))
+    return SMLM_ERR_CUDA;
   PfArgs a;
+  a.scratch = workspace;
   a.o = o; a.q = q; a.qo_indptr = qo_indptr; a.kv_ptrs = kv_ptrs; a.kv_indptr = kv_indptr;
   a.last_page_offset = last_page_offset; a.err = status_word;
   a.batch = batch_size; a.num_kv_heads = num_kv_heads; a.num_layers = num_layers; a.layer_idx = layer_idx;
   a.page_size = page_size; a.total_pages = total_pages; a.total_q = total_q;
   a.log2_theta = std::log2(rope_theta);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  return dtype == SMLM_F16 ? dispatch_prefill<__half>(a, group, st) : dispatch_prefill<__nv_bfloat16>(a, group, st);
+  return dtype == SMLM_F16 ? dispatch_prefill<__half>(a, kvmap, group, st)
+                           : dispatch_prefill<__nv_bfloat16>(a, kvmap, group, st);
 }
 
 int smlm_b200_append_kv(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32_t* last_page_offset,

@@ -197,8 +197,8 @@ def append_kv(kv_ptrs: torch.Tensor, kv_indptr: torch.Tensor, last_page_offset: 
 
 def install_as_loquetier_kernels() -> types.ModuleType:
     """Make ``import loquetier.ops._kernels`` resolve to this module.  It carries the names of the SMLM
-    path, ``rms_norm`` and the decode side of the paged cache (``batch_decode``, ``init_kv``,
-    ``append_kv``); the reference's ``batch_prefill`` is not provided."""
+    path, ``rms_norm`` and the paged-cache attention (``batch_prefill``, ``batch_decode``, ``init_kv``,
+    ``append_kv``): every name the reference's extension module exports."""
     me = sys.modules[__name__]
     pkg = sys.modules.get("loquetier")
     if pkg is None:

@@ -199,12 +199,28 @@ def batch_decode(q: torch.Tensor, kv: BatchedKvCache, base: float, layer_idx: in
                              kv.pool.num_heads, base, kv.pool.page_len)
 
 
+_PREFILL_WS = {}
+
+
+def prefill_workspace(device, total_pages: int, page_size: int, num_kv_heads: int) -> torch.Tensor:
+    """Scratch of the prefill kernels (a dense, rotated copy of the batch's keys and values), cached per
+    device and grown on demand.  Calls that may overlap on different streams need workspaces of their own."""
+    need = int(lib.smlm_b200_batch_prefill_workspace_bytes(int(total_pages), int(page_size), int(num_kv_heads)))
+    ws = _PREFILL_WS.get(device)
+    if ws is None or ws.numel() < need:
+        ws = torch.empty(max(need, 1 << 20), dtype=torch.uint8, device=device)
+        _PREFILL_WS[device] = ws
+    return ws
+
+
 def batch_prefill_into(o, q, qo_indptr, kv_ptrs, kv_indptr, last_page_offset, num_layers, layer_idx, num_kv_heads,
-                       base, page_size, status_word=None):
+                       base, page_size, workspace=None, status_word=None):
+    ws = workspace if workspace is not None else prefill_workspace(q.device, kv_ptrs.numel(), page_size,
+                                                                   num_kv_heads)
     with torch.cuda.device(q.device):
         check(lib.smlm_b200_batch_prefill(o.data_ptr(), q.data_ptr(), qo_indptr.data_ptr(), kv_ptrs.data_ptr(),
-                                          kv_indptr.data_ptr(), last_page_offset.data_ptr(),
-                                          None if status_word is None else status_word.data_ptr(),
+                                          kv_indptr.data_ptr(), last_page_offset.data_ptr(), ws.data_ptr(),
+                                          ws.numel(), None if status_word is None else status_word.data_ptr(),
                                           int(last_page_offset.numel()), int(q.size(0)), int(kv_ptrs.numel()),
                                           int(q.size(1)), int(num_kv_heads), int(q.size(2)), int(num_layers),
                                           int(layer_idx), int(page_size), float(base), _dtype_code(q), _stream(q)),
