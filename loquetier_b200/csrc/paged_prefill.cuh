@@ -21,14 +21,17 @@
 //   S[128, 64]   = Q . K_tile^T      tcgen05.mma, A = Q and B = K both K-major in shared memory, fp32
 //                                    accumulator in tensor memory (two buffers: the product of the next
 //                                    tile runs under the softmax of this one)
-//   P            = exp2(S - m)       thread i owns row i (tensor-memory lane i): no shuffles
+//   P            = exp2(S - m)       a row is a tensor-memory lane: two threads per row, no shuffles
 //   O[128, 128] += P . V_tile        A = P (written to shared memory as 16-bit), B = V MN-major, i.e.
 //                                    exactly as the cache stores it; the accumulator stays in tensor
 //                                    memory for the whole walk
 //
-// Warp roles: warps 0-3 softmax (and the rotation of Q in the prologue), warp 4 the TMA producer of K and V
-// tiles (two-stage rings each: a K stage is free as soon as S is formed, V is held until P . V has been
-// read), warp 5 issues the MMAs.  All hand-offs are mbarriers; every wait is bounded.
+// Warp roles: warps 0-7 softmax (and the rotation of Q in the prologue) - two threads per row, each with
+// half of the columns, because one warp issues a chain of dependent instructions too slowly to keep up
+// with the tensor cores; warp 8 the TMA producer of K and V tiles (two-stage rings each: a K stage is free as
+// soon as S is formed, V is held until P . V has been read), warp 9 issues the MMAs of S and warp 10 those
+// of P . V.  All hand-offs are mbarriers (and one 64-thread barrier per row pair and tile); every wait is
+// bounded.
 //
 // The running maximum of a row is only raised when the new one exceeds it by more than 2^8: until then P
 // is formed against the old maximum (values up to 256, exact in fp32 sums and harmless in 16 bits), and
@@ -45,14 +48,15 @@ namespace smlm {
 
 constexpr int kPfRows = 128;                      // rows of a query tile
 constexpr int kPfKeys = 64;                       // keys of a tile
-constexpr int kPfThreads = 192;
+constexpr int kPfThreads = 352;                  // 8 softmax warps, the producer, two MMA issuers
 constexpr int kPfQBytes = 2 * kPfRows * 128;      // two 64-dim panels of [128 rows][128 B]
 constexpr int kPfKvBytes = 2 * kPfKeys * 128;     // two 64-dim panels of [64 keys][128 B]
-constexpr int kPfKOff = kPfQBytes;                // K ring: 2 stages
-constexpr int kPfVOff = kPfKOff + 2 * kPfKvBytes; // V ring: 2 stages
-constexpr int kPfPOff = kPfVOff + 2 * kPfKvBytes; // P: [128 rows][128 B]
+constexpr int kPfStages = 2;                      // stages of the K ring and of the V ring
+constexpr int kPfKOff = kPfQBytes;
+constexpr int kPfVOff = kPfKOff + kPfStages * kPfKvBytes;
+constexpr int kPfPOff = kPfVOff + kPfStages * kPfKvBytes;   // P: [128 rows][128 B]
 constexpr int kPfBarOff = kPfPOff + kPfRows * 128;
-constexpr int kPfSmem = kPfBarOff + 128;          // 15 mbarriers, the tensor-memory address
+constexpr int kPfSmem = kPfBarOff + 4 * kPfStages * 8 + 64;   // the rings' barriers, 7 more, the tensor-memory address
 constexpr int kPfTmemCols = 256;                  // S: 2 x 64 columns, O: 128 columns
 constexpr float kPfRaise = 8.0f;                  // a row's maximum is raised when exceeded by this much (log2)
 static_assert(2 * (kPfSmem + 1024) <= 228 * 1024, "two CTAs per SM");
@@ -68,7 +72,17 @@ struct PfArgs {
   int* err;                       // error word, may be null
   int batch, num_kv_heads, num_layers, layer_idx, page_size, total_pages, total_q;
   float log2_theta;
+#ifdef SMLM_PF_TIMING
+  long long* timing;              // development builds only: clock stamps of CTA 0
+#endif
 };
+
+#ifdef SMLM_PF_TIMING
+#define PF_STAMP(role, j, k) \
+  do { if (blockIdx.x == 0 && (j) < 64) a.timing[((role) * 64 + (j)) * 8 + (k)] = clock64(); } while (0)
+#else
+#define PF_STAMP(role, j, k) do { } while (0)
+#endif
 
 __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
@@ -81,6 +95,52 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
       : "memory");
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+// one column of 32 lanes
+__device__ __forceinline__ void tc_st1(uint32_t taddr, uint32_t v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n" ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t tc_ld1(uint32_t taddr) {   // load and wait for it
+  uint32_t v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];\n"
+               "tcgen05.wait::ld.sync.aligned;\n" : "=r"(v) : "r"(taddr) : "memory");
+  return v;
+}
+// packed pairs of fp32 (one instruction for two lanes on sm_100) and the three-input maximum
+__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) {
+  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
+// 64-thread barrier of the two warps that hold the same rows.  The barrier number is an immediate: with a
+// register operand the compiler reserves all 16 hardware barriers for the CTA, and only one CTA fits an SM.
+__device__ __forceinline__ void pair_barrier(int wq) {
+  switch (wq) {
+    case 0: asm volatile("bar.sync 1, 64;\n" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;\n" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;\n" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;\n" ::: "memory"); break;
+  }
+}
 
 // bounded wait that also works without an error word
 __device__ __forceinline__ void pf_wait(uint32_t bar, uint32_t parity, int* err, bool& dead) {
@@ -248,11 +308,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   const uint32_t vs0 = sbase + kPfVOff;
   const uint32_t ps = sbase + kPfPOff;
   const uint32_t bars = sbase + kPfBarOff;
-  const uint32_t k_full = bars, k_empty = bars + 16, v_full = bars + 32, v_empty = bars + 48;   // two each
-  const uint32_t s_full = bars + 64, s_empty = bars + 80;                                        // two each
-  const uint32_t p_full = bars + 96, o_done = bars + 104, q_full = bars + 112;
-  const uint32_t tmem_slot = bars + 120;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 120);
+  constexpr int NS = kPfStages;
+  const uint32_t k_full = bars, k_empty = bars + NS * 8, v_full = bars + 2 * NS * 8, v_empty = bars + 3 * NS * 8;
+  const uint32_t s_full = bars + 4 * NS * 8, s_empty = s_full + 16;                              // two each
+  const uint32_t p_full = s_full + 32, o_done = s_full + 40, q_full = s_full + 48;
+  const uint32_t tmem_slot = s_full + 56;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 4 * NS * 8 + 56);
 
   T* O = static_cast<T*>(a.o);
   if (ntiles == 0) {   // no key is visible: zeros
@@ -265,20 +326,22 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   }
 
   if (tid == 0) {
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NS; ++i) {
       mbar_init(k_full + i * 8, 1);
       mbar_init(k_empty + i * 8, 1);
       mbar_init(v_full + i * 8, 1);
       mbar_init(v_empty + i * 8, 1);
-      mbar_init(s_full + i * 8, 1);
-      mbar_init(s_empty + i * 8, kPfRows);
     }
-    mbar_init(p_full, kPfRows);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(s_full + i * 8, 1);
+      mbar_init(s_empty + i * 8, 2 * kPfRows);
+    }
+    mbar_init(p_full, 2 * kPfRows);
     mbar_init(o_done, 1);
-    mbar_init(q_full, kPfRows);
+    mbar_init(q_full, 2 * kPfRows);
     fence_mbar_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     tc_alloc(tmem_slot, kPfTmemCols);
     tc_relinquish();
   }
@@ -288,13 +351,13 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   const uint32_t tmem = *tmem_slot_ptr;
   bool dead = false;
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ---------------- producer: K and V tiles by TMA ----------------
     if (lane == 0) {
       const int row0 = p0 * P;                    // the request's first slot of the scratch
       const int xk = kvh * kPdDim, xv = (a.num_kv_heads + kvh) * kPdDim;
       for (int j = 0; j < ntiles; ++j) {
-        const int st = j & 1, use = j >> 1;
+        const int st = j % NS, use = j / NS;
         const int y = row0 + j * kPfKeys;
         if (use > 0) pf_wait(k_empty + st * 8, (use - 1) & 1, a.err, dead);
         if (dead) break;   // nothing new is put in flight once a wait has given up
@@ -308,15 +371,15 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         tma_load_2d(vs0 + st * kPfKvBytes + kPfKeys * 128, &kvmap, xv + 64, y, v_full + st * 8);
       }
     }
-  } else if (warp == 5) {
-    // ---------------- MMA issuer ----------------
+  } else if (warp == 9) {
+    // ---------------- issuer of S = Q . K^T: runs up to two tiles ahead of the softmax ----------------
     if (lane == 0) {
       const uint32_t idesc_s = tc_idesc<T>(kPfKeys, false);
-      const uint32_t idesc_o = tc_idesc<T>(kPdDim, true);
-      auto issue_s = [&](int j) {   // S(j) = Q . K(j)^T into S buffer j & 1
-        const int st = j & 1, use = j >> 1;
-        pf_wait(k_full + st * 8, use & 1, a.err, dead);
-        if (use > 0) pf_wait(s_empty + st * 8, (use - 1) & 1, a.err, dead);
+      pf_wait(q_full, 0, a.err, dead);
+      for (int j = 0; j < ntiles; ++j) {
+        const int st = j % NS, sb = j & 1;
+        pf_wait(k_full + st * 8, (j / NS) & 1, a.err, dead);
+        if (j >= 2) pf_wait(s_empty + sb * 8, ((j >> 1) - 1) & 1, a.err, dead);
         tc_fence_after();
         if (!dead) {
           const uint32_t kst = ks0 + st * kPfKvBytes;
@@ -324,19 +387,25 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
           for (int kk = 0; kk < 8; ++kk) {
             const uint64_t ad = desc_kmajor(qs + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
             const uint64_t bd = desc_kmajor(kst + (kk >> 2) * (kPfKeys * 128) + (kk & 3) * 32);
-            tc_mma(tmem + st * kPfKeys, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
+            tc_mma(tmem + sb * kPfKeys, ad, bd, idesc_s, kk > 0 ? 1u : 0u);
           }
         }
         tc_commit(k_empty + st * 8);
-        tc_commit(s_full + st * 8);
-      };
-      pf_wait(q_full, 0, a.err, dead);
-      issue_s(0);
+        tc_commit(s_full + sb * 8);
+        PF_STAMP(1, j, 0);
+      }
+    }
+  } else if (warp == 10) {
+    // ---------------- issuer of O += P . V (a thread of its own: one thread issuing both products was
+    // the slowest link of the chain) ----------------
+    if (lane == 0) {
+      const uint32_t idesc_o = tc_idesc<T>(kPdDim, true);
       for (int j = 0; j < ntiles; ++j) {
-        if (j + 1 < ntiles) issue_s(j + 1);
-        const int st = j & 1;
-        pf_wait(v_full + st * 8, (j >> 1) & 1, a.err, dead);
+        const int st = j % NS;
+        pf_wait(v_full + st * 8, (j / NS) & 1, a.err, dead);
+        PF_STAMP(1, j, 1);
         pf_wait(p_full, j & 1, a.err, dead);
+        PF_STAMP(1, j, 2);
         tc_fence_after();
         if (!dead) {
           const uint32_t vst = vs0 + st * kPfKvBytes;
@@ -349,22 +418,31 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         }
         tc_commit(v_empty + st * 8);
         tc_commit(o_done);
+        PF_STAMP(1, j, 3);
       }
     }
   } else {
-    // ---------------- softmax warps: thread = row ----------------
-    const int my_qi = qi0 + tid / G;
-    const int my_head = kvh * G + tid % G;
-    const bool my_valid = tid / G < nq;
+    // ---------------- softmax warps: thread = (row, half of the columns) ----------------
+    // Warps w and w + 4 hold the same 32 rows (a warp reaches the tensor-memory lanes 32 (w mod 4) ...):
+    // the first takes columns 0-31 of a tile of S and 0-63 of O, the second the rest.  The two threads of a
+    // row agree on the row's maximum through tensor memory itself: each parks its half's maximum in a
+    // column of the S buffer that it has already read, and reads the other's after a 64-thread barrier.
+    const int half = warp >> 2;
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane;
+    const int my_qi = qi0 + row / G;
+    const int my_head = kvh * G + row % G;
+    const bool my_valid = row / G < nq;
     const int my_pos = my_valid ? pos0 + my_qi : last_pos;   // rows past the end behave like the last one
-    const uint32_t my_tmem = tmem + (static_cast<uint32_t>(warp * 32) << 16);
+    const uint32_t my_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+    const uint32_t o_tmem = my_tmem + 2 * kPfKeys + half * 64;
 
     // the rotated, pre-scaled queries: A operand, K-major.  16 threads per row (4 dims and their partners
-    // each), 8 rows per pass; the position advances by 8 / G per pass, so the angle is stepped, not recomputed
+    // each), 16 rows per pass; the position advances by 16 / G per pass, so the angle is stepped, not recomputed
     {
       const int d0 = (tid & 15) * 4;
       const int rg = tid >> 4;
-      constexpr int STEP = 8 / G;
+      constexpr int STEP = 16 / G;
       const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
       float cc[4], ss[4], c1[4], s1[4];
 #pragma unroll
@@ -374,8 +452,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         sincospif(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
       }
 #pragma unroll 4
-      for (int it = 0; it < kPfRows / 8; ++it) {
-        const int r = rg + 8 * it;
+      for (int it = 0; it < kPfRows / 16; ++it) {
+        const int r = rg + 16 * it;
         const int qi = qi0 + r / G;
         uint32_t wo0 = 0u, wo1 = 0u, wp0 = 0u, wp1 = 0u;
         if (r / G < nq) {
@@ -407,32 +485,44 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
       mbar_arrive(q_full);
     }
 
-    float m_ref = -INFINITY, l_run = 0.f;
+    float m_ref = -INFINITY;
+    uint64_t l2 = pack_f32x2(0.f, 0.f);   // this thread's share of the row sum, two lanes
     for (int j = 0; j < ntiles; ++j) {
-      const int st = j & 1;
-      pf_wait(s_full + st * 8, (j >> 1) & 1, a.err, dead);
+      const int sb = j & 1;
+      if (tid == 0) PF_STAMP(0, j, 0);
+      pf_wait(s_full + sb * 8, (j >> 1) & 1, a.err, dead);
+      if (tid == 0) PF_STAMP(0, j, 1);
       tc_fence_after();
-      uint32_t sv[2][32];
-      tc_ld32(my_tmem + st * kPfKeys, sv[0]);
-      tc_ld32(my_tmem + st * kPfKeys + 32, sv[1]);
+      uint32_t sv[32];
+      tc_ld32(my_tmem + sb * kPfKeys + half * 32, sv);
       tc_wait_ld();
+      if (tid == 0) PF_STAMP(0, j, 2);
+      const int lim = my_pos - j * kPfKeys - half * 32;   // columns above lim are later keys
+      if (lim < 31) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (i > lim) sv[i] = __float_as_uint(-INFINITY);
+      }
+      float mx = max3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
+      float mxb = max3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
+#pragma unroll
+      for (int i = 6; i < 30; i += 4) {
+        mx = max3(mx, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+        mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+      }
+      mx = max3(mx, __uint_as_float(sv[30]), __uint_as_float(sv[31]));
+      mx = fmaxf(mx, mxb);
+      // exchange with the other half's thread: own maximum into the first column of the own half
+      tc_st1(my_tmem + sb * kPfKeys + half * 32, __float_as_uint(mx));
+      tc_wait_st();
       tc_fence_before();
-      mbar_arrive(s_empty + st * 8);   // the S buffer may be overwritten by the tile after next
-      const int lim = my_pos - j * kPfKeys;   // columns above lim are later keys
-      if (lim < kPfKeys - 1) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (h * 32 + i > lim) sv[h][i] = __float_as_uint(-INFINITY);
-      }
-      float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        mx0 = fmaxf(mx0, __uint_as_float(sv[0][i]));
-        mx1 = fmaxf(mx1, __uint_as_float(sv[1][i]));
-      }
-      const float mx = fmaxf(mx0, mx1);
+      pair_barrier(wq);
+      tc_fence_after();
+      const float other = __uint_as_float(tc_ld1(my_tmem + sb * kPfKeys + (half ^ 1) * 32));
+      tc_fence_before();
+      mbar_arrive(s_empty + sb * 8);   // the S buffer may be overwritten by the tile after next
+      if (tid == 0) PF_STAMP(0, j, 3);
+      mx = fmaxf(mx, other);
       float rescale = 1.0f;
       bool raise = false;
       if (mx > m_ref + kPfRaise || m_ref == -INFINITY) {   // (-inf + 8 = -inf: the first visible key always raises)
@@ -442,54 +532,69 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
           m_ref = mx;
         }
       }
-      const float mm = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum0 = 0.f, sum1 = 0.f;
-      uint32_t pw[32];
+      const float nm = m_ref == -INFINITY ? 0.f : -m_ref;
+      const uint64_t nm2 = pack_f32x2(nm, nm);
+      uint64_t sum2 = pack_f32x2(0.f, 0.f);
+      uint32_t pw[16];
 #pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float e0 = exp2f(__uint_as_float(sv[h][i]) - mm), e1 = exp2f(__uint_as_float(sv[h][i + 1]) - mm);
-          sum0 += e0;
-          sum1 += e1;
-          pw[h * 16 + (i >> 1)] = pack2<T>(e0, e1);
-        }
-      l_run = l_run * rescale + (sum0 + sum1);
+      for (int i = 0; i < 32; i += 2) {
+        float x0, x1;
+        unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), nm2), x0, x1);
+        const float e0 = exp2f(x0), e1 = exp2f(x1);
+        sum2 = add_f32x2(sum2, pack_f32x2(e0, e1));
+        pw[i >> 1] = pack2<T>(e0, e1);
+      }
+      l2 = add_f32x2(mul_f32x2(l2, pack_f32x2(rescale, rescale)), sum2);
       // P . V of the previous tile has been read: P and O are free
+      if (tid == 0) PF_STAMP(0, j, 4);
       if (j > 0) {
         pf_wait(o_done, (j - 1) & 1, a.err, dead);
+        if (tid == 0) PF_STAMP(0, j, 5);
         tc_fence_after();
         if (__any_sync(0xffffffffu, raise)) {
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = 0; c < 2; ++c) {
             uint32_t ov[32];
-            tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
+            tc_ld32(o_tmem + c * 32, ov);
             tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * rescale);
-            tc_st32(my_tmem + 2 * kPfKeys + c * 32, ov);
+            tc_st32(o_tmem + c * 32, ov);
           }
           tc_wait_st();
         }
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(ps + tid * 128 + ((c ^ (tid & 7)) << 4)),
+      for (int c = 0; c < 4; ++c)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
+                     ::"r"(ps + row * 128 + (((half * 4 + c) ^ (row & 7)) << 4)),
                      "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
+      if (tid == 0) PF_STAMP(0, j, 6);
       tc_fence_before();
       fence_proxy_async();   // the MMA reads P through the async proxy
       mbar_arrive(p_full);
+      if (tid == 0) PF_STAMP(0, j, 7);
     }
 
-    // ---- the result: O / l ----
+    // ---- the result: O / l; the two halves' sums meet through tensor memory as the maxima did ----
     pf_wait(o_done, (ntiles - 1) & 1, a.err, dead);
     tc_fence_after();
+    float la, lb;
+    unpack_f32x2(l2, la, lb);
+    const float l_mine = la + lb;
+    tc_st1(my_tmem + half * 32, __float_as_uint(l_mine));   // S buffer 0: no product is in flight any more
+    tc_wait_st();
+    tc_fence_before();
+    pair_barrier(wq);
+    tc_fence_after();
+    const float l_other = __uint_as_float(tc_ld1(my_tmem + (half ^ 1) * 32));
+    const float l_run = l_mine + l_other;
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-    T* op = O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim;
+    T* op = O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim + half * 64;
 #pragma unroll 1
-    for (int c = 0; c < 4; ++c) {
+    for (int c = 0; c < 2; ++c) {
       uint32_t ov[32];
-      tc_ld32(my_tmem + 2 * kPfKeys + c * 32, ov);
+      tc_ld32(o_tmem + c * 32, ov);
       tc_wait_ld();
       if (my_valid && !dead) {
 #pragma unroll
@@ -508,7 +613,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  if (warp == 5) tc_dealloc(tmem, kPfTmemCols);
+  if (warp == 9) tc_dealloc(tmem, kPfTmemCols);
 }
 
 }  // namespace smlm
