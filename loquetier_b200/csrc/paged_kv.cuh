@@ -24,7 +24,7 @@
 namespace smlm {
 
 constexpr int kPdDim = 128;          // head dimension served
-constexpr int kPdStages = 3;         // tiles of 16 keys in flight per warp
+constexpr int kPdStages = 2;         // tiles of 16 keys in flight per warp
 constexpr int kPdMaxSplits = 16;
 constexpr int kPdRec = kPdDim + 4;   // floats of a parked softmax state: m, d, two unused, then o[128] (16-byte aligned)
 
@@ -140,7 +140,7 @@ constexpr int kPdSmem = kPdQOff + 8 * kPdDim * 2 + 64;
 // positions of the tile with the angle-addition recurrence, re-seeded exactly at every tile.  The rotated
 // keys are rounded to the storage type - what a cache that stores rotated keys holds anyway.
 template <typename T, int G>
-__global__ void __launch_bounds__(kPdWarps * 32) paged_decode_kernel(const PdArgs a) {
+__global__ void __launch_bounds__(kPdWarps * 32, 3) paged_decode_kernel(const PdArgs a) {
   extern __shared__ __align__(128) unsigned char pd_smem[];
   __shared__ int s_last;
   const int tid = threadIdx.x;

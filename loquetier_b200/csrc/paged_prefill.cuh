@@ -9,7 +9,7 @@
 // prefill_gather_kernel   reads every page of the batch once and writes the keys - rotated for their
 //                         position, rounded to the storage type - and the values into a dense scratch
 //                         [page slot = page * page_size + entry][K of all kv heads | V of all kv heads].  A
-//                         request's slots are consecutive, so a tile of 64 keys of one head is a box of a 2-D
+//                         request's slots are consecutive, so a tile of 64 keys of one head is two boxes of a 2-D
 //                         tensor map: the attention kernel needs no address arithmetic, no page table and
 //                         no rotation in its loop.  Unused entries of a request's last page become zeros.
 //
@@ -47,19 +47,23 @@
 namespace smlm {
 
 constexpr int kPfRows = 128;                      // rows of a query tile
-constexpr int kPfKeys = 64;                       // keys of a tile
+constexpr int kPfKeys = 64;                       // keys of a tile (64: two CTAs per SM; 128: one)
 constexpr int kPfThreads = 352;                  // 8 softmax warps, the producer, two MMA issuers
 constexpr int kPfQBytes = 2 * kPfRows * 128;      // two 64-dim panels of [128 rows][128 B]
-constexpr int kPfKvBytes = 2 * kPfKeys * 128;     // two 64-dim panels of [64 keys][128 B]
+constexpr int kPfKvBytes = 2 * kPfKeys * 128;     // two 64-dim panels of [keys][128 B]
 constexpr int kPfStages = 2;                      // stages of the K ring and of the V ring
 constexpr int kPfKOff = kPfQBytes;
 constexpr int kPfVOff = kPfKOff + kPfStages * kPfKvBytes;
-constexpr int kPfPOff = kPfVOff + kPfStages * kPfKvBytes;   // P: [128 rows][128 B]
-constexpr int kPfBarOff = kPfPOff + kPfRows * 128;
+constexpr int kPfPOff = kPfVOff + kPfStages * kPfKvBytes;   // P: 64-key panels of [128 rows][128 B]
+constexpr int kPfPBytes = kPfRows * kPfKeys * 2;
+constexpr int kPfBarOff = kPfPOff + kPfPBytes;
 constexpr int kPfSmem = kPfBarOff + 4 * kPfStages * 8 + 64;   // the rings' barriers, 7 more, the tensor-memory address
-constexpr int kPfTmemCols = 256;                  // S: 2 x 64 columns, O: 128 columns
+constexpr int kPfTmemCols = kPfKeys == 64 ? 256 : 512;   // S: 2 x keys columns, O: 128 columns (a power of two)
+constexpr int kPfCtasPerSm = kPfKeys == 64 ? 2 : 1;
+constexpr int kPfHalf = kPfKeys / 2;              // columns of S per softmax thread
 constexpr float kPfRaise = 8.0f;                  // a row's maximum is raised when exceeded by this much (log2)
-static_assert(2 * (kPfSmem + 1024) <= 228 * 1024, "two CTAs per SM");
+static_assert(kPfCtasPerSm * (kPfSmem + 1024) <= 228 * 1024, "shared memory budget");
+static_assert(kPfKeys == 64 || kPfKeys == 128, "tile of 64 or 128 keys");
 
 struct PfArgs {
   void* o;                        // [total_q, Nq, 128]
@@ -229,10 +233,10 @@ __global__ void __launch_bounds__(128) prefill_gather_kernel(const PfArgs a) {
 // ---------------------------------------------------------------------------------------------
 
 // grid: (upper bound of query tiles over all requests) * Nkv; a CTA finds its request and tile itself,
-// because the query lengths live on the device.  kvmap: the scratch as [slots][2 * Nkv * 128], boxes of 64
+// because the query lengths live on the device.  kvmap: the scratch as [slots][2 * Nkv * 128], boxes of a tile's
 // slots x 64 columns with the 128-byte swizzle.
 template <typename T, int G>
-__global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfArgs a,
+__global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel(const PfArgs a,
                                                                       const __grid_constant__ CUtensorMap kvmap) {
   extern __shared__ __align__(1024) unsigned char pf_smem[];
   constexpr int PPT = kPfRows / G;   // query positions per tile
@@ -244,15 +248,23 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   const int Nq = a.num_kv_heads * G;
   const int P = a.page_size;
 
+  if (tid == 0) PF_STAMP(0, 63, 0);
   pdl_wait();
   // ---- which (request, query tile) is slot? every warp runs the same scan ----
+  // (each lane also fetches its request's page range, so that everything arrives with one memory latency)
   int b = -1, local = 0, ntq = 0;
+  int qo0 = 0, qo_len = 0, p0 = 0, p1 = 0, last_valid = 0;
   {
     int base = 0;
     for (int b0 = 0; b0 < a.batch && b < 0; b0 += 32) {
       const int bb = b0 + lane;
-      int n = 0;
-      if (bb < a.batch) n = max(0, a.qo_indptr[bb + 1] - a.qo_indptr[bb]);
+      int q0l = 0, q1l = 0, k0l = 0, k1l = 0, lvl = 0;
+      if (bb < a.batch) {
+        q0l = a.qo_indptr[bb]; q1l = a.qo_indptr[bb + 1];
+        k0l = a.kv_indptr[bb]; k1l = a.kv_indptr[bb + 1];
+        lvl = a.last_page_offset[bb];
+      }
+      const int n = max(0, q1l - q0l);
       const int nt = (n + PPT - 1) / PPT;
       int incl = nt;
 #pragma unroll
@@ -266,25 +278,27 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         b = b0 + src;
         ntq = __shfl_sync(0xffffffffu, nt, src);
         local = slot - (base + __shfl_sync(0xffffffffu, incl, src) - ntq);
+        qo0 = __shfl_sync(0xffffffffu, q0l, src);
+        qo_len = __shfl_sync(0xffffffffu, q1l, src) - qo0;
+        p0 = __shfl_sync(0xffffffffu, k0l, src);
+        p1 = __shfl_sync(0xffffffffu, k1l, src);
+        last_valid = __shfl_sync(0xffffffffu, lvl, src);
       }
       base += __shfl_sync(0xffffffffu, incl, 31);
     }
   }
   if (b < 0) return;   // a slot past the last tile (uniform over the CTA)
   const int qt = ntq - 1 - local;   // the tiles with the most keys first
-  const int qo0 = a.qo_indptr[b];
-  const int qo_len = a.qo_indptr[b + 1] - qo0;
   if (qo0 < 0 || qo0 + qo_len > a.total_q) {
     if (tid == 0 && a.err != nullptr) atomicOr(a.err, kErrBadIndptr);
     return;
   }
-  int p0 = a.kv_indptr[b], p1 = a.kv_indptr[b + 1];
   if (p0 < 0 || p1 < p0 || p1 > a.total_pages) {
     if (tid == 0 && a.err != nullptr) atomicOr(a.err, kErrBadIndptr);
     p1 = p0 = 0;
   }
   const int npages = p1 - p0;
-  int last_valid = npages > 0 ? a.last_page_offset[b] : 0;
+  if (npages == 0) last_valid = 0;
   if (last_valid < 0 || last_valid > P) {
     if (tid == 0 && a.err != nullptr) atomicOr(a.err, kErrBadIndptr);
     last_valid = 0;
@@ -325,6 +339,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
     return;
   }
 
+  if (tid == 0) PF_STAMP(0, 63, 1);
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
       mbar_init(k_full + i * 8, 1);
@@ -350,6 +365,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
   tc_fence_after();
   const uint32_t tmem = *tmem_slot_ptr;
   bool dead = false;
+  if (tid == 0) PF_STAMP(0, 63, 2);
 
   if (warp == 8) {
     // ---------------- producer: K and V tiles by TMA ----------------
@@ -410,8 +426,8 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         if (!dead) {
           const uint32_t vst = vs0 + st * kPfKvBytes;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t ad = desc_kmajor(ps + kk * 32);
+          for (int kk = 0; kk < kPfKeys / 16; ++kk) {
+            const uint64_t ad = desc_kmajor(ps + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
             const uint64_t bd = desc_mnmajor(vst + kk * 2048, kPfKeys * 128);
             tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
           }
@@ -451,15 +467,25 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         sincospif(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
         sincospif(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
       }
-#pragma unroll 4
+      // all loads of the thread first (one exposure of the memory latency), then the arithmetic
+      uint2 qo_raw[kPfRows / 16], qp_raw[kPfRows / 16];
+#pragma unroll
       for (int it = 0; it < kPfRows / 16; ++it) {
         const int r = rg + 16 * it;
-        const int qi = qi0 + r / G;
+        qo_raw[it] = qp_raw[it] = make_uint2(0u, 0u);
+        if (r / G < nq) {
+          const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi0 + r / G) * Nq + kvh * G + r % G) * kPdDim;
+          qo_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0));
+          qp_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0 + 64));
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < kPfRows / 16; ++it) {
+        const int r = rg + 16 * it;
         uint32_t wo0 = 0u, wo1 = 0u, wp0 = 0u, wp1 = 0u;
         if (r / G < nq) {
-          const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi) * Nq + kvh * G + r % G) * kPdDim;
-          const uint2 uo = *reinterpret_cast<const uint2*>(qp + d0);
-          const uint2 up = *reinterpret_cast<const uint2*>(qp + d0 + 64);
+          const uint2 uo = qo_raw[it];
+          const uint2 up = qp_raw[it];
           const float2 o0 = unpack2<T>(uo.x), o1 = unpack2<T>(uo.y), q0 = unpack2<T>(up.x), q1 = unpack2<T>(up.y);
           const float own[4] = {o0.x, o0.y, o1.x, o1.y}, par[4] = {q0.x, q0.y, q1.x, q1.y};
           float ro[4], rp[4];
@@ -483,6 +509,7 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
       }
       fence_proxy_async();   // the MMA reads Q through the async proxy
       mbar_arrive(q_full);
+      if (tid == 0) PF_STAMP(0, 63, 3);
     }
 
     float m_ref = -INFINITY;
@@ -493,32 +520,35 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
       pf_wait(s_full + sb * 8, (j >> 1) & 1, a.err, dead);
       if (tid == 0) PF_STAMP(0, j, 1);
       tc_fence_after();
-      uint32_t sv[32];
-      tc_ld32(my_tmem + sb * kPfKeys + half * 32, sv);
+      constexpr int HC = kPfHalf;
+      uint32_t sv[HC];
+#pragma unroll
+      for (int c = 0; c < HC / 32; ++c)
+        tc_ld32(my_tmem + sb * kPfKeys + half * HC + c * 32, *reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]));
       tc_wait_ld();
       if (tid == 0) PF_STAMP(0, j, 2);
-      const int lim = my_pos - j * kPfKeys - half * 32;   // columns above lim are later keys
-      if (lim < 31) {
+      const int lim = my_pos - j * kPfKeys - half * HC;   // columns above lim are later keys
+      if (lim < HC - 1) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
+        for (int i = 0; i < HC; ++i)
           if (i > lim) sv[i] = __float_as_uint(-INFINITY);
       }
       float mx = max3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
       float mxb = max3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
 #pragma unroll
-      for (int i = 6; i < 30; i += 4) {
+      for (int i = 6; i < HC - 2; i += 4) {
         mx = max3(mx, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
         mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
       }
-      mx = max3(mx, __uint_as_float(sv[30]), __uint_as_float(sv[31]));
+      mx = max3(mx, __uint_as_float(sv[HC - 2]), __uint_as_float(sv[HC - 1]));
       mx = fmaxf(mx, mxb);
       // exchange with the other half's thread: own maximum into the first column of the own half
-      tc_st1(my_tmem + sb * kPfKeys + half * 32, __float_as_uint(mx));
+      tc_st1(my_tmem + sb * kPfKeys + half * HC, __float_as_uint(mx));
       tc_wait_st();
       tc_fence_before();
       pair_barrier(wq);
       tc_fence_after();
-      const float other = __uint_as_float(tc_ld1(my_tmem + sb * kPfKeys + (half ^ 1) * 32));
+      const float other = __uint_as_float(tc_ld1(my_tmem + sb * kPfKeys + (half ^ 1) * HC));
       tc_fence_before();
       mbar_arrive(s_empty + sb * 8);   // the S buffer may be overwritten by the tile after next
       if (tid == 0) PF_STAMP(0, j, 3);
@@ -535,9 +565,9 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
       const float nm = m_ref == -INFINITY ? 0.f : -m_ref;
       const uint64_t nm2 = pack_f32x2(nm, nm);
       uint64_t sum2 = pack_f32x2(0.f, 0.f);
-      uint32_t pw[16];
+      uint32_t pw[HC / 2];
 #pragma unroll
-      for (int i = 0; i < 32; i += 2) {
+      for (int i = 0; i < HC; i += 2) {
         float x0, x1;
         unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), nm2), x0, x1);
         const float e0 = exp2f(x0), e1 = exp2f(x1);
@@ -565,10 +595,12 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
         }
       }
 #pragma unroll
-      for (int c = 0; c < 4; ++c)
+      for (int c = 0; c < HC / 8; ++c) {   // 16-byte chunks of this thread's keys; 8 chunks make a panel row
+        const int ch = half * (HC / 8) + c;
         asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
-                     ::"r"(ps + row * 128 + (((half * 4 + c) ^ (row & 7)) << 4)),
+                     ::"r"(ps + (ch >> 3) * (kPfRows * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)),
                      "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
+      }
       if (tid == 0) PF_STAMP(0, j, 6);
       tc_fence_before();
       fence_proxy_async();   // the MMA reads P through the async proxy
@@ -577,43 +609,65 @@ __global__ void __launch_bounds__(kPfThreads, 2) paged_prefill_kernel(const PfAr
     }
 
     // ---- the result: O / l; the two halves' sums meet through tensor memory as the maxima did ----
+    if (tid == 0) PF_STAMP(0, 63, 4);
     pf_wait(o_done, (ntiles - 1) & 1, a.err, dead);
     tc_fence_after();
+    if (tid == 0) PF_STAMP(0, 63, 5);
     float la, lb;
     unpack_f32x2(l2, la, lb);
     const float l_mine = la + lb;
-    tc_st1(my_tmem + half * 32, __float_as_uint(l_mine));   // S buffer 0: no product is in flight any more
+    tc_st1(my_tmem + half * kPfHalf, __float_as_uint(l_mine));   // S buffer 0: no product is in flight any more
     tc_wait_st();
     tc_fence_before();
     pair_barrier(wq);
     tc_fence_after();
-    const float l_other = __uint_as_float(tc_ld1(my_tmem + (half ^ 1) * 32));
+    const float l_other = __uint_as_float(tc_ld1(my_tmem + (half ^ 1) * kPfHalf));
     const float l_run = l_mine + l_other;
     const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
-    T* op = O + (static_cast<size_t>(qo0 + my_qi) * Nq + my_head) * kPdDim + half * 64;
+    // Through shared memory (the Q tile's space: every product that reads it has completed), so that the
+    // stores to global memory are whole 256-byte rows instead of 64 bytes per thread at a row stride.
+    // Staging layout: [128 rows][16 chunks of 16 B], chunk c of row r at slot c ^ (r & 15).
 #pragma unroll 1
     for (int c = 0; c < 2; ++c) {
       uint32_t ov[32];
       tc_ld32(o_tmem + c * 32, ov);
       tc_wait_ld();
-      if (my_valid && !dead) {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t w[4];
+      for (int i = 0; i < 4; ++i) {
+        uint32_t w[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            w[k] = pack2<T>(__uint_as_float(ov[i * 8 + 2 * k]) * inv, __uint_as_float(ov[i * 8 + 2 * k + 1]) * inv);
-          *reinterpret_cast<uint4*>(op + c * 32 + i * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+        for (int k = 0; k < 4; ++k)
+          w[k] = pack2<T>(__uint_as_float(ov[i * 8 + 2 * k]) * inv, __uint_as_float(ov[i * 8 + 2 * k + 1]) * inv);
+        const int ch = half * 8 + c * 4 + i;
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n" ::"r"(qs + row * 256 + ((ch ^ (row & 15)) << 4)),
+                     "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]) : "memory");
+      }
+    }
+    asm volatile("bar.sync 5, 256;\n" ::: "memory");
+    if (!dead) {
+#pragma unroll
+      for (int it = 0; it < kPfRows * 16 / 256; ++it) {
+        const int idx = it * 256 + tid;
+        const int r = idx >> 4, ch = idx & 15;
+        if (r / G < nq) {
+          uint4 v;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                       : "r"(qs + r * 256 + ((ch ^ (r & 15)) << 4)));
+          *reinterpret_cast<uint4*>(O + (static_cast<size_t>(qo0 + qi0 + r / G) * Nq + kvh * G + r % G) * kPdDim + ch * 8) = v;
         }
       }
     }
+    (void)my_head;
+    (void)my_valid;
   }
 
   // everyone is done with tensor memory: hand it back
+  if (tid == 0) PF_STAMP(0, 63, 6);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   if (warp == 9) tc_dealloc(tmem, kPfTmemCols);
+  if (tid == 0) PF_STAMP(0, 63, 7);
 }
 
 }  // namespace smlm

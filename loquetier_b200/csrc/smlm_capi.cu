@@ -622,7 +622,7 @@ int launch_rms_bwd(void* dx, void* dw, const void* go, const void* x, const void
 // sequence lengths live on the device, so the choice depends on the batch shape only.
 inline int decode_splits(int batch, int num_kv_heads) {
   const int ctas = std::max(1, batch * num_kv_heads);
-  return std::max(1, std::min(kPdMaxSplits, (2 * kNumSMs + ctas - 1) / ctas));
+  return std::max(1, std::min(kPdMaxSplits, (3 * kNumSMs + ctas - 1) / ctas));
 }
 
 inline size_t decode_ticket_bytes(int batch, int num_kv_heads) {
