@@ -57,10 +57,11 @@ constexpr int kPfVOff = kPfKOff + kPfStages * kPfKvBytes;
 constexpr int kPfPOff = kPfVOff + kPfStages * kPfKvBytes;   // P: 64-key panels of [128 rows][128 B]
 constexpr int kPfPBytes = kPfRows * kPfKeys * 2;
 constexpr int kPfBarOff = kPfPOff + kPfPBytes;
-constexpr int kPfSmem = kPfBarOff + 4 * kPfStages * 8 + 64;   // the rings' barriers, 7 more, the tensor-memory address
+constexpr int kPfSmem = kPfBarOff + 4 * kPfStages * 8 + 80;   // the rings' barriers, 8 more, the tensor-memory address
 constexpr int kPfTmemCols = kPfKeys == 64 ? 256 : 512;   // S: 2 x keys columns, O: 128 columns (a power of two)
 constexpr int kPfCtasPerSm = kPfKeys == 64 ? 2 : 1;
 constexpr int kPfHalf = kPfKeys / 2;              // columns of S per softmax thread
+constexpr bool kPfPTmem = true;                   // P stays in tensor memory (the upper half of the columns its thread read)
 constexpr float kPfRaise = 8.0f;                  // a row's maximum is raised when exceeded by this much (log2)
 static_assert(kPfCtasPerSm * (kPfSmem + 1024) <= 228 * 1024, "shared memory budget");
 static_assert(kPfKeys == 64 || kPfKeys == 128, "tile of 64 or 128 keys");
@@ -100,6 +101,22 @@ __device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 
+// A operand from tensor memory (lane = row, two 16-bit elements of K per 32-bit column), B from shared memory
+__device__ __forceinline__ void tc_mma_ts(uint32_t tmem_c, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n}\n"
+      ::"r"(tmem_c), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(acc), "r"(0), "r"(0), "r"(0), "r"(0)
+      : "memory");
+}
+__device__ __forceinline__ void tc_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
 // one column of 32 lanes
 __device__ __forceinline__ void tc_st1(uint32_t taddr, uint32_t v) {
   asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};\n" ::"r"(taddr), "r"(v) : "memory");
@@ -325,9 +342,12 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
   constexpr int NS = kPfStages;
   const uint32_t k_full = bars, k_empty = bars + NS * 8, v_full = bars + 2 * NS * 8, v_empty = bars + 3 * NS * 8;
   const uint32_t s_full = bars + 4 * NS * 8, s_empty = s_full + 16;                              // two each
-  const uint32_t p_full = s_full + 32, o_done = s_full + 40, q_full = s_full + 48;
-  const uint32_t tmem_slot = s_full + 56;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 4 * NS * 8 + 56);
+  // o_done: two barriers used by alternate tiles.  A softmax thread consumes the completion of tile j - 1
+  // after it has released tile j; with a single barrier the product of tile j could complete in between and
+  // the parity of tile j - 1 could no longer be told from that of tile j + 1.
+  const uint32_t p_full = s_full + 32, o_done = s_full + 40, q_full = s_full + 56;
+  const uint32_t tmem_slot = s_full + 64;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(pf_smem + kPfBarOff + 4 * NS * 8 + 64);
 
   T* O = static_cast<T*>(a.o);
   if (ntiles == 0) {   // no key is visible: zeros
@@ -349,10 +369,11 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + i * 8, 1);
-      mbar_init(s_empty + i * 8, 2 * kPfRows);
+      mbar_init(s_empty + i * 8, kPfPTmem ? 1 : 2 * kPfRows);   // P in tensor memory: freed by the P . V commit
     }
     mbar_init(p_full, 2 * kPfRows);
     mbar_init(o_done, 1);
+    mbar_init(o_done + 8, 1);
     mbar_init(q_full, 2 * kPfRows);
     fence_mbar_init();
   }
@@ -427,13 +448,21 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
           const uint32_t vst = vs0 + st * kPfKvBytes;
 #pragma unroll
           for (int kk = 0; kk < kPfKeys / 16; ++kk) {
-            const uint64_t ad = desc_kmajor(ps + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
             const uint64_t bd = desc_mnmajor(vst + kk * 2048, kPfKeys * 128);
-            tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            if constexpr (kPfPTmem) {
+              // keys 16 kk .. 16 kk + 15: eight columns in the upper half of the columns of the thread that made them
+              constexpr int PER = kPfHalf / 16;
+              const uint32_t pa = tmem + (j & 1) * kPfKeys + (kk / PER) * kPfHalf + kPfHalf / 2 + (kk % PER) * 8;
+              tc_mma_ts(tmem + 2 * kPfKeys, pa, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            } else {
+              const uint64_t ad = desc_kmajor(ps + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
+              tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+            }
           }
         }
+        if constexpr (kPfPTmem) tc_commit(s_empty + (j & 1) * 8);   // S buffer j & 1 held P: free for the tile after next
         tc_commit(v_empty + st * 8);
-        tc_commit(o_done);
+        tc_commit(o_done + (j & 1) * 8);
         PF_STAMP(1, j, 3);
       }
     }
@@ -550,7 +579,7 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       tc_fence_after();
       const float other = __uint_as_float(tc_ld1(my_tmem + sb * kPfKeys + (half ^ 1) * HC));
       tc_fence_before();
-      mbar_arrive(s_empty + sb * 8);   // the S buffer may be overwritten by the tile after next
+      if constexpr (!kPfPTmem) mbar_arrive(s_empty + sb * 8);   // the S buffer may be overwritten by the tile after next
       if (tid == 0) PF_STAMP(0, j, 3);
       mx = fmaxf(mx, other);
       float rescale = 1.0f;
@@ -575,42 +604,59 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
         pw[i >> 1] = pack2<T>(e0, e1);
       }
       l2 = add_f32x2(mul_f32x2(l2, pack_f32x2(rescale, rescale)), sum2);
-      // P . V of the previous tile has been read: P and O are free
       if (tid == 0) PF_STAMP(0, j, 4);
-      if (j > 0) {
-        pf_wait(o_done, (j - 1) & 1, a.err, dead);
-        if (tid == 0) PF_STAMP(0, j, 5);
-        tc_fence_after();
-        if (__any_sync(0xffffffffu, raise)) {
-#pragma unroll 1
-          for (int c = 0; c < 2; ++c) {
-            uint32_t ov[32];
-            tc_ld32(o_tmem + c * 32, ov);
-            tc_wait_ld();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * rescale);
-            tc_st32(o_tmem + c * 32, ov);
-          }
-          tc_wait_st();
+      bool waited = j == 0;
+      auto wait_prev = [&]() {   // P . V of the previous tile has completed: O is stable (and the P buffer free)
+        if (!waited) {
+          pf_wait(o_done + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, a.err, dead);
+          tc_fence_after();
+          waited = true;
         }
-      }
+      };
+      if constexpr (!kPfPTmem) wait_prev();
+      if (j > 0 && __any_sync(0xffffffffu, raise)) {
+        wait_prev();
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t ov[32];
+          tc_ld32(o_tmem + c * 32, ov);
+          tc_wait_ld();
 #pragma unroll
-      for (int c = 0; c < HC / 8; ++c) {   // 16-byte chunks of this thread's keys; 8 chunks make a panel row
-        const int ch = half * (HC / 8) + c;
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
-                     ::"r"(ps + (ch >> 3) * (kPfRows * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)),
-                     "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
+          for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * rescale);
+          tc_st32(o_tmem + c * 32, ov);
+        }
+        tc_wait_st();
       }
-      if (tid == 0) PF_STAMP(0, j, 6);
-      tc_fence_before();
-      fence_proxy_async();   // the MMA reads P through the async proxy
-      mbar_arrive(p_full);
+      if (tid == 0) PF_STAMP(0, j, 5);
+      if constexpr (kPfPTmem) {
+        // P overwrites the upper half of the S columns this thread has read (the lower half keeps the
+        // exchanged maximum); the other thread of the row has read its own columns before the exchange
+        static_assert(kPfHalf == 32, "the 16-column store below is for tiles of 64 keys");
+        tc_st16(my_tmem + sb * kPfKeys + half * HC + HC / 2, pw);
+        tc_wait_st();
+        if (tid == 0) PF_STAMP(0, j, 6);
+        tc_fence_before();
+        mbar_arrive(p_full);
+        wait_prev();   // every phase of the barrier is consumed, so that its parity stays readable
+      } else {
+#pragma unroll
+        for (int c = 0; c < HC / 8; ++c) {   // 16-byte chunks of this thread's keys; 8 chunks make a panel row
+          const int ch = half * (HC / 8) + c;
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
+                       ::"r"(ps + (ch >> 3) * (kPfRows * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)),
+                       "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
+        }
+        if (tid == 0) PF_STAMP(0, j, 6);
+        tc_fence_before();
+        fence_proxy_async();   // the MMA reads P through the async proxy
+        mbar_arrive(p_full);
+      }
       if (tid == 0) PF_STAMP(0, j, 7);
     }
 
     // ---- the result: O / l; the two halves' sums meet through tensor memory as the maxima did ----
     if (tid == 0) PF_STAMP(0, 63, 4);
-    pf_wait(o_done, (ntiles - 1) & 1, a.err, dead);
+    pf_wait(o_done + ((ntiles - 1) & 1) * 8, ((ntiles - 1) >> 1) & 1, a.err, dead);
     tc_fence_after();
     if (tid == 0) PF_STAMP(0, 63, 5);
     float la, lb;

@@ -2,7 +2,7 @@
 next to this library's on the same seeded inputs, on one GPU.  TEST INFRASTRUCTURE: a measurement aid
 for the baseline tables, not part of the product and not used by ``bench.py``.
 
-    python oracle/time_ref.py > gpurun_out/time_ref.json
+    python oracle/time_ref.py > time_ref.json
 
 Cases: the SMLM forward (shrink then expand, the two operator calls of add_lora.forward) on the
 q_proj-shaped mixed batch (C2), on the q_proj and gate_proj shapes of the Llama-3-8B batch (C3) and on

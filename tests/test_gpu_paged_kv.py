@@ -52,14 +52,14 @@ def test_decode_matches_oracle_large_batch_one_range_per_request():
     from loquetier_b200.cabi import lib
     N, group, P, Lyr = 8, 4, 16, 1
     rng = np.random.default_rng(5)
-    seqlens = [int(v) for v in rng.integers(1, 200, size=48)]
-    assert lib.smlm_b200_batch_decode_workspace_bytes(48, 32, 8) < (1 << 20)
+    seqlens = [int(v) for v in rng.integers(1, 200, size=64)]
+    assert lib.smlm_b200_batch_decode_workspace_bytes(64, 32, 8) < (2 << 20)   # one range: 132 floats per (request, head)
     pages, indptr, last = A.make_cache(21, seqlens, Lyr, N, P, 128, torch.bfloat16)
     g = torch.Generator().manual_seed(22)
-    q = torch.randn((48, N * group, 128), generator=g).to(torch.bfloat16)
+    q = torch.randn((64, N * group, 128), generator=g).to(torch.bfloat16)
     pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
     o = _decode(q.to(DEV), ptrs, ind, lst, Lyr, 0, N, P)
-    assert_close(o, A.batch_decode(q, pages, indptr, last, 0, THETA), what="48 requests")
+    assert_close(o, A.batch_decode(q, pages, indptr, last, 0, THETA), what="64 requests")
 
 
 def test_decode_long_sequence_rotation_stays_accurate():
