@@ -88,17 +88,38 @@ __global__ void __launch_bounds__(128) append_kv_kernel(const AppendArgs a) {
   const T* K = static_cast<const T*>(a.k);
   const T* V = static_cast<const T*>(a.v);
   const size_t kv_delta = static_cast<size_t>(a.num_kv_heads) * P * kPdDim;
-  for (int j = blockIdx.y * 8 + row; j < n; j += gridDim.y * 8) {
-    const int pos = start + j;
-    T* page = static_cast<T*>(const_cast<void*>(a.kv_ptrs[p0 + pos / P]));
-    if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) {
-      if (tx == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
-      continue;
+  // four tokens per thread and step: their page addresses and source rows are fetched together, so that a
+  // step costs one round of memory latency instead of four
+  constexpr int U = 4;
+  const int stride = gridDim.y * 8;
+  for (int j0 = blockIdx.y * 8 + row; j0 < n; j0 += U * stride) {
+    T* kd[U];
+    uint4 kk[U], vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * stride;
+      kd[u] = nullptr;
+      kk[u] = vv[u] = make_uint4(0u, 0u, 0u, 0u);
+      if (j < n) {
+        const int pos = start + j;
+        T* page = static_cast<T*>(const_cast<void*>(a.kv_ptrs[p0 + pos / P]));
+        if (page == nullptr || (reinterpret_cast<uintptr_t>(page) & 15) != 0) {
+          if (tx == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
+        } else {
+          kd[u] = page + ((static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + h) * P + pos % P) * kPdDim + tx * 8;
+        }
+        const size_t so = (static_cast<size_t>(src0 + j) * a.num_kv_heads + h) * kPdDim + tx * 8;
+        kk[u] = __ldg(reinterpret_cast<const uint4*>(K + so));
+        vv[u] = __ldg(reinterpret_cast<const uint4*>(V + so));
+      }
     }
-    T* kd = page + ((static_cast<size_t>(a.layer_idx) * 2 * a.num_kv_heads + h) * P + pos % P) * kPdDim + tx * 8;
-    const size_t so = (static_cast<size_t>(src0 + j) * a.num_kv_heads + h) * kPdDim + tx * 8;
-    *reinterpret_cast<uint4*>(kd) = *reinterpret_cast<const uint4*>(K + so);
-    *reinterpret_cast<uint4*>(kd + kv_delta) = *reinterpret_cast<const uint4*>(V + so);
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (kd[u] != nullptr) {
+        *reinterpret_cast<uint4*>(kd[u]) = kk[u];
+        *reinterpret_cast<uint4*>(kd[u] + kv_delta) = vv[u];
+      }
+    }
   }
 }
 

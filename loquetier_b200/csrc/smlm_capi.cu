@@ -687,8 +687,8 @@ int run_append(const void* const* kv_ptrs, const int32_t* kv_indptr, const int32
   const int rows = batch * num_kv_heads;
   int chunks = 1;
   if (append_indptr != nullptr) {
-    const int per = std::max(1, (max_tokens + 7) / 8);
-    chunks = std::max(1, std::min(per, (4 * kNumSMs + rows - 1) / rows));
+    const int per = std::max(1, (max_tokens + 31) / 32);   // a CTA moves 8 rows x 4 tokens per step
+    chunks = std::max(1, std::min(per, (16 * kNumSMs + rows - 1) / rows));
   }
   const dim3 grid(rows, chunks, 1);
   return dtype == SMLM_F16 ? launch(append_kv_kernel<__half>, grid, 128, 1, 0, stream, a)
