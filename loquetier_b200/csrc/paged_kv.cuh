@@ -311,28 +311,31 @@ __global__ void __launch_bounds__(kPdWarps * 32, 3) paged_decode_kernel(const Pd
     const int key0 = (tile0 + warp + j * kPdWarps) * kPdTile;
     const uint32_t kst = ring + (j % kPdStages) * (2 * kPdTileBytes);
     const uint32_t vst = kst + kPdTileBytes;
-    // rotate the 16 keys in place
+    // rotate the 16 keys in place (both frequencies of the lane at once: packed fp32 pairs)
     {
       float cc[2], ss[2];
 #pragma unroll
       for (int i = 0; i < 2; ++i) sincospif(static_cast<float>(key0) * fr[i], &ss[i], &cc[i]);
+      uint64_t c2 = pack_f32x2(cc[0], cc[1]), s2 = pack_f32x2(ss[0], ss[1]);
+      const uint64_t c1p = pack_f32x2(c1[0], c1[1]), s1p = pack_f32x2(s1[0], s1[1]);
+      const uint64_t ns1p = pack_f32x2(-s1[0], -s1[1]);
 #pragma unroll
       for (int e = 0; e < kPdTile; ++e) {
         const uint32_t ao = kst + e * 256 + ((((lane >> 2) ^ (e & 7))) << 4) + (lane & 3) * 4;
         uint32_t wo, wp;
         asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wo) : "r"(ao));
         asm volatile("ld.shared.b32 %0, [%1];\n" : "=r"(wp) : "r"(ao + 128));
-        const float2 ko = unpack2<T>(wo), kp = unpack2<T>(wp);
-        const uint32_t no = pack2<T>(ko.x * cc[0] - kp.x * ss[0], ko.y * cc[1] - kp.y * ss[1]);
-        const uint32_t np = pack2<T>(kp.x * cc[0] + ko.x * ss[0], kp.y * cc[1] + ko.y * ss[1]);
-        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao), "r"(no) : "memory");
-        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao + 128), "r"(np) : "memory");
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const float cn = cc[i] * c1[i] - ss[i] * s1[i];
-          ss[i] = ss[i] * c1[i] + cc[i] * s1[i];
-          cc[i] = cn;
-        }
+        const float2 kof = unpack2<T>(wo), kpf = unpack2<T>(wp);
+        const uint64_t ko = pack_f32x2(kof.x, kof.y), kp = pack_f32x2(kpf.x, kpf.y);
+        const uint64_t ns2 = s2 ^ 0x8000000080000000ull;   // -s2: both sign bits flipped
+        float a0, a1, b0, b1;
+        unpack_f32x2(fma_f32x2(kp, ns2, mul_f32x2(ko, c2)), a0, a1);   // ko * c - kp * s
+        unpack_f32x2(fma_f32x2(ko, s2, mul_f32x2(kp, c2)), b0, b1);    // kp * c + ko * s
+        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao), "r"(pack2<T>(a0, a1)) : "memory");
+        asm volatile("st.shared.b32 [%0], %1;\n" ::"r"(ao + 128), "r"(pack2<T>(b0, b1)) : "memory");
+        const uint64_t cn = fma_f32x2(s2, ns1p, mul_f32x2(c2, c1p));   // c c1 - s s1
+        s2 = fma_f32x2(c2, s1p, mul_f32x2(s2, c1p));                   // s c1 + c s1
+        c2 = cn;
       }
     }
     __syncwarp();

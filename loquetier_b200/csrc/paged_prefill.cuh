@@ -127,31 +127,6 @@ __device__ __forceinline__ uint32_t tc_ld1(uint32_t taddr) {   // load and wait 
                "tcgen05.wait::ld.sync.aligned;\n" : "=r"(v) : "r"(taddr) : "memory");
   return v;
 }
-// packed pairs of fp32 (one instruction for two lanes on sm_100) and the three-input maximum
-__device__ __forceinline__ uint64_t pack_f32x2(float a, float b) {
-  uint64_t r;
-  asm("mov.b64 %0, {%1, %2};\n" : "=l"(r) : "f"(a), "f"(b));
-  return r;
-}
-__device__ __forceinline__ void unpack_f32x2(uint64_t v, float& a, float& b) {
-  asm("mov.b64 {%0, %1}, %2;\n" : "=f"(a), "=f"(b) : "l"(v));
-}
-__device__ __forceinline__ uint64_t add_f32x2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("add.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ uint64_t mul_f32x2(uint64_t a, uint64_t b) {
-  uint64_t r;
-  asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(r) : "l"(a), "l"(b));
-  return r;
-}
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;\n" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
 // 64-thread barrier of the two warps that hold the same rows.  The barrier number is an immediate: with a
 // register operand the compiler reserves all 16 hardware barriers for the CTA, and only one CTA fits an SM.
 __device__ __forceinline__ void pair_barrier(int wq) {
