@@ -315,7 +315,7 @@ __global__ void __launch_bounds__(kPdWarps * 32, 3) paged_decode_kernel(const Pd
     {
       float cc[2], ss[2];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) sincospif(static_cast<float>(key0) * fr[i], &ss[i], &cc[i]);
+      for (int i = 0; i < 2; ++i) fast_sincospi(static_cast<float>(key0) * fr[i], &ss[i], &cc[i]);
       uint64_t c2 = pack_f32x2(cc[0], cc[1]), s2 = pack_f32x2(ss[0], ss[1]);
       const uint64_t c1p = pack_f32x2(c1[0], c1[1]), s1p = pack_f32x2(s1[0], s1[1]);
       const uint64_t ns1p = pack_f32x2(-s1[0], -s1[1]);

@@ -468,8 +468,8 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
-        sincospif(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
-        sincospif(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
+        fast_sincospi(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
+        fast_sincospi(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
       }
       // all loads of the thread first (one exposure of the memory latency), then the arithmetic
       uint2 qo_raw[kPfRows / 16], qp_raw[kPfRows / 16];

@@ -242,6 +242,16 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
   return r;
 }
 
+// sin and cos of pi * x on the special-function unit: x (half-turns) is reduced to [-1, 1] exactly, then the
+// hardware approximations are good to about 1e-6 absolute - far below the rounding of 16-bit operands.  The
+// library routine sincospif costs an order of magnitude more instructions; it stays where a value is computed
+// once per kernel.
+__device__ __forceinline__ void fast_sincospi(float x, float* s, float* c) {
+  const float r = x - 2.0f * rintf(0.5f * x);
+  *s = __sinf(3.14159265358979f * r);
+  *c = __cosf(3.14159265358979f * r);
+}
+
 // ---------------------------------------------------------------------------
 // mbarrier + TMA (bulk asynchronous copies).  Every CTA fetches its own tiles; no
 // copy is shared between CTAs.
