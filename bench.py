@@ -1080,7 +1080,7 @@ def run_prefill(a, rank, world, local, torch, dist, blocks, steps):
                              frac=flops / (ms * 1e-3) / 1e12 / peak, peak_source=which, traffic=None,
                              algorithmic_flops=flops,
                              note="causal flops only (visible keys); the step also holds the init_kv copy"),
-               launch_mode="eager" if a.no_graph else "cuda graph replay", gpu_launches_per_step=2)
+               launch_mode="eager" if a.no_graph else "cuda graph replay", gpu_launches_per_step=3)
     if a.check and rank == 0:
         from oracle import attention_oracle as AO
         sel = [int(i) for i in np.argsort(seqlens)[[0, B // 2]]]   # the shortest and the median prompt

@@ -47,24 +47,28 @@
 namespace smlm {
 
 constexpr int kPfRows = 128;                      // rows of a query tile
-constexpr int kPfKeys = 64;                       // keys of a tile (64: two CTAs per SM; 128: one)
-constexpr int kPfThreads = 352;                  // 8 softmax warps, the producer, two MMA issuers
+// Keys per tile.  64: two S buffers (the next tile's product runs under this tile's softmax) and two-stage
+// rings, two CTAs per SM.  128 (one S buffer of 128 columns, one-stage rings, still two CTAs per SM) halves the
+// tcgen05.mma instructions per key, but the next S then has to wait for P . V of this tile, which reads P out
+// of the same columns: measured slower (0.98 ms against 0.84 ms on the benchmark step).
+constexpr int kPfKeys = 64;
+constexpr int kPfSBufs = kPfKeys == 64 ? 2 : 1;   // S buffers in tensor memory
+constexpr int kPfStages = kPfKeys == 64 ? 2 : 1;  // stages of the K ring and of the V ring
+constexpr int kPfThreads = 352;                   // 8 softmax warps, the producer, two MMA issuers
 constexpr int kPfQBytes = 2 * kPfRows * 128;      // two 64-dim panels of [128 rows][128 B]
 constexpr int kPfKvBytes = 2 * kPfKeys * 128;     // two 64-dim panels of [keys][128 B]
-constexpr int kPfStages = 2;                      // stages of the K ring and of the V ring
 constexpr int kPfKOff = kPfQBytes;
 constexpr int kPfVOff = kPfKOff + kPfStages * kPfKvBytes;
-constexpr int kPfPOff = kPfVOff + kPfStages * kPfKvBytes;   // P: 64-key panels of [128 rows][128 B]
-constexpr int kPfPBytes = kPfRows * kPfKeys * 2;
-constexpr int kPfBarOff = kPfPOff + kPfPBytes;
+constexpr int kPfBarOff = kPfVOff + kPfStages * kPfKvBytes;
 constexpr int kPfSmem = kPfBarOff + 4 * kPfStages * 8 + 80;   // the rings' barriers, 8 more, the tensor-memory address
-constexpr int kPfTmemCols = kPfKeys == 64 ? 256 : 512;   // S: 2 x keys columns, O: 128 columns (a power of two)
-constexpr int kPfCtasPerSm = kPfKeys == 64 ? 2 : 1;
+constexpr int kPfOCol = kPfSBufs * kPfKeys;       // first column of O
+constexpr int kPfTmemCols = 256;                  // S buffers + O (128 columns)
+constexpr int kPfCtasPerSm = 2;
 constexpr int kPfHalf = kPfKeys / 2;              // columns of S per softmax thread
-constexpr bool kPfPTmem = true;                   // P stays in tensor memory (the upper half of the columns its thread read)
 constexpr float kPfRaise = 8.0f;                  // a row's maximum is raised when exceeded by this much (log2)
-static_assert(kPfCtasPerSm * (kPfSmem + 1024) <= 228 * 1024, "shared memory budget");
 static_assert(kPfKeys == 64 || kPfKeys == 128, "tile of 64 or 128 keys");
+static_assert(kPfOCol + 128 <= kPfTmemCols, "tensor memory budget");
+static_assert(kPfCtasPerSm * (kPfSmem + 1024) <= 228 * 1024, "shared memory budget");
 
 struct PfArgs {
   void* o;                        // [total_q, Nq, 128]
@@ -312,7 +316,6 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
   const uint32_t qs = sbase;
   const uint32_t ks0 = sbase + kPfKOff;
   const uint32_t vs0 = sbase + kPfVOff;
-  const uint32_t ps = sbase + kPfPOff;
   const uint32_t bars = sbase + kPfBarOff;
   constexpr int NS = kPfStages;
   const uint32_t k_full = bars, k_empty = bars + NS * 8, v_full = bars + 2 * NS * 8, v_empty = bars + 3 * NS * 8;
@@ -344,7 +347,7 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full + i * 8, 1);
-      mbar_init(s_empty + i * 8, kPfPTmem ? 1 : 2 * kPfRows);   // P in tensor memory: freed by the P . V commit
+      mbar_init(s_empty + i * 8, 1);   // P lives in the S buffer: freed by the commit of P . V
     }
     mbar_init(p_full, 2 * kPfRows);
     mbar_init(o_done, 1);
@@ -389,9 +392,9 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       const uint32_t idesc_s = tc_idesc<T>(kPfKeys, false);
       pf_wait(q_full, 0, a.err, dead);
       for (int j = 0; j < ntiles; ++j) {
-        const int st = j % NS, sb = j & 1;
+        const int st = j % NS, sb = j % kPfSBufs, use = j / kPfSBufs;
         pf_wait(k_full + st * 8, (j / NS) & 1, a.err, dead);
-        if (j >= 2) pf_wait(s_empty + sb * 8, ((j >> 1) - 1) & 1, a.err, dead);
+        if (use > 0) pf_wait(s_empty + sb * 8, (use - 1) & 1, a.err, dead);
         tc_fence_after();
         if (!dead) {
           const uint32_t kst = ks0 + st * kPfKvBytes;
@@ -424,18 +427,13 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
 #pragma unroll
           for (int kk = 0; kk < kPfKeys / 16; ++kk) {
             const uint64_t bd = desc_mnmajor(vst + kk * 2048, kPfKeys * 128);
-            if constexpr (kPfPTmem) {
-              // keys 16 kk .. 16 kk + 15: eight columns in the upper half of the columns of the thread that made them
-              constexpr int PER = kPfHalf / 16;
-              const uint32_t pa = tmem + (j & 1) * kPfKeys + (kk / PER) * kPfHalf + kPfHalf / 2 + (kk % PER) * 8;
-              tc_mma_ts(tmem + 2 * kPfKeys, pa, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-            } else {
-              const uint64_t ad = desc_kmajor(ps + (kk >> 2) * (kPfRows * 128) + (kk & 3) * 32);
-              tc_mma(tmem + 2 * kPfKeys, ad, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
-            }
+            // keys 16 kk .. 16 kk + 15: eight columns in the upper half of the columns of the thread that made them
+            constexpr int PER = kPfHalf / 16;
+            const uint32_t pa = tmem + (j % kPfSBufs) * kPfKeys + (kk / PER) * kPfHalf + kPfHalf / 2 + (kk % PER) * 8;
+            tc_mma_ts(tmem + kPfOCol, pa, bd, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
           }
         }
-        if constexpr (kPfPTmem) tc_commit(s_empty + (j & 1) * 8);   // S buffer j & 1 held P: free for the tile after next
+        tc_commit(s_empty + (j % kPfSBufs) * 8);   // the S buffer held P: free for the next product into it
         tc_commit(v_empty + st * 8);
         tc_commit(o_done + (j & 1) * 8);
         PF_STAMP(1, j, 3);
@@ -455,7 +453,7 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     const bool my_valid = row / G < nq;
     const int my_pos = my_valid ? pos0 + my_qi : last_pos;   // rows past the end behave like the last one
     const uint32_t my_tmem = tmem + (static_cast<uint32_t>(wq * 32) << 16);
-    const uint32_t o_tmem = my_tmem + 2 * kPfKeys + half * 64;
+    const uint32_t o_tmem = my_tmem + kPfOCol + half * 64;
 
     // the rotated, pre-scaled queries: A operand, K-major.  16 threads per row (4 dims and their partners
     // each), 16 rows per pass; the position advances by 16 / G per pass, so the angle is stepped, not recomputed
@@ -519,42 +517,49 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     float m_ref = -INFINITY;
     uint64_t l2 = pack_f32x2(0.f, 0.f);   // this thread's share of the row sum, two lanes
     for (int j = 0; j < ntiles; ++j) {
-      const int sb = j & 1;
+      const int sb = j % kPfSBufs;
       if (tid == 0) PF_STAMP(0, j, 0);
-      pf_wait(s_full + sb * 8, (j >> 1) & 1, a.err, dead);
+      pf_wait(s_full + sb * 8, (j / kPfSBufs) & 1, a.err, dead);
       if (tid == 0) PF_STAMP(0, j, 1);
       tc_fence_after();
       constexpr int HC = kPfHalf;
-      uint32_t sv[HC];
-#pragma unroll
-      for (int c = 0; c < HC / 32; ++c)
-        tc_ld32(my_tmem + sb * kPfKeys + half * HC + c * 32, *reinterpret_cast<uint32_t (*)[32]>(&sv[c * 32]));
-      tc_wait_ld();
-      if (tid == 0) PF_STAMP(0, j, 2);
+      constexpr int NCH = HC / 32;           // the thread's columns are handled 32 at a time
+      const uint32_t my_s = my_tmem + sb * kPfKeys + half * HC;
       const int lim = my_pos - j * kPfKeys - half * HC;   // columns above lim are later keys
-      if (lim < HC - 1) {
+      uint32_t sv[32];
+      auto load_chunk = [&](int c) {
+        tc_ld32(my_s + c * 32, sv);
+        tc_wait_ld();
+        if (lim - c * 32 < 31) {
 #pragma unroll
-        for (int i = 0; i < HC; ++i)
-          if (i > lim) sv[i] = __float_as_uint(-INFINITY);
-      }
-      float mx = max3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
-      float mxb = max3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
+          for (int i = 0; i < 32; ++i)
+            if (i > lim - c * 32) sv[i] = __float_as_uint(-INFINITY);
+        }
+      };
+      // pass 1: the maximum of the thread's columns
+      float mx = -INFINITY;
+      uint32_t first_col = 0u;               // column 0 is about to carry the exchanged maximum
 #pragma unroll
-      for (int i = 6; i < HC - 2; i += 4) {
-        mx = max3(mx, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
-        mxb = max3(mxb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+      for (int c = 0; c < NCH; ++c) {
+        load_chunk(c);
+        if (c == 0) first_col = sv[0];
+        float ma = max3(__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]));
+        float mb = max3(__uint_as_float(sv[3]), __uint_as_float(sv[4]), __uint_as_float(sv[5]));
+#pragma unroll
+        for (int i = 6; i < 30; i += 4) {
+          ma = max3(ma, __uint_as_float(sv[i]), __uint_as_float(sv[i + 1]));
+          mb = max3(mb, __uint_as_float(sv[i + 2]), __uint_as_float(sv[i + 3]));
+        }
+        mx = max3(mx, max3(ma, __uint_as_float(sv[30]), __uint_as_float(sv[31])), mb);
       }
-      mx = max3(mx, __uint_as_float(sv[HC - 2]), __uint_as_float(sv[HC - 1]));
-      mx = fmaxf(mx, mxb);
+      if (tid == 0) PF_STAMP(0, j, 2);
       // exchange with the other half's thread: own maximum into the first column of the own half
-      tc_st1(my_tmem + sb * kPfKeys + half * HC, __float_as_uint(mx));
+      tc_st1(my_s, __float_as_uint(mx));
       tc_wait_st();
       tc_fence_before();
       pair_barrier(wq);
       tc_fence_after();
       const float other = __uint_as_float(tc_ld1(my_tmem + sb * kPfKeys + (half ^ 1) * HC));
-      tc_fence_before();
-      if constexpr (!kPfPTmem) mbar_arrive(s_empty + sb * 8);   // the S buffer may be overwritten by the tile after next
       if (tid == 0) PF_STAMP(0, j, 3);
       mx = fmaxf(mx, other);
       float rescale = 1.0f;
@@ -569,26 +574,38 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       const float nm = m_ref == -INFINITY ? 0.f : -m_ref;
       const uint64_t nm2 = pack_f32x2(nm, nm);
       uint64_t sum2 = pack_f32x2(0.f, 0.f);
+      // pass 2: P.  With two chunks the columns are read again (the registers would not hold 64 scores and 32
+      // words of P with two CTAs on the SM), the upper chunk first: P will overwrite it.
       uint32_t pw[HC / 2];
 #pragma unroll
-      for (int i = 0; i < HC; i += 2) {
-        float x0, x1;
-        unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), nm2), x0, x1);
-        const float e0 = exp2f(x0), e1 = exp2f(x1);
-        sum2 = add_f32x2(sum2, pack_f32x2(e0, e1));
-        pw[i >> 1] = pack2<T>(e0, e1);
+      for (int cc = NCH - 1; cc >= 0; --cc) {
+        if (NCH > 1) {
+          load_chunk(cc);
+          if (cc == 0) sv[0] = first_col;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float x0, x1;
+          unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), nm2), x0, x1);
+#ifdef SMLM_PF_NOEXP   // development experiment: how much of the tile time is the exponential?
+          const float e0 = fmaf(x0, 0.001f, 1.0f), e1 = fmaf(x1, 0.001f, 1.0f);
+#else
+          const float e0 = exp2f(x0), e1 = exp2f(x1);
+#endif
+          sum2 = add_f32x2(sum2, pack_f32x2(e0, e1));
+          pw[cc * 16 + (i >> 1)] = pack2<T>(e0, e1);
+        }
       }
       l2 = add_f32x2(mul_f32x2(l2, pack_f32x2(rescale, rescale)), sum2);
       if (tid == 0) PF_STAMP(0, j, 4);
       bool waited = j == 0;
-      auto wait_prev = [&]() {   // P . V of the previous tile has completed: O is stable (and the P buffer free)
+      auto wait_prev = [&]() {   // P . V of the previous tile has completed: O is stable
         if (!waited) {
           pf_wait(o_done + ((j - 1) & 1) * 8, ((j - 1) >> 1) & 1, a.err, dead);
           tc_fence_after();
           waited = true;
         }
       };
-      if constexpr (!kPfPTmem) wait_prev();
       if (j > 0 && __any_sync(0xffffffffu, raise)) {
         wait_prev();
 #pragma unroll 1
@@ -603,29 +620,15 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
         tc_wait_st();
       }
       if (tid == 0) PF_STAMP(0, j, 5);
-      if constexpr (kPfPTmem) {
-        // P overwrites the upper half of the S columns this thread has read (the lower half keeps the
-        // exchanged maximum); the other thread of the row has read its own columns before the exchange
-        static_assert(kPfHalf == 32, "the 16-column store below is for tiles of 64 keys");
-        tc_st16(my_tmem + sb * kPfKeys + half * HC + HC / 2, pw);
-        tc_wait_st();
-        if (tid == 0) PF_STAMP(0, j, 6);
-        tc_fence_before();
-        mbar_arrive(p_full);
-        wait_prev();   // every phase of the barrier is consumed, so that its parity stays readable
-      } else {
-#pragma unroll
-        for (int c = 0; c < HC / 8; ++c) {   // 16-byte chunks of this thread's keys; 8 chunks make a panel row
-          const int ch = half * (HC / 8) + c;
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};\n"
-                       ::"r"(ps + (ch >> 3) * (kPfRows * 128) + row * 128 + (((ch & 7) ^ (row & 7)) << 4)),
-                       "r"(pw[4 * c]), "r"(pw[4 * c + 1]), "r"(pw[4 * c + 2]), "r"(pw[4 * c + 3]) : "memory");
-        }
-        if (tid == 0) PF_STAMP(0, j, 6);
-        tc_fence_before();
-        fence_proxy_async();   // the MMA reads P through the async proxy
-        mbar_arrive(p_full);
-      }
+      // P overwrites the upper half of the S columns this thread has read (the lower half keeps the exchanged
+      // maximum); the other thread of the row has read its own columns before the exchange
+      if constexpr (HC == 32) tc_st16(my_s + HC / 2, pw);
+      else tc_st32(my_s + HC / 2, *reinterpret_cast<uint32_t (*)[32]>(&pw[0]));
+      tc_wait_st();
+      if (tid == 0) PF_STAMP(0, j, 6);
+      tc_fence_before();
+      mbar_arrive(p_full);
+      wait_prev();   // every phase of the barrier is consumed, so that its parity stays readable
       if (tid == 0) PF_STAMP(0, j, 7);
     }
 
