@@ -214,12 +214,17 @@ class Workload:
         # grouped where it changes anything: decode tokens are gathered by adapter for the forward launches
         from loquetier_b200.segments import wants_grouped_plan
         lens, ids = self.spec["lens"], self.spec["ids"]
-        if self.sched in ("split", "split2") and self.iseg is not None:
+        if self.sched in ("split", "split2", "split3") and self.iseg is not None:
             # the train rows go through the partition plan, the other rows get a plan of their own
             g = self.grouped and wants_grouped_plan(lens[self.npart:], ids[self.npart:])
+            self.plan = None
+            if self.sched == "split3" and self.tl:
+                self.iplan, self.pplan = self.ops.plan_pair(self.iseg, self.T, self.part, self.tl,
+                                                            seg_ids_a=self.iids if g else None,
+                                                            n_table_a=self.spec["n_adapters"])
+                return
             self.iplan = self.ops.Plan(self.iseg, self.T, seg_ids=self.iids if g else None,
                                        n_table=self.spec["n_adapters"])
-            self.plan = None
         else:
             g = self.grouped and wants_grouped_plan(lens, ids)
             self.iplan = None
@@ -241,9 +246,11 @@ class Workload:
     def launches_per_step(self):
         """Kernels of this library launched per step: the plans, then per class one launch (multi / split)
         or one per projection (single)."""
-        nplan = 1 + (1 if self.tl and (self.sched in ("single", "split", "split2") or self.pset is None) else 0)
+        nplan = 1 + (1 if self.tl and (self.sched in ("single", "split", "split2", "split3") or self.pset is None) else 0)
         if self.sched == "single" or self.pset is None:
             return nplan + len(self.proj) * (1 + (2 if self.tl else 0))
+        if self.sched == "split3" and self.iseg is not None and self.tl:
+            return 1 + 4
         if self.sched in ("split", "split2") and self.iseg is not None and self.tl:
             return nplan + 4
         return nplan + 1 + (2 if self.tl else 0)
@@ -254,6 +261,19 @@ class Workload:
         ops, r, torch = self.ops, self.spec["rank"], self.torch
         self.build_plans()
         n_ad = self.spec["n_adapters"]
+        if self.sched == "split3" and self.iseg is not None and self.tl:
+            # One stream.  The weight gradients need v and dV of the train rows only, so the forward is cut in
+            # two: the train rows' forward runs next to dV/dX, the weight gradients follow, and the forward of
+            # the other rows - most of the step - is launched last as an independent launch: it touches nothing
+            # the weight gradients touch, so its CTAs run next to theirs (pure reads next to reads and writes).
+            ops.bwd_dx_multi(self.pset, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale)
+            ops.fwd_multi(self.pset, self.pplan, r, seg_ids=self.part_ids, seg_scale=self.scale,
+                          independent=self.overlap)
+            ops.wgrad_pair_multi(self.pset, self.part, self.pplan, r, part_ids=self.part_ids,
+                                 part_scale=self.scale, n_table=n_ad, accumulate=self.accumulate_grads)
+            ops.fwd_multi(self.pset, self.iplan, r, seg_ids=self.iids, seg_scale=self.scale,
+                          independent=self.overlap)
+            return
         if self.sched in ("split", "split2") and self.iseg is not None and self.tl:
             # The weight gradients need v and dV of the train rows only, so the forward is cut in two: the
             # train rows (through the partition plan) and the other rows (a plan of their own).
@@ -1150,7 +1170,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear", "decode", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps; the median is reported")
-    ap.add_argument("--sched", default="multi", choices=["multi", "multi_f", "split", "split2", "single"],
+    ap.add_argument("--sched", default="multi", choices=["multi", "multi_f", "split", "split2", "split3", "single"],
                     help="multi: one launch per kernel class over all projections (dV/dX, forward, weight "
                          "gradients); multi_f: the same with the forward first; split: the forward of the inference "
                          "rows on a second stream; single: one launch per projection")
