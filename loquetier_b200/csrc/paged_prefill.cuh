@@ -587,11 +587,7 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
         for (int i = 0; i < 32; i += 2) {
           float x0, x1;
           unpack_f32x2(add_f32x2(pack_f32x2(__uint_as_float(sv[i]), __uint_as_float(sv[i + 1])), nm2), x0, x1);
-#ifdef SMLM_PF_NOEXP   // development experiment: how much of the tile time is the exponential?
-          const float e0 = fmaf(x0, 0.001f, 1.0f), e1 = fmaf(x1, 0.001f, 1.0f);
-#else
           const float e0 = exp2f(x0), e1 = exp2f(x1);
-#endif
           sum2 = add_f32x2(sum2, pack_f32x2(e0, e1));
           pw[cc * 16 + (i >> 1)] = pack2<T>(e0, e1);
         }
