@@ -652,7 +652,8 @@ int dispatch_prefill(const PfArgs& a, const CUtensorMap& kvmap, int group, cudaS
   if (rc != SMLM_OK) return rc;
   // query tiles: sum over requests of ceil(len / positions per tile) <= total_q / positions per tile + batch
   const int ppt = kPfRows / group;
-  const dim3 grid((a.total_q / ppt + a.batch) * a.num_kv_heads, 1, 1);
+  const int slots = (a.total_q / ppt + a.batch) * a.num_kv_heads;
+  const dim3 grid(slots, 1, 1);
   switch (group) {
     case 1: return launch(paged_prefill_kernel<T, 1>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);
     case 2: return launch(paged_prefill_kernel<T, 2>, grid, kPfThreads, 1, kPfSmem, stream, a, kvmap);

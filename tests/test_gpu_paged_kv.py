@@ -344,3 +344,4 @@ def test_prefill_against_reference_kernel(dtype, group):
     want = A.batch_prefill(q, qind, pages, indptr, last, layer, THETA)
     assert_close(o_ref, want, what="reference kernel vs oracle")
     assert_close(o_lib, o_ref, what="library vs reference kernel")
+
