@@ -253,7 +253,7 @@ class Workload:
             return 1 + 4
         if self.sched in ("split", "split2") and self.iseg is not None and self.tl:
             return nplan + 4
-        return nplan + 1 + (2 if self.tl else 0)
+        return nplan + 1 + ((3 if self.sched == "multi_s" else 2) if self.tl else 0)
 
     def step(self):
         if self.sched == "single" or self.pset is None:
@@ -316,6 +316,16 @@ class Workload:
         # two is marked independent and starts while the first drains; the weight gradients consume v
         # and dV and come last.  "multi": dV/dX first; "multi_f": the forward first, so that the weight
         # gradients follow dV/dX directly (the gO rows it read last are still in L2).
+        if self.sched == "multi_s" and self.tl:
+            # dA = dV^T . X needs nothing of the forward: it follows dV/dX directly, the forward runs next to it
+            # as an independent launch (reads next to reads and writes), and only dB = gO^T . V is left for the end
+            ops.bwd_dx_multi(self.pset, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale)
+            ops.wgrad_pair_multi(self.pset, self.part, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale,
+                                 n_table=n_ad, accumulate=self.accumulate_grads, which=ops.WGRAD_DA)
+            ops.fwd_multi(self.pset, self.plan, r, seg_ids=self.ids, seg_scale=self.scale, independent=self.overlap)
+            ops.wgrad_pair_multi(self.pset, self.part, self.pplan, r, part_ids=self.part_ids, part_scale=self.scale,
+                                 n_table=n_ad, accumulate=self.accumulate_grads, which=ops.WGRAD_DB)
+            return
         if self.sched == "multi_f":
             ops.fwd_multi(self.pset, self.plan, r, seg_ids=self.ids, seg_scale=self.scale)
             if self.tl:
@@ -1170,7 +1180,7 @@ def main():
     ap.add_argument("--workload", default="c3", choices=["c2", "c3", "c4", "c4s", "c5", "rmsnorm", "linear", "decode", "prefill"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--blocks", type=int, default=25, help="timed blocks of --steps steps; the median is reported")
-    ap.add_argument("--sched", default="multi", choices=["multi", "multi_f", "split", "split2", "split3", "single"],
+    ap.add_argument("--sched", default="multi", choices=["multi", "multi_s", "multi_f", "split", "split2", "split3", "single"],
                     help="multi: one launch per kernel class over all projections (dV/dX, forward, weight "
                          "gradients); multi_f: the same with the forward first; split: the forward of the inference "
                          "rows on a second stream; single: one launch per projection")

@@ -291,6 +291,17 @@ int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int
                                size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
                                int is_row_major, int accumulate, int grad_fp32, int independent, void* stream);
 
+/* The same launch for one kind of gradient only: `which` = SMLM_WGRAD_DB (dB = gO^T . V: reads v, go), SMLM_WGRAD_DA
+ * (dA = dV^T . X: reads dv, x) or both.  dA needs nothing of the forward, so a step can launch it right behind
+ * smlm_b200_bwd_dx_multi, let the forward run next to it as an independent launch, and keep only dB for the end.
+ * Two such launches may share a workspace when they do not overlap in time. */
+#define SMLM_WGRAD_DB 1
+#define SMLM_WGRAD_DA 2
+int smlm_b200_wgrad_select_multi(const smlm_b200_proj* projs, int nproj, int which, const int32_t* part_indptr,
+                                 const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
+                                 size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
+                                 int is_row_major, int accumulate, int grad_fp32, int independent, void* stream);
+
 /* ---- RMSNorm: the caller on either side of the q/k/v and gate/up projections ----------------- */
 
 /* Replaces dispatch_rms_norm / rms_norm<T> (kernel_src/csrc/loquetier_ops.cc:326-358,

@@ -62,6 +62,8 @@ SIGNATURES = {
     "smlm_b200_wgrad_multi_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad_pair_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_size_t] + [c_int] * 9 + [c_void_p]),
+    "smlm_b200_wgrad_select_multi": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_size_t] + [c_int] * 9 + [c_void_p]),
     "smlm_b200_batch_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "smlm_b200_batch_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "smlm_b200_batch_prefill": (c_int, [c_void_p] * 7 + [c_size_t, c_void_p] + [c_int] * 9 + [c_float, c_int, c_void_p]),

@@ -1044,30 +1044,45 @@ size_t smlm_b200_wgrad_multi_workspace_bytes(const smlm_b200_proj* projs, int np
   return wgrad_workspace_need(T, npart, rank, hs, 2 * nproj);
 }
 
-int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_indptr,
-                               const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
-                               size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
-                               int is_row_major, int accumulate, int grad_fp32, int independent, void* stream) {
-  if (T < 0 || npart < 0 || n_table < 0 || !projs_ok(projs, nproj)) return SMLM_ERR_INVALID_ARGUMENT;
+int smlm_b200_wgrad_select_multi(const smlm_b200_proj* projs, int nproj, int which, const int32_t* part_indptr,
+                                 const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
+                                 size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
+                                 int is_row_major, int accumulate, int grad_fp32, int independent, void* stream) {
+  if (T < 0 || npart < 0 || n_table < 0 || !projs_ok(projs, nproj) || (which & 3) == 0 || (which & ~3) != 0)
+    return SMLM_ERR_INVALID_ARGUMENT;
   if (dtype != SMLM_F16 && dtype != SMLM_BF16) return SMLM_ERR_DTYPE;
   if (npart == 0 || T == 0) return SMLM_OK;
   if (part_indptr == nullptr || plan == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
   if (!aligned16(plan)) return SMLM_ERR_MISALIGNED;
   if (!small_dim_ok(rank)) return SMLM_ERR_NO_KERNEL;
   WgradJobDesc jobs[2 * SMLM_MAX_PROJ];
+  int nj = 0;
   for (int j = 0; j < nproj; ++j) {
     const smlm_b200_proj& p = projs[j];
-    if (p.dA_table == nullptr || p.dB_table == nullptr || p.dv == nullptr || p.x == nullptr || p.v == nullptr ||
-        p.go == nullptr)
-      return SMLM_ERR_INVALID_ARGUMENT;
-    if (!aligned16(p.dv) || !aligned16(p.x) || !aligned16(p.v) || !aligned16(p.go)) return SMLM_ERR_MISALIGNED;
     if (!large_dim_ok(p.h_in) || !large_dim_ok(p.h_out)) return SMLM_ERR_NO_KERNEL;
-    jobs[2 * j] = {p.dB_table, p.v, p.go, p.h_out, is_row_major ? 0 : 1, part_scale != nullptr};
-    jobs[2 * j + 1] = {p.dA_table, p.dv, p.x, p.h_in, is_row_major ? 1 : 0, 0};
+    if (which & SMLM_WGRAD_DB) {
+      if (p.dB_table == nullptr || p.v == nullptr || p.go == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+      if (!aligned16(p.v) || !aligned16(p.go)) return SMLM_ERR_MISALIGNED;
+      jobs[nj++] = {p.dB_table, p.v, p.go, p.h_out, is_row_major ? 0 : 1, part_scale != nullptr};
+    }
+    if (which & SMLM_WGRAD_DA) {
+      if (p.dA_table == nullptr || p.dv == nullptr || p.x == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+      if (!aligned16(p.dv) || !aligned16(p.x)) return SMLM_ERR_MISALIGNED;
+      jobs[nj++] = {p.dA_table, p.dv, p.x, p.h_in, is_row_major ? 1 : 0, 0};
+    }
   }
-  return run_wgrad(jobs, 2 * nproj, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes,
-                   npart, T, rank, dtype, accumulate, grad_fp32, independent != 0, wgrad_uses_tensor_cores(rank),
+  return run_wgrad(jobs, nj, part_indptr, part_scale, part_ids, n_table, plan, workspace, workspace_bytes, npart, T,
+                   rank, dtype, accumulate, grad_fp32, independent != 0, wgrad_uses_tensor_cores(rank),
                    static_cast<cudaStream_t>(stream));
+}
+
+int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_indptr,
+                               const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
+                               size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
+                               int is_row_major, int accumulate, int grad_fp32, int independent, void* stream) {
+  return smlm_b200_wgrad_select_multi(projs, nproj, SMLM_WGRAD_DB | SMLM_WGRAD_DA, part_indptr, part_ids, part_scale,
+                                      plan, workspace, workspace_bytes, n_table, npart, T, rank, dtype, is_row_major,
+                                      accumulate, grad_fp32, independent, stream);
 }
 
 // ---- paged key-value cache ------------------------------------------------------------------

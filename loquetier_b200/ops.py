@@ -283,18 +283,22 @@ def wgrad_multi_workspace(ps: ProjSet, T: int, npart: int, rank: int, slot: str 
     return ws
 
 
+WGRAD_DB, WGRAD_DA = 1, 2
+
+
 def wgrad_pair_multi(ps: ProjSet, part_indptr, plan: Plan, rank: int, is_row_major=False, part_ids=None,
                      part_scale=None, n_table=0, accumulate=False, grad_fp32=False, workspace=None,
-                     independent=False):
-    """``wgrad_pair`` for every projection of the set in one launch."""
+                     independent=False, which=WGRAD_DB | WGRAD_DA):
+    """``wgrad_pair`` for every projection of the set in one launch; ``which`` restricts it to dB (reads v, go)
+    or dA (reads dv, x)."""
     ws = workspace if workspace is not None else wgrad_multi_workspace(ps, plan.T, plan.nseg, rank)
     with torch.cuda.device(ps.ref.device):
-        check(lib.smlm_b200_wgrad_pair_multi(ps.ptr, ps.n, part_indptr.data_ptr(), _p(part_ids), _p(part_scale),
-                                             plan.buf.data_ptr(), ws.data_ptr(), ws.numel(), int(n_table),
-                                             int(part_indptr.numel()) - 1, plan.T, int(rank), ps._dt("go"),
-                                             int(bool(is_row_major)), int(bool(accumulate)), int(bool(grad_fp32)),
-                                             int(bool(independent)), _stream(ps.ref)),
-              "smlm_b200_wgrad_pair_multi")
+        check(lib.smlm_b200_wgrad_select_multi(ps.ptr, ps.n, int(which), part_indptr.data_ptr(), _p(part_ids),
+                                               _p(part_scale), plan.buf.data_ptr(), ws.data_ptr(), ws.numel(),
+                                               int(n_table), int(part_indptr.numel()) - 1, plan.T, int(rank),
+                                               ps._dt("go"), int(bool(is_row_major)), int(bool(accumulate)),
+                                               int(bool(grad_fp32)), int(bool(independent)), _stream(ps.ref)),
+              "smlm_b200_wgrad_select_multi")
 
 
 # ---------------------------------------------------------------------------

@@ -27,7 +27,7 @@ def _poison_outputs(wl):
             p["dB"].fill_(float("nan"))
 
 
-@pytest.mark.parametrize("sched", ["multi", "multi_f", "split", "split3", "single"])
+@pytest.mark.parametrize("sched", ["multi", "multi_s", "multi_f", "split", "split3", "single"])
 def test_c3_timed_step_every_projection_matches_oracle(sched):
     spec = bench.workload_spec("c3")
     parts = [l for l, f in zip(spec["lens"], spec["ft"]) if f]
