@@ -1187,7 +1187,7 @@ def main():
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison of every output of the timed step with the CPU oracle (rank 0)")
     ap.add_argument("--no-extras", action="store_true", help="c3 only: skip the c5 and rmsnorm records")
-    ap.add_argument("--chunks", type=int, default=2, help="c5: slot ranges of the last projection's exchange")
+    ap.add_argument("--chunks", type=int, default=1, help="c5: slot ranges of the last projection's exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-e2e", action="store_true")
