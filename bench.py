@@ -875,6 +875,10 @@ class DataParallelStep:
             self.ranges.append((s0, s1, (parts[0], parts[-1] + 1) if parts else None))
         self.exchange = True
         self.sub = {}
+        # "fused": per projection forward, dV/dX (one fused launch), weight gradients.  "grads_first": the
+        # input gradients are cut in two - dV = scale gO . B right away, dX = dV . A at the very end - so that
+        # the weight gradients of BOTH projections are out early and their exchange runs under the dX launches
+        self.order = "fused"
 
     def _sub(self, p0, p1):
         """Index pointer, ids, tables and plan of partitions [p0, p1) for a partial weight-gradient launch."""
@@ -886,7 +890,31 @@ class DataParallelStep:
         d["plan"] = ops.Plan(d["part"], wl.tl)
         return d
 
+    def step_grads_first(self):
+        wl, ops, b = self.wl, self.wl.ops, self.bucket
+        r, n_ad = wl.spec["rank"], wl.spec["n_adapters"]
+        b.zero_except(self.local_ids)
+        wl.sched = "single"
+        wl.build_plans()
+        for i, p in enumerate(wl.proj):
+            ops.fwd(p["y"], p["x"], p["v"], p["wa"], p["wb"], wl.plan, r, seg_ids=wl.ids, seg_scale=wl.scale,
+                    independent=i > 0)
+            # dV = scale * gO . B alone (B is [h_out, r]: the row-major operand of this product)
+            ops.gemm(p["dv"], p["go"], p["wb"], wl.pplan, is_row_major=True, seg_ids=wl.part_ids, seg_scale=wl.scale)
+        for i, p in enumerate(wl.proj):
+            ops.wgrad_pair(p["dA_t"], p["dB_t"], p["dv"], p["x"], p["v"], p["go"], wl.part, wl.pplan, r,
+                           part_ids=wl.part_ids, part_scale=wl.scale, n_table=n_ad,
+                           workspace=ops.wgrad_workspace(wl.dev, wl.tl, wl.npart, r, p["h_out"], p["h_in"], slot=i))
+            if self.exchange:
+                b.reduce_slots(i, 0, b.n_slots)
+        for p in wl.proj:
+            # dX = dV . A last: the largest writes of the backward run while the gradients travel
+            ops.gemm(p["dx"], p["dv"], p["wa"], wl.pplan, is_row_major=True, seg_ids=wl.part_ids)
+        b.finish()
+
     def step(self):
+        if self.order == "grads_first":
+            return self.step_grads_first()
         wl, ops, b = self.wl, self.wl.ops, self.bucket
         r, n_ad = wl.spec["rank"], wl.spec["n_adapters"]
         b.zero_except(self.local_ids)
@@ -949,6 +977,7 @@ def run_c5(a, rank, world, local, torch, dist, blocks, steps):
     wl = Workload(spec, torch.device("cuda", local))
     # one rank alone exchanges nothing: its weight gradients stay one launch per projection
     dp = DataParallelStep(wl, torch, dist if world > 1 else None, chunks=a.chunks if world > 1 else 1)
+    dp.order = a.c5_order
     T = wl.T
     dp.step()
     torch.cuda.synchronize()
@@ -956,7 +985,7 @@ def run_c5(a, rank, world, local, torch, dist, blocks, steps):
         pl.raise_if_failed()
     rec = dict(workload="c5: " + WORKLOAD_TEXT["c5"], tokens_per_gpu=T, n_gpus=world,
                allreduce_bytes_per_step=dp.bucket.nbytes if world > 1 else 0, slots=dp.bucket.n_slots,
-               chunks_of_last_projection=len(dp.ranges))
+               chunks_of_last_projection=len(dp.ranges), order=dp.order)
     mode = "eager"
     fn = dp.step
     if not a.no_graph:
@@ -979,13 +1008,14 @@ def run_c5(a, rank, world, local, torch, dist, blocks, steps):
         rec["parity_max_rel_err"], rec["parity_share_outside_literal_tolerance"] = check_step(wl, torch)
         rec["parity_checked"] = True
     if world > 1:
-        # the same step without the exchange: the compute one GPU needs alone (per-GPU work is fixed)
-        dp.exchange = False
+        # the step one GPU needs alone for the same work: no exchange, the fused order (per-GPU work is fixed)
+        order = dp.order
+        dp.exchange, dp.order = False, "fused"
         fn0 = dp.step
         if mode != "eager":
             fn0 = capture(dp.step, torch)
         ms0, _ = timed(fn0, steps, 3, torch, dist, None, max(1, blocks // 2))
-        dp.exchange = True
+        dp.exchange, dp.order = True, order
         rec.update(ms_per_step_without_exchange=ms0, exposed_comm_ms=ms - ms0, efficiency_vs_n1=ms0 / ms)
     return rec
 
@@ -1187,6 +1217,10 @@ def main():
     ap.add_argument("--no-check", dest="check", action="store_false",
                     help="skip the comparison of every output of the timed step with the CPU oracle (rank 0)")
     ap.add_argument("--no-extras", action="store_true", help="c3 only: skip the c5 and rmsnorm records")
+    ap.add_argument("--c5-order", default="fused", choices=["fused", "grads_first"],
+                    help="c5: fused = dV/dX in one launch per projection; grads_first = dV early, dX last, so that the "
+                         "exchange of all weight gradients runs under the dX launches (the half products run on the "
+                         "mma.sync kernel, which is slow at rank 64: 3.24 ms against 1.68 ms per step on one GPU)")
     ap.add_argument("--chunks", type=int, default=1, help="c5: slot ranges of the last projection's exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

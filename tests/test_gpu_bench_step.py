@@ -101,13 +101,15 @@ def test_c3_host_pipeline_matches_oracle():
     assert all(v < 1e-2 for v in worst.values()), worst
 
 
-def test_c5_data_parallel_step_one_rank_matches_oracle():
+@pytest.mark.parametrize("order", ["fused", "grads_first"])
+def test_c5_data_parallel_step_one_rank_matches_oracle(order):
     """Workload c5 as bench.py runs it (tcgen05 kernels, gradients written into bucket slots, the last
     projection's weight gradients in slot ranges) at full size: 16 partitions of 2048 rows, rank 64, both
-    directions 4096 <-> 14336."""
+    directions 4096 <-> 14336.  Both orders of a step: dV/dX fused, or dV early and dX last."""
     spec = bench.workload_spec("c5")
     wl = bench.Workload(spec, DEV)
     dp = bench.DataParallelStep(wl, torch, None, chunks=4)
+    dp.order = order
     assert len(dp.ranges) == 4 and dp.bucket.n_slots == 16
     dp.step()
     torch.cuda.synchronize()
