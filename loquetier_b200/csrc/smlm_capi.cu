@@ -228,7 +228,8 @@ int dispatch_tc(const TcArgs& a, const TcMaps& tm, int max_tall, cudaStream_t st
 // The 128-row MMA tile pays off when segments are long enough to fill it and the batch has
 // enough of them for every SM; short ragged segments stay on the 64-row mma.sync kernel.
 inline bool use_tensor_core_kernel(int T, int nseg, int R, int mode) {
-  if (mode != kFusedBoth || R <= 32) return false;
+  (void)mode;   // the tcgen05 kernel serves both products and either half alone
+  if (R <= 32) return false;
   const int m = g_tensor_core_mode.load(std::memory_order_relaxed);
   if (m < 0) return false;
   if (m > 0) return true;
@@ -260,8 +261,13 @@ int run_fused(const FusedJobDesc* jobs, int njobs, const int32_t* ids, const flo
       t.plan = static_cast<int*>(plan);
       t.n_table = n_table; t.K1 = d.K1; t.R = R; t.N2 = d.N2; t.scale_mid = scale_mid; t.accumulate = d.accumulate;
       t.independent = (independent || j > 0) ? 1 : 0;
+      t.mode = mode;
       TcMaps m;
-      if (!make_map_2d(&m.in16, d.in, T, d.K1, 16, dtype) || !make_map_2d(&m.out16, d.out, T, d.N2, 16, dtype))
+      // one half alone has only one of the two large tensors: the other map is never used, any valid one will do
+      const void* in_t = mode == kFusedExpandOnly ? d.out : d.in;
+      const void* out_t = mode == kFusedShrinkOnly ? d.in : d.out;
+      const int in_cols = mode == kFusedExpandOnly ? d.N2 : d.K1, out_cols = mode == kFusedShrinkOnly ? d.K1 : d.N2;
+      if (!make_map_2d(&m.in16, in_t, T, in_cols, 16, dtype) || !make_map_2d(&m.out16, out_t, T, out_cols, 16, dtype))
         return SMLM_ERR_CUDA;
       int rc;
       if (dtype == SMLM_F16)

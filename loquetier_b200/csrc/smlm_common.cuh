@@ -242,6 +242,11 @@ __device__ __forceinline__ uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c
   return r;
 }
 
+// what a fused launch computes: both products, or one half alone (one reference operator call)
+constexpr int kFusedBoth = 0;
+constexpr int kFusedShrinkOnly = 1;
+constexpr int kFusedExpandOnly = 2;
+
 // sin and cos of pi * x on the special-function unit: x (half-turns) is reduced to [-1, 1] exactly, then the
 // hardware approximations are good to about 1e-6 absolute - far below the rounding of 16-bit operands.  The
 // library routine sincospif costs an order of magnitude more instructions; it stays where a value is computed

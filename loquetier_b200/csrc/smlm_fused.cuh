@@ -154,9 +154,6 @@ struct FusedMapsN {
   FusedMaps m[kFusedMaxJobs];
 };
 
-constexpr int kFusedBoth = 0;
-constexpr int kFusedShrinkOnly = 1;
-constexpr int kFusedExpandOnly = 2;
 
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(nthreads) : "memory");

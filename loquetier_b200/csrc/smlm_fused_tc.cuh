@@ -82,6 +82,7 @@ struct TcArgs {
   int scale_mid;
   int accumulate;
   int independent;
+  int mode;                     // kFusedBoth, kFusedShrinkOnly (MID = IN . W1 only) or kFusedExpandOnly (MID is read)
 };
 
 struct TcMaps {
@@ -176,9 +177,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
   const int nrows = pc.nrows;
   const int K1 = a.K1, R = a.R, N2 = a.N2;
   int* err = a.plan + 1;
-  const T* w1 = static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
-  const T* w2 = static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
-  const bool w_ok = (w1 != nullptr) && (w2 != nullptr);
+  const T* w1 = a.mode == kFusedExpandOnly ? nullptr
+                                            : static_cast<const T*>(adapter_ptr(a.w1_table, a.ids, a.n_table, pc.seg, err));
+  const T* w2 = a.mode == kFusedShrinkOnly ? nullptr
+                                            : static_cast<const T*>(adapter_ptr(a.w2_table, a.ids, a.n_table, pc.seg, err));
+  const bool w_ok = (a.mode == kFusedExpandOnly || w1 != nullptr) && (a.mode == kFusedShrinkOnly || w2 != nullptr);
   const float sc = adapter_scale(a.scale, a.ids, a.n_table, pc.seg);
   const float sc_mid = a.scale_mid ? sc : 1.0f;
   const float sc_out = a.scale_mid ? 1.0f : sc;
@@ -221,8 +224,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
   const uint32_t acc1 = tmem;               // columns [0, KP)
   const uint32_t acc2 = tmem + KP;          // two buffers of kTcNG columns
 
-  const int ksteps = w_ok ? (K1 + KC - 1) / KC : 0;
-  const int ngroups = w_ok ? (N2 + kTcNG - 1) / kTcNG : 0;
+  // one half alone: the other half's loops run zero times (its barriers complete at once or are never waited for)
+  const int ksteps = (w_ok && a.mode != kFusedExpandOnly) ? (K1 + KC - 1) / KC : 0;
+  const int ngroups = (w_ok && a.mode != kFusedShrinkOnly) ? (N2 + kTcNG - 1) / kTcNG : 0;
   const int nblk = (nrows + 15) >> 4;
   bool dead = false;
 
@@ -375,25 +379,34 @@ __global__ void __launch_bounds__(kTcThreads, 1) fused_tc_kernel(const TcArgs a,
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint32_t v[32];
-          tc_ld32(acc1 + lane_base + blk * 64 + h * 32, v);
-          tc_wait_ld();
+          if (a.mode != kFusedExpandOnly) {
+            tc_ld32(acc1 + lane_base + blk * 64 + h * 32, v);
+            tc_wait_ld();
+          }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {     // four 16-byte chunks of 8 elements
             uint32_t p[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const int col = blk * 64 + h * 32 + q * 8 + e * 2;
-              const float f0 = (w_ok && !dead && col < R) ? __uint_as_float(v[q * 8 + e * 2]) * sc_mid : 0.f;
-              const float f1 = (w_ok && !dead && col + 1 < R) ? __uint_as_float(v[q * 8 + e * 2 + 1]) * sc_mid : 0.f;
-              p[e] = pack2<T>(f0, f1);
-            }
             const int c = h * 4 + q;
+            if (a.mode == kFusedExpandOnly) {
+              // the expand alone: MID comes from global memory (rows past the piece and columns past R are zeros)
+              uint4 m = make_uint4(0u, 0u, 0u, 0u);
+              if (row < nrows && blk * 64 + c * 8 < R && w_ok) m = *reinterpret_cast<const uint4*>(mrow + blk * 64 + c * 8);
+              p[0] = m.x; p[1] = m.y; p[2] = m.z; p[3] = m.w;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const int col = blk * 64 + h * 32 + q * 8 + e * 2;
+                const float f0 = (w_ok && !dead && col < R) ? __uint_as_float(v[q * 8 + e * 2]) * sc_mid : 0.f;
+                const float f1 = (w_ok && !dead && col + 1 < R) ? __uint_as_float(v[q * 8 + e * 2 + 1]) * sc_mid : 0.f;
+                p[e] = pack2<T>(f0, f1);
+              }
+            }
             asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(mids + blk * (kTcRows * 128) + row * 128 +
                                                                          ((c ^ (row & 7)) << 4)),
                          "r"(p[0]), "r"(p[1]), "r"(p[2]), "r"(p[3])
                          : "memory");
             const int col0 = blk * 64 + c * 8;
-            if (row < nrows && col0 < R && w_ok && !dead)
+            if (a.mode != kFusedExpandOnly && row < nrows && col0 < R && w_ok && !dead)
               *reinterpret_cast<uint4*>(mrow + col0) = make_uint4(p[0], p[1], p[2], p[3]);
           }
         }
