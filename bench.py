@@ -1219,8 +1219,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="c3 only: skip the c5 and rmsnorm records")
     ap.add_argument("--c5-order", default="fused", choices=["fused", "grads_first"],
                     help="c5: fused = dV/dX in one launch per projection; grads_first = dV early, dX last, so that the "
-                         "exchange of all weight gradients runs under the dX launches (the half products run on the "
-                         "mma.sync kernel, which is slow at rank 64: 3.24 ms against 1.68 ms per step on one GPU)")
+                         "exchange of all weight gradients runs under the dX launches (measured: no faster at two GPUs)")
     ap.add_argument("--chunks", type=int, default=1, help="c5: slot ranges of the last projection's exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
