@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(kPdWarps * 32, 3) paged_decode_kernel(const Pd
       mma16816<T>(o[jn], pa, bf[0], bf[1]);
       mma16816<T>(o[jn + 1], pa, bf[2], bf[3]);
     }
-    __syncwarp();   // the stage is free for the copy issued two iterations from now
+    __syncwarp();   // the stage is free for the copy issued in the next iteration
   }
   cp_async_wait<0>();
   if (__any_sync(0xffffffffu, bad_ptr) && lane == 0 && a.err != nullptr) atomicOr(a.err, kErrBadPointer);
