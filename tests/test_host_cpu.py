@@ -52,6 +52,47 @@ def test_argument_validation_needs_no_gpu():
         cabi.check(3, "x")
 
 
+def test_attention_entry_points_validate_before_any_cuda_call():
+    """The paged-cache entry points reject bad arguments before any CUDA call (no GPU needed)."""
+    from loquetier_b200 import cabi
+    L = cabi.lib
+    # workspace sizes follow the batch shape
+    assert L.smlm_b200_batch_prefill_workspace_bytes(10, 16, 8) == 10 * 16 * 2 * 8 * 128 * 2
+    assert L.smlm_b200_batch_prefill_workspace_bytes(0, 16, 8) == 0
+    assert L.smlm_b200_batch_decode_workspace_bytes(0, 32, 8) == 0
+    ws = L.smlm_b200_batch_prefill_workspace_bytes(4, 16, 8)
+
+    def pre(o=256, wsp=1 << 20, ws_bytes=ws, pages=4, nq=32, hd=128, layer=0, P=16, theta=10000.0, dt=1):
+        return L.smlm_b200_batch_prefill(o, 256, 256, 256, 256, 256, wsp, ws_bytes, None, 2, 64, pages, nq, 8, hd, 1,
+                                         layer, P, theta, dt, None)
+
+    assert pre(dt=5) == 2                      # dtype
+    assert pre(hd=64) == 3                     # head dim outside the path: "No suitable kernel."
+    assert pre(P=12) == 3                      # page size
+    assert pre(nq=24) == 3                     # 24 query heads on 8 kv heads: a group of 3
+    assert pre(layer=1) == 1                   # layer index past the layers
+    assert pre(theta=0.0) == 1
+    assert pre(o=264) == 4                     # o not 16-byte aligned
+    assert pre(wsp=None) == 5 and pre(ws_bytes=ws - 1) == 5   # workspace missing / too small
+    assert pre(wsp=(1 << 20) + 16) == 4        # workspace not 128-byte aligned
+    assert pre(pages=0) == 1                   # queries without a single page of keys
+
+    def dec(nq=32, hd=128, P=16, dt=1):
+        return L.smlm_b200_batch_decode(256, 256, 256, 256, 256, None, 0, None, 2, 4, nq, 8, hd, 1, 0, P, 10000.0, dt,
+                                        None)
+
+    assert dec(dt=7) == 2 and dec(hd=96) == 3 and dec(P=128) == 3 and dec(nq=40) == 3
+    assert dec() == 5                          # 2 requests x 8 heads are cut into page ranges: a workspace is needed
+
+    def app(k=256, hd=128, dt=0):
+        return L.smlm_b200_append_kv(256, 256, 256, k, 256, None, 2, 4, 1, 0, 8, hd, 16, dt, None)
+
+    assert app(dt=9) == 2 and app(hd=256) == 3 and app(k=264) == 4
+    # the weight gradients of one kind: `which` must name dB, dA or both
+    assert L.smlm_b200_wgrad_select_multi(None, 0, 0, None, None, None, None, None, 0, 0, 0, 0, 16, 1, 0, 0, 0, 0,
+                                          None) == 1
+
+
 def test_batch_len_info_matches_reference():
     from loquetier_b200.kernel_utils import BatchLenInfo
     for row in load_bookkeeping()["batch_len_info"]:
