@@ -345,3 +345,20 @@ def test_prefill_against_reference_kernel(dtype, group):
     assert_close(o_ref, want, what="reference kernel vs oracle")
     assert_close(o_lib, o_ref, what="library vs reference kernel")
 
+
+
+def test_prefill_many_short_requests():
+    """More requests than one pass of the kernels' request scan covers (32 per pass), some of them empty."""
+    N, group, P, Lyr = 2, 4, 16, 1
+    rng = np.random.default_rng(77)
+    seqlens = [int(v) for v in rng.integers(0, 41, size=70)]
+    seqlens[33] = 0
+    qlens = list(seqlens)
+    pages, indptr, last = A.make_cache(401, seqlens, Lyr, N, P, 128, torch.bfloat16)
+    g = torch.Generator().manual_seed(402)
+    qind = _qind(qlens)
+    q = torch.randn((qind[-1], N * group, 128), generator=g).to(torch.bfloat16)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, 0, N, P)
+    want = A.batch_prefill(q, qind, pages, indptr, last, 0, THETA)
+    assert_close(o, want, what="70 short requests")
