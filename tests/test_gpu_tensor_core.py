@@ -230,3 +230,49 @@ def test_c5_full_size_both_kernels_and_oracle_slices():
     dA_ref = dvs.T @ x[a:b].float()
     close(dB[s], dB_ref, "dB vs fp32")
     close(dA[s], dA_ref, "dA vs fp32")
+
+
+# ---- either product alone (one reference operator call each) on the tcgen05 kernel ----
+
+def _check_halves(case, scale=None, accumulate=False, y_init=None):
+    """v = x . W1 by one shrink-only call, y (+)= scale * v . W2 by one expand-only call, against the oracle's
+    two-call forward (v rounded to the storage type in between)."""
+    from gpu_util import dev, oracle_forward, ptr_table, to_dev
+    from loquetier_b200 import ops
+    c = to_dev(case)
+    T = c["x"].shape[0]
+    plan = ops.Plan(c["seg_d"], T)
+    wa_t = ptr_table([c["wa_d"][i] for i in c["ids"]])
+    wb_t = ptr_table([c["wb_d"][i] for i in c["ids"]])
+    v = torch.full((T, c["rank"]), 7.0, dtype=c["dtype"], device=dev())
+    y = (torch.zeros((T, c["h_out"]), dtype=c["dtype"], device=dev()) if y_init is None else y_init.to(dev()).clone())
+    sc = None if scale is None else torch.tensor([scale[i] for i in c["ids"]], dtype=torch.float32, device=dev())
+    ops.gemm(v, c["x"], wa_t, plan, is_row_major=c["is_row_major"])
+    ops.gemm(y, v, wb_t, plan, is_row_major=c["is_row_major"], seg_scale=sc, accumulate=accumulate)
+    torch.cuda.synchronize()
+    plan.raise_if_failed()
+    y_ref, v_ref = oracle_forward(case, scale=scale, y_init=y_init)
+    a, b = case["seg"][0], case["seg"][-1]
+    assert_close(v.cpu()[a:b], v_ref[a:b], what="v (shrink alone)")
+    assert_close(y.cpu()[a:b], y_ref[a:b], what="y (expand alone)")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rm", [False, True])
+@pytest.mark.parametrize("rank", [40, 64, 128])
+def test_halves_edge_lengths(dtype, rm, rank):
+    _check_halves(_case(600 + rank, TALL_LENS, 5, 200, 328, rank, dtype, rm))
+
+
+@pytest.mark.parametrize("h_in,h_out", [(4096, 1024), (14336, 4096), (4096, 14336)])
+@pytest.mark.parametrize("rm", [False, True])
+def test_halves_shapes(h_in, h_out, rm):
+    _check_halves(_case(27, [200, 1, 3, 130, 128], 4, h_in, h_out, 64, torch.bfloat16, rm))
+
+
+def test_halves_scale_and_accumulate():
+    c = _case(28, [140, 1, 290, 17], 3, 512, 776, 64, torch.bfloat16)
+    g = torch.Generator().manual_seed(2)
+    y0 = torch.randn((sum(c["lens"]), 776), generator=g).to(torch.bfloat16)
+    _check_halves(c, scale=[2.0, 0.5, 1.25])
+    _check_halves(c, scale=[2.0, 0.5, 1.25], accumulate=True, y_init=y0)
