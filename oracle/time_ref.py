@@ -175,7 +175,7 @@ def main():
     assert ref_cuda.available(), "build oracle/_ref/libref.so first (python oracle/build_ref.py --reference ...)"
     res = dict(gpu=torch.cuda.get_device_name(0),
                smlm_forward=dict(c2=smlm_case("c2"), c3=smlm_case("c3", only=("q_proj", "gate_proj")),
-                                 c4=smlm_case("c4")),
+                                 c4=smlm_case("c4"), c5=smlm_case("c5")),
                rms_norm_forward=rms_case(), decode_attention=decode_case(), prefill_attention=prefill_case())
     print(json.dumps(res, indent=1))
 
