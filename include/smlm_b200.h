@@ -59,6 +59,13 @@ const char* smlm_b200_status_string(int status);
  * writes into that buffer. */
 size_t smlm_b200_tmp_size(int num_problems);
 
+/* For callers that have one weight pointer per segment and no adapter table (the arguments of the reference
+ * operator, loquetier_ops.cc:277-281): ids_out[i] = index of the first segment whose pointer equals w_table[i].
+ * Passing w_table as the adapter table (n_table = nseg) and ids_out as seg_ids to smlm_b200_plan_grouped and to the
+ * compute call gathers the decode tokens of one adapter into one piece wherever they sit in the batch - what the
+ * reference only gets from a batch sorted by adapter.  nseg <= 4096 for the grouped plan to apply. */
+int smlm_b200_group_ids_from_pointers(const void* const* w_table, int nseg, int32_t* ids_out, void* stream);
+
 /* Segment bookkeeping on the device: the run-length merge of the ordered requests of a step into
  * segments, bit-identical to the reference's host loop (src/loquetier_src/model_generation.py:267-283:
  * neighbours with the same adapter become one segment; `segment` = cumsum of the lengths with a

@@ -38,6 +38,7 @@ SIGNATURES = {
     "smlm_b200_version": (c_int, []),
     "smlm_b200_status_string": (c_char_p, [c_int]),
     "smlm_b200_tmp_size": (c_size_t, [c_int]),
+    "smlm_b200_group_ids_from_pointers": (c_int, [c_void_p, c_int, c_void_p, c_void_p]),
     "smlm_b200_merge_segments": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "smlm_b200_piece_rows": (c_int, [c_int]),
     "smlm_b200_set_tensor_core_mode": (c_int, [c_int]),

@@ -808,6 +808,14 @@ int smlm_b200_merge_segments(const int32_t* req_ids, const int32_t* req_len, int
   return SMLM_OK;
 }
 
+int smlm_b200_group_ids_from_pointers(const void* const* w_table, int nseg, int32_t* ids_out, void* stream) {
+  if (nseg < 0) return SMLM_ERR_INVALID_ARGUMENT;
+  if (nseg == 0) return SMLM_OK;
+  if (w_table == nullptr || ids_out == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
+  return launch(pointer_groups_kernel, dim3((nseg + kGroupThreads - 1) / kGroupThreads, 1, 1), kGroupThreads, 1, 0,
+                static_cast<cudaStream_t>(stream), w_table, nseg, ids_out);
+}
+
 int smlm_b200_plan_status(const void* plan, int* n_pieces, void* stream) {
   if (plan == nullptr) return SMLM_ERR_INVALID_ARGUMENT;
   int hdr[kPlanHeaderInts] = {0, 0, 0, 0};

@@ -94,4 +94,36 @@ __global__ void __launch_bounds__(kMergeThreads) merge_segments_kernel(
   for (int k = tid; k < n; k += kMergeThreads) seg_len[k] = seg_indptr[k + 1] - seg_indptr[k];
 }
 
+// Adapter indices for callers that only have one weight pointer per segment (the reference operator's
+// arguments, kernel_src/csrc/loquetier_ops.cc:277-281): ids[i] = the first segment whose pointer equals
+// w[i].  With the pointer array itself as the adapter table and these ids, a grouped plan gathers the decode
+// tokens of one adapter into one piece exactly as it does for callers that keep an adapter table.  Integer
+// work; n up to a few thousand, so the quadratic scan (shared-memory tiles of pointers) is microseconds.
+constexpr int kGroupThreads = 256;
+__global__ void __launch_bounds__(kGroupThreads) pointer_groups_kernel(const void* const* __restrict__ w, int n,
+                                                                         int32_t* __restrict__ ids) {
+  __shared__ const void* tile[kGroupThreads];
+  pdl_wait();
+  const int i = blockIdx.x * kGroupThreads + threadIdx.x;
+  const void* mine = i < n ? w[i] : nullptr;
+  int first = i;
+  const int limit = min(n, (static_cast<int>(blockIdx.x) + 1) * kGroupThreads);   // only j < i matters
+  for (int j0 = 0; j0 < limit; j0 += kGroupThreads) {
+    const int j = j0 + threadIdx.x;
+    tile[threadIdx.x] = j < n ? w[j] : nullptr;
+    __syncthreads();
+    if (i < n && first == i) {
+      const int m = min(kGroupThreads, i - j0);   // candidates j0 .. i - 1 of this tile
+      for (int k = 0; k < m; ++k) {
+        if (tile[k] == mine) {
+          first = j0 + k;
+          break;
+        }
+      }
+    }
+    __syncthreads();
+  }
+  if (i < n) ids[i] = first;
+}
+
 }  // namespace smlm

@@ -48,7 +48,20 @@ def smlm_forward_cutlass(y: torch.Tensor, x: torch.Tensor, w_ptr: torch.Tensor, 
         raise RuntimeError("y and x must have the same number of rows")
     if nseg <= 0 or x.size(0) == 0:
         return
-    plan = ops.Plan(s, x.size(0))
+    T = int(x.size(0))
+    if 16 <= nseg <= 4096 and T <= 32 * nseg:
+        # Many short segments (a decode batch): segments that share a weight pointer share an adapter.  Their
+        # indices are derived on the device and a grouped plan gathers each adapter's decode tokens into one
+        # piece, so that its panel is fetched once - sorted batch or not.  Nothing is read back to the host.
+        ids = torch.empty(nseg, dtype=torch.int32, device=x.device)
+        with torch.cuda.device(x.device):
+            ops.check(lib.smlm_b200_group_ids_from_pointers(w_ptr.data_ptr(), nseg, ids.data_ptr(),
+                                                            torch.cuda.current_stream(x.device).cuda_stream),
+                      "smlm_b200_group_ids_from_pointers")
+        plan = ops.Plan(s, T, seg_ids=ids, n_table=nseg)
+        ops.gemm(y, x, w_ptr[:nseg], plan, is_row_major=bool(is_row_major), seg_ids=ids)
+        return
+    plan = ops.Plan(s, T)
     ops.gemm(y, x, w_ptr, plan, is_row_major=bool(is_row_major))
 
 
