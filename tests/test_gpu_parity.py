@@ -445,3 +445,19 @@ def test_plan_pair_builds_the_same_two_plans_in_one_launch():
         n = p.status()[0]
         return p.buf[:4 + 4 * n]
     assert torch.equal(used(a0), used(a1)) and torch.equal(used(b0), used(b1))
+
+
+@pytest.mark.parametrize("n", [1, 17, 256, 257, 1000, 4096])
+def test_adapter_groups_from_pointers_are_first_occurrences(n):
+    """ids[i] = first j with w[j] == w[i]: integer work, bit-exact against the host loop; several tiles and CTAs."""
+    from loquetier_b200.cabi import check, lib
+    rng = np.random.default_rng(n)
+    vals = rng.integers(1, max(2, n // 3 + 1), size=n).astype(np.int64) * 4096   # many repeats
+    w = torch.tensor(vals, dtype=torch.int64, device="cuda:0")
+    ids = torch.full((n,), -1, dtype=torch.int32, device="cuda:0")
+    check(lib.smlm_b200_group_ids_from_pointers(w.data_ptr(), n, ids.data_ptr(),
+                                                torch.cuda.current_stream().cuda_stream), "group ids")
+    torch.cuda.synchronize()
+    first = {}
+    want = [first.setdefault(int(v), i) for i, v in enumerate(vals)]
+    assert ids.cpu().tolist() == want
