@@ -362,3 +362,29 @@ def test_prefill_many_short_requests():
     o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, 0, N, P)
     want = A.batch_prefill(q, qind, pages, indptr, last, 0, THETA)
     assert_close(o, want, what="70 short requests")
+
+
+@pytest.mark.parametrize("seed", list(range(12)))
+def test_prefill_random_shapes(seed):
+    """Seeded random batches: group size, page size, kv heads, layers, batch size, cached prefix lengths and
+    storage type all vary; every row against the oracle."""
+    rng = np.random.default_rng(9000 + seed)
+    group = int(rng.choice([1, 2, 4, 8]))
+    P = int(rng.choice([8, 16, 32, 64]))
+    N = int(rng.integers(1, 4))
+    Lyr = int(rng.integers(1, 3))
+    layer = int(rng.integers(0, Lyr))
+    dtype = torch.bfloat16 if seed % 2 == 0 else torch.float16
+    B = int(rng.integers(1, 10))
+    seqlens = [int(v) for v in rng.integers(0, 260, size=B)]
+    qlens = [int(rng.integers(0, L + 1)) if rng.random() < 0.4 else L for L in seqlens]
+    if sum(qlens) == 0:
+        seqlens[0], qlens[0] = 70, 70
+    pages, indptr, last = A.make_cache(9100 + seed, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(9200 + seed)
+    qind = _qind(qlens)
+    q = torch.randn((qind[-1], N * group, 128), generator=g).to(dtype)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    want = A.batch_prefill(q, qind, pages, indptr, last, layer, THETA)
+    assert_close(o, want, what=f"seed {seed}: group {group} page {P} heads {N} batch {B} {dtype}")
