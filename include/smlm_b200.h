@@ -169,9 +169,16 @@ int smlm_b200_fwd(void* y, const void* x, void* v, const void* const* wa_table, 
 /* Bytes of the workspace the weight-gradient kernels need for a batch of T token
  * rows in npart partitions and one (h1 == 0) or two column counts.  The workspace
  * holds tickets and parked partial sums of partitions that are spread over several
- * CTAs.  It must be zero-filled ONCE after allocation; every launch leaves it
- * zeroed again.  Launches that overlap in time must not share a workspace. */
+ * CTAs.  Its head - smlm_b200_wgrad_ticket_bytes(...) bytes, the tickets - must be
+ * zero when a launch starts; every launch leaves the tickets it used zeroed again.  So:
+ * zero-fill the workspace once after allocation, and zero the head again whenever the
+ * next call's shape (T, npart, rank, column counts, or the kinds selected by
+ * smlm_b200_wgrad_select_multi) differs from the previous call's on the same workspace:
+ * a different shape puts the boundary between tickets and parked sums elsewhere, and what
+ * one shape parked lies where another expects tickets.  Launches that overlap in time must
+ * not share a workspace. */
 size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h1);
+size_t smlm_b200_wgrad_ticket_bytes(int T, int npart, int rank, int h0, int h1);
 
 /* Per-partition weight gradient  G_p = scale_p * P[rows_p]^T . Q[rows_p]  with P
  * [T, rank] and Q [T, h]; G_p is [rank, h] (transposed == 0) or [h, rank]
@@ -291,6 +298,9 @@ int smlm_b200_bwd_dx_multi(const smlm_b200_proj* projs, int nproj, const int32_t
 /* Workspace of smlm_b200_wgrad_pair_multi for these projections (h_in, h_out are read); same rules as
  * smlm_b200_wgrad_workspace_bytes. */
 size_t smlm_b200_wgrad_multi_workspace_bytes(const smlm_b200_proj* projs, int nproj, int T, int npart, int rank);
+/* The head of that workspace that has to be zero (see smlm_b200_wgrad_workspace_bytes), for the whole set; it covers
+ * the head of every subset that smlm_b200_wgrad_select_multi may launch. */
+size_t smlm_b200_wgrad_multi_ticket_bytes(const smlm_b200_proj* projs, int nproj, int T, int npart, int rank);
 
 /* smlm_b200_wgrad_pair for every projection: reads dv, x, v, go; writes through dA_table, dB_table. */
 int smlm_b200_wgrad_pair_multi(const smlm_b200_proj* projs, int nproj, const int32_t* part_indptr,

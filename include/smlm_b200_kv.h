@@ -34,9 +34,13 @@ extern "C" {
 
 /* Bytes of the workspace of smlm_b200_batch_decode for this batch shape.  The reference asks its
  * caller for a fixed 64 MiB `tmpbuf` (loquetier_ops.cc:152-153); here the size follows the batch.  The
- * workspace must be zero-filled ONCE after allocation; every launch leaves it ready for the next.
- * Launches that may overlap in time must not share a workspace. */
+ * head of the workspace - smlm_b200_batch_decode_ticket_bytes(...) bytes - must be zero when a launch starts;
+ * every launch leaves it zeroed again.  So: zero-fill once after allocation, and zero the head again whenever
+ * batch_size * num_kv_heads differs from the previous call's on the same workspace (a different shape moves the
+ * boundary between the tickets and the parked softmax states).  Launches that may overlap in time must not share
+ * a workspace. */
 size_t smlm_b200_batch_decode_workspace_bytes(int batch_size, int num_qo_heads, int num_kv_heads);
+size_t smlm_b200_batch_decode_ticket_bytes(int batch_size, int num_kv_heads);
 
 /* Decode attention of a batch of one-token requests over their paged caches:
  *   o[b, h] = softmax( rope(q[b, h], L_b - 1) . rope(K_b[:, h / group], 0..L_b-1)^T / sqrt(head_dim) ) . V_b

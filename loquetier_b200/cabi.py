@@ -54,6 +54,7 @@ SIGNATURES = {
     "smlm_b200_fwd": (c_int, [c_void_p] * 8 + [c_int] * 11 + [c_void_p]),
     "smlm_b200_bwd_dx": (c_int, [c_void_p] * 8 + [c_int] * 10 + [c_void_p]),
     "smlm_b200_wgrad_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "smlm_b200_wgrad_ticket_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad": (c_int, [c_void_p] * 7 + [c_size_t] + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_static": (c_int, [c_void_p] * 6 + [c_int] * 8 + [c_void_p]),
     "smlm_b200_wgrad_pair": (c_int, [c_void_p] * 11 + [c_size_t] + [c_int] * 11 + [c_void_p]),
@@ -61,11 +62,13 @@ SIGNATURES = {
     "smlm_b200_fwd_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 9 + [c_void_p]),
     "smlm_b200_bwd_dx_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p] + [c_int] * 7 + [c_void_p]),
     "smlm_b200_wgrad_multi_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
+    "smlm_b200_wgrad_multi_ticket_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
     "smlm_b200_wgrad_pair_multi": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_size_t] + [c_int] * 9 + [c_void_p]),
     "smlm_b200_wgrad_select_multi": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_size_t] + [c_int] * 9 + [c_void_p]),
     "smlm_b200_batch_decode_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "smlm_b200_batch_decode_ticket_bytes": (c_size_t, [c_int, c_int]),
     "smlm_b200_batch_prefill_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "smlm_b200_batch_prefill": (c_int, [c_void_p] * 7 + [c_size_t, c_void_p] + [c_int] * 9 + [c_float, c_int, c_void_p]),
     "smlm_b200_batch_decode": (c_int, [c_void_p] * 6 + [c_size_t, c_void_p] + [c_int] * 8 + [c_float, c_int, c_void_p]),

@@ -527,6 +527,13 @@ size_t wgrad_workspace_need(int T, int npart, int R, const int* h, int nh) {
   return std::max(a.ticket_bytes + a.scratch_bytes, b.ticket_bytes + b.scratch_bytes);
 }
 
+// The head of a workspace that holds the tickets, for either kernel variant (the larger of the two).
+size_t wgrad_ticket_need(int T, int npart, int R, const int* h, int nh) {
+  const WgradShape a = wgrad_shape(T, npart, R, h, nh, false);
+  const WgradShape b = wgrad_shape(T, npart, R, h, nh, true);
+  return std::max(a.ticket_bytes, b.ticket_bytes);
+}
+
 // ---- built-in scratch for callers that cannot allocate ------------------------------
 // Some hosts of this library run where device allocation is off the table: inside a
 // latency-critical serving loop that has pre-carved all of its memory, in a plugin that
@@ -892,6 +899,12 @@ size_t smlm_b200_wgrad_workspace_bytes(int T, int npart, int rank, int h0, int h
   return wgrad_workspace_need(T, npart, rank, hs, 2);
 }
 
+size_t smlm_b200_wgrad_ticket_bytes(int T, int npart, int rank, int h0, int h1) {
+  if (T < 0 || npart < 0 || rank <= 0 || h0 <= 0 || h1 < 0) return 0;
+  const int hs[2] = {h0, h1};
+  return wgrad_ticket_need(T, npart, rank, hs, 2);
+}
+
 int smlm_b200_wgrad(void* const* g_table, const void* p, const void* q, const int32_t* part_indptr,
                     const float* part_scale, void* plan, void* workspace, size_t workspace_bytes, int npart, int T,
                     int rank, int h, int dtype, int transposed, int accumulate, int grad_fp32, void* stream) {
@@ -1058,6 +1071,16 @@ size_t smlm_b200_wgrad_multi_workspace_bytes(const smlm_b200_proj* projs, int np
   return wgrad_workspace_need(T, npart, rank, hs, 2 * nproj);
 }
 
+size_t smlm_b200_wgrad_multi_ticket_bytes(const smlm_b200_proj* projs, int nproj, int T, int npart, int rank) {
+  if (T < 0 || npart < 0 || rank <= 0 || !projs_ok(projs, nproj)) return 0;
+  int hs[2 * SMLM_MAX_PROJ];
+  for (int j = 0; j < nproj; ++j) {
+    hs[2 * j] = projs[j].h_out;
+    hs[2 * j + 1] = projs[j].h_in;
+  }
+  return wgrad_ticket_need(T, npart, rank, hs, 2 * nproj);
+}
+
 int smlm_b200_wgrad_select_multi(const smlm_b200_proj* projs, int nproj, int which, const int32_t* part_indptr,
                                  const int32_t* part_ids, const float* part_scale, void* plan, void* workspace,
                                  size_t workspace_bytes, int n_table, int npart, int T, int rank, int dtype,
@@ -1106,6 +1129,11 @@ size_t smlm_b200_batch_decode_workspace_bytes(int batch_size, int num_qo_heads, 
   return decode_ticket_bytes(batch_size, num_kv_heads) +
          static_cast<size_t>(batch_size) * num_qo_heads * decode_splits(batch_size, num_kv_heads) * kPdRec *
              sizeof(float);
+}
+
+size_t smlm_b200_batch_decode_ticket_bytes(int batch_size, int num_kv_heads) {
+  if (batch_size <= 0 || num_kv_heads <= 0) return 0;
+  return decode_ticket_bytes(batch_size, num_kv_heads);
 }
 
 int smlm_b200_batch_decode(void* o, const void* q, const void* const* kv_ptrs, const int32_t* kv_indptr,

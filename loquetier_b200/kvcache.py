@@ -153,6 +153,7 @@ class BatchedKvCache:
 # ---------------------------------------------------------------------------
 
 _WORKSPACES = {}
+_WS_SHAPE = {}
 
 
 def _stream(t):
@@ -167,13 +168,22 @@ def _dtype_code(t):
 
 
 def decode_workspace(device, batch: int, num_qo_heads: int, num_kv_heads: int) -> Optional[torch.Tensor]:
-    """Zero-filled scratch of the decode kernel, cached per device and grown on demand (the kernel
-    leaves it zeroed).  Calls that may overlap on different streams need workspaces of their own."""
-    need = int(lib.smlm_b200_batch_decode_workspace_bytes(int(batch), int(num_qo_heads), int(num_kv_heads)))
+    """Scratch of the decode kernel with its tickets zeroed, cached per device and grown on demand.  The kernel
+    leaves the tickets zeroed, but another batch shape moves the boundary between tickets and parked softmax
+    states, so the head is cleared again whenever the shape differs from the previous one.  Ask for it right
+    before the launch; calls that may overlap on different streams need workspaces of their own."""
+    shape = (int(batch), int(num_qo_heads), int(num_kv_heads))
+    need = int(lib.smlm_b200_batch_decode_workspace_bytes(*shape))
     ws = _WORKSPACES.get(device)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 1 << 16), dtype=torch.uint8, device=device)
         _WORKSPACES[device] = ws
+    elif _WS_SHAPE.get(device) != shape:
+        tickets = int(lib.smlm_b200_batch_decode_ticket_bytes(int(batch), int(num_kv_heads)))
+        if tickets > 0:
+            with torch.cuda.device(device):
+                ws[:tickets].zero_()
+    _WS_SHAPE[device] = shape
     return ws
 
 

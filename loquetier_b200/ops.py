@@ -154,17 +154,33 @@ def bwd_dx(dx, dv, go, wa_table, wb_table, plan: Plan, rank: int, is_row_major=F
 _WORKSPACES = {}
 
 
-def wgrad_workspace(device, T: int, npart: int, rank: int, h0: int, h1: int = 0, slot: int = 0) -> torch.Tensor:
-    """Zero-filled scratch of the weight-gradient kernels, cached per device and grown
-    on demand.  The kernels leave it zeroed, so it is cleared only when (re)allocated.
-    One workspace per device: calls that may overlap on different streams need their
-    own: ask for a different ``slot``."""
-    need = int(lib.smlm_b200_wgrad_workspace_bytes(int(T), int(npart), int(rank), int(h0), int(h1)))
-    ws = _WORKSPACES.get((device, slot))
+_WS_SHAPE = {}   # (device, slot) -> the shape the cached workspace was last handed out for
+
+
+def _cached_workspace(device, slot, need: int, shape, ticket_bytes: int) -> torch.Tensor:
+    """One buffer per (device, slot), grown on demand and zero-filled when (re)allocated.  The kernels leave
+    the tickets at its head zeroed, but a different shape moves the boundary between tickets and parked sums,
+    so the head is cleared again (a few KB, on the current stream) whenever the shape differs from the one the
+    buffer was last handed out for."""
+    key = (device, slot)
+    ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < need:
         ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=device)
-        _WORKSPACES[(device, slot)] = ws
+        _WORKSPACES[key] = ws
+    elif _WS_SHAPE.get(key) != shape and ticket_bytes > 0:
+        with torch.cuda.device(device):
+            ws[:ticket_bytes].zero_()
+    _WS_SHAPE[key] = shape
     return ws
+
+
+def wgrad_workspace(device, T: int, npart: int, rank: int, h0: int, h1: int = 0, slot: int = 0) -> torch.Tensor:
+    """Scratch of the weight-gradient kernels with its tickets zeroed, cached per device and ``slot``.  Ask for
+    it right before the launch that uses it (on the stream of that launch); calls that may overlap on different
+    streams need workspaces of their own: different slots."""
+    shape = (int(T), int(npart), int(rank), int(h0), int(h1))
+    need = int(lib.smlm_b200_wgrad_workspace_bytes(*shape))
+    return _cached_workspace(device, slot, need, shape, int(lib.smlm_b200_wgrad_ticket_bytes(*shape)))
 
 
 def wgrad(g_table, p, q, part_indptr, plan: Plan, transposed: bool, part_scale=None, accumulate=False,
@@ -272,15 +288,14 @@ def bwd_dx_multi(ps: ProjSet, plan: Plan, rank: int, is_row_major=False, part_id
               "smlm_b200_bwd_dx_multi")
 
 
-def wgrad_multi_workspace(ps: ProjSet, T: int, npart: int, rank: int, slot: str = "multi") -> torch.Tensor:
-    """Zero-filled workspace of ``wgrad_pair_multi`` for this set, cached per device and slot."""
+def wgrad_multi_workspace(ps: ProjSet, T: int, npart: int, rank: int, slot: str = "multi", which: int = 3) -> torch.Tensor:
+    """Workspace of ``wgrad_pair_multi`` for this set with its tickets zeroed, cached per device and slot (see
+    ``wgrad_workspace``); ``which`` is the kinds the launch will select."""
     need = int(lib.smlm_b200_wgrad_multi_workspace_bytes(ps.ptr, ps.n, int(T), int(npart), int(rank)))
-    dev = ps.ref.device
-    ws = _WORKSPACES.get((dev, slot))
-    if ws is None or ws.numel() < need:
-        ws = torch.zeros(max(need, 1 << 20), dtype=torch.uint8, device=dev)
-        _WORKSPACES[(dev, slot)] = ws
-    return ws
+    tickets = int(lib.smlm_b200_wgrad_multi_ticket_bytes(ps.ptr, ps.n, int(T), int(npart), int(rank)))
+    shape = (int(T), int(npart), int(rank), tuple((int(ps.arr[i].h_in), int(ps.arr[i].h_out)) for i in range(ps.n)),
+             int(which))
+    return _cached_workspace(ps.ref.device, slot, need, shape, tickets)
 
 
 WGRAD_DB, WGRAD_DA = 1, 2
@@ -291,7 +306,7 @@ def wgrad_pair_multi(ps: ProjSet, part_indptr, plan: Plan, rank: int, is_row_maj
                      independent=False, which=WGRAD_DB | WGRAD_DA):
     """``wgrad_pair`` for every projection of the set in one launch; ``which`` restricts it to dB (reads v, go)
     or dA (reads dv, x)."""
-    ws = workspace if workspace is not None else wgrad_multi_workspace(ps, plan.T, plan.nseg, rank)
+    ws = workspace if workspace is not None else wgrad_multi_workspace(ps, plan.T, plan.nseg, rank, which=which)
     with torch.cuda.device(ps.ref.device):
         check(lib.smlm_b200_wgrad_select_multi(ps.ptr, ps.n, int(which), part_indptr.data_ptr(), _p(part_ids),
                                                _p(part_scale), plan.buf.data_ptr(), ws.data_ptr(), ws.numel(),

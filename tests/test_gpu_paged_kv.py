@@ -388,3 +388,26 @@ def test_prefill_random_shapes(seed):
     o = _prefill(q.to(DEV), torch.tensor(qind, dtype=torch.int32, device=DEV), ptrs, ind, lst, Lyr, layer, N, P)
     want = A.batch_prefill(q, qind, pages, indptr, last, layer, THETA)
     assert_close(o, want, what=f"seed {seed}: group {group} page {P} heads {N} batch {B} {dtype}")
+
+
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_decode_random_shapes(seed):
+    """Seeded random decode batches (group size, page size, kv heads, layers, batch size, context lengths,
+    storage type), every row against the oracle; small batches are cut into key ranges, large ones are not."""
+    rng = np.random.default_rng(9500 + seed)
+    group = int(rng.choice([1, 2, 4, 8]))
+    P = int(rng.choice([8, 16, 32, 64]))
+    N = int(rng.integers(1, 5))
+    Lyr = int(rng.integers(1, 3))
+    layer = int(rng.integers(0, Lyr))
+    dtype = torch.bfloat16 if seed % 2 == 0 else torch.float16
+    B = int(rng.choice([1, 3, 17, 130]))
+    hi = 1200 if B < 20 else 90
+    seqlens = [int(v) for v in rng.integers(1, hi, size=B)]
+    pages, indptr, last = A.make_cache(9600 + seed, seqlens, Lyr, N, P, 128, dtype)
+    g = torch.Generator().manual_seed(9700 + seed)
+    q = torch.randn((B, N * group, 128), generator=g).to(dtype)
+    pd, ptrs, ind, lst = _to_dev(pages, indptr, last)
+    o = _decode(q.to(DEV), ptrs, ind, lst, Lyr, layer, N, P)
+    want = A.batch_decode(q, pages, indptr, last, layer, THETA)
+    assert_close(o, want, what=f"seed {seed}: group {group} page {P} heads {N} batch {B} {dtype}")

@@ -461,3 +461,19 @@ def test_adapter_groups_from_pointers_are_first_occurrences(n):
     first = {}
     want = [first.setdefault(int(v), i) for i, v in enumerate(vals)]
     assert ids.cpu().tolist() == want
+
+
+def test_cached_workspace_survives_alternating_shapes():
+    """The cached weight-gradient workspace is used for one shape, then another whose tickets reach into what the
+    first one parked, then the first again: every result must still match.  Long partitions, so that partial
+    sums really are parked (a partition spread over several CTAs)."""
+    shapes = [(1600, [0, 900, 1600], 2048, 256, 16), (1900, [0, 100, 1900], 256, 4096, 16),
+              (1600, [0, 900, 1600], 2048, 256, 16), (700, [0, 700], 512, 512, 64)]
+    for k, (T, part, h_in, h_out, rank) in enumerate(shapes * 2):
+        c = _case(500 + k % len(shapes), [T], len(part) - 1, h_in, h_out, rank, torch.bfloat16, False, ids=[0])
+        dx, dA, dB = _run_bwd(c, part)
+        gx, gA, gB = _oracle_bwd(c, part)
+        _grad_close(dx, gx, f"dX, call {k}")
+        for p in range(len(part) - 1):
+            _grad_close(dA[p], gA[p], f"dA{p}, call {k}")
+            _grad_close(dB[p], gB[p], f"dB{p}, call {k}")
