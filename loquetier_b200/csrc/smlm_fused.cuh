@@ -321,6 +321,14 @@ __global__ void __launch_bounds__(kFusedThreads, fused_ctas_per_sm(R16)) fused_k
       const int kcols = min(KC, K1 - k0);
       const int nch = (kcols + 63) >> 6;
       const uint32_t wbytes = static_cast<uint32_t>(kcols) * R * 2;
+      if (gather && (kcols & 15) != 0 && it >= S) {
+        // the slot held a full step before: the 8 columns past kcols that the last 16-column step
+        // reads carry that step's data, not the zeros written before the loop.  The consumers have
+        // released the slot (the wait above) and see these stores through the barrier's release.
+        for (int r = lane; r < nrows; r += 32)
+          *reinterpret_cast<uint4*>(smem + slot * SM::kStage + r * SM::XPad + kcols * 2) = make_uint4(0, 0, 0, 0);
+        __syncwarp();
+      }
       if (lane == 0)
         mbar_expect_tx(fb, (gather ? static_cast<uint32_t>(nrows) * kcols * 2 : rowbytes * nch) + wbytes);
       __syncwarp();

@@ -477,3 +477,53 @@ def test_cached_workspace_survives_alternating_shapes():
         for p in range(len(part) - 1):
             _grad_close(dA[p], gA[p], f"dA{p}, call {k}")
             _grad_close(dB[p], gB[p], f"dB{p}, call {k}")
+
+
+@pytest.mark.parametrize("seed", list(range(16)))
+def test_forward_and_backward_random_shapes(seed):
+    """Seeded random batches: segment lengths (empty, single-token, long), ranks 8..128, hidden sizes that are
+    multiples of 8 but of nothing larger, both layouts, both storage types, pointer-per-segment and adapter-table
+    calls; forward and backward against the oracle."""
+    from gpu_util import check_forward
+    rng = np.random.default_rng(7000 + seed)
+    rank = int(rng.choice([8, 16, 24, 32, 40, 64, 96, 128]))
+    h_in = int(rng.integers(4, 300)) * 8
+    h_out = int(rng.integers(4, 300)) * 8
+    dtype = torch.bfloat16 if seed % 2 == 0 else torch.float16
+    rm = bool(rng.integers(0, 2))
+    nseg = int(rng.integers(1, 24))
+    kinds = rng.integers(0, 4, size=nseg)
+    lens = [0 if k == 0 else 1 if k == 1 else int(rng.integers(2, 40)) if k == 2 else int(rng.integers(40, 400))
+            for k in kinds]
+    if sum(lens) == 0:
+        lens[0] = 77
+    n_ad = int(rng.integers(1, 7))
+    c = _case(7100 + seed, lens, n_ad, h_in, h_out, rank, dtype, rm)
+    check_forward(c)
+    check_forward(c, indexed=True)
+    # backward over the first few segments as train partitions (pointer tables per partition)
+    npart = int(rng.integers(1, min(nseg, n_ad) + 1))
+    part = [0]
+    for n in lens[:npart]:
+        part.append(part[-1] + n)
+    if part[-1] == 0:
+        return
+    cb = _case(7200 + seed, [sum(lens)], max(npart, 1), h_in, h_out, rank, dtype, rm, ids=[0])
+    dx, dA, dB = _run_bwd(cb, part)
+    gx, gA, gB = _oracle_bwd(cb, part)
+    _grad_close(dx[:part[-1]], gx[:part[-1]], f"dX seed {seed}")
+    for p in range(npart):
+        _grad_close(dA[p], gA[p], f"dA{p} seed {seed}")
+        _grad_close(dB[p], gB[p], f"dB{p} seed {seed}")
+
+
+@pytest.mark.parametrize("rank,rm", [(8, False), (16, True), (16, False), (32, True)])
+def test_grouped_plan_hidden_size_ending_in_half_a_step(rank, rm):
+    """Gathered rows of short segments with a hidden size of 16k + 8 and more column steps than ring
+    stages: the last 16-column step of a row reads 8 columns past the hidden size, which must be zeros
+    although the stage held a full step before."""
+    from gpu_util import check_forward
+    lens = [1, 3, 1, 2, 1, 1, 5, 1, 40, 1, 1, 2]
+    c = _case(812, lens, 3, 2056 + 1024, 136, rank, torch.bfloat16, rm)
+    check_forward(c, indexed=True)
+    check_forward(c)
