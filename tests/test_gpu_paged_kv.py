@@ -1,6 +1,8 @@
 """The paged key-value cache on the GPU through the C ABI: appending keys/values (bit-exact), batch
 decode and causal prefill attention (rtol = atol = 1e-2 for 16-bit storage with fp32 arithmetic) against the CPU oracle,
 and - where oracle/_ref/libref.so has been built - against the reference's own kernels."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -12,6 +14,7 @@ from oracle import attention_oracle as A
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
 THETA = 10000.0
+MORE = max(1, int(os.environ.get("SMLM_RANDOM_SEEDS", "1")))   # multiplies the seeds of the random-shape tests
 
 
 def _to_dev(pages, indptr, last):
@@ -364,7 +367,7 @@ def test_prefill_many_short_requests():
     assert_close(o, want, what="70 short requests")
 
 
-@pytest.mark.parametrize("seed", list(range(12)))
+@pytest.mark.parametrize("seed", list(range(12 * MORE)))
 def test_prefill_random_shapes(seed):
     """Seeded random batches: group size, page size, kv heads, layers, batch size, cached prefix lengths and
     storage type all vary; every row against the oracle."""
@@ -390,7 +393,7 @@ def test_prefill_random_shapes(seed):
     assert_close(o, want, what=f"seed {seed}: group {group} page {P} heads {N} batch {B} {dtype}")
 
 
-@pytest.mark.parametrize("seed", list(range(8)))
+@pytest.mark.parametrize("seed", list(range(8 * MORE)))
 def test_decode_random_shapes(seed):
     """Seeded random decode batches (group size, page size, kv heads, layers, batch size, context lengths,
     storage type), every row against the oracle; small batches are cut into key ranges, large ones are not."""
