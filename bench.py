@@ -760,6 +760,32 @@ class HostPipeline:
                     h["dB"].copy_(p["dB"], non_blocking=True)
         cur.wait_stream(self.s_out)
 
+    def copies_only(self):
+        """The host-link bound of a step, measured: the same uploads and downloads on the same two streams
+        with no kernel and no dependency between them, both directions busy from start to end."""
+        torch, wl = self.torch, self.wl
+        cur = torch.cuda.current_stream()
+        self.s_in.wait_stream(cur)
+        self.s_out.wait_stream(cur)
+        with torch.cuda.stream(self.s_in):
+            for i, b in self.units:
+                p, h = wl.proj[i], self.h[i]
+                lo, hi, _ = self.blocks[b]
+                p["x"][lo:hi].copy_(h["x"][lo:hi], non_blocking=True)
+                if wl.tl and lo == 0:
+                    p["go"].copy_(h["go"], non_blocking=True)
+        with torch.cuda.stream(self.s_out):
+            for i, b in self.units:
+                p, h = wl.proj[i], self.h[i]
+                lo, hi, _ = self.blocks[b]
+                h["y"][lo:hi].copy_(p["y"][lo:hi], non_blocking=True)
+                if wl.tl and lo == 0:
+                    h["dx"].copy_(p["dx"], non_blocking=True)
+                    h["dA"].copy_(p["dA"], non_blocking=True)
+                    h["dB"].copy_(p["dB"], non_blocking=True)
+        cur.wait_stream(self.s_in)
+        cur.wait_stream(self.s_out)
+
 
 # ---------------------------------------------------------------------------
 # CPU path (the oracle port of the reference's per-segment torch path)
@@ -1223,6 +1249,7 @@ def main():
     ap.add_argument("--chunks", type=int, default=1, help="c5: slot ranges of the last projection's exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--e2e-blocks", type=int, default=4, help="row blocks the end-to-end step cuts the batch into")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-overlap", action="store_true", help="do not mark launches independent of each other")
     ap.add_argument("--streams", type=int, default=3, help="single: streams the backward launches are dealt over")
@@ -1389,7 +1416,7 @@ def main():
                                    launches=v[2], share=v[0] / sum(x[0] for x in kb.values())) for k, v in kb.items()}
 
     if not a.no_e2e:
-        hp = HostPipeline(wl, torch)
+        hp = HostPipeline(wl, torch, nblocks=a.e2e_blocks)
         e_ms, e_per = timed(hp.step, max(3, min(a.steps, 10)), 3, torch, dist, None, 3)
         for pl in hp.plans:
             pl.raise_if_failed()
@@ -1402,6 +1429,12 @@ def main():
                                 "one unit overlap the kernels and copies of the others; bound by the host link")
         if a.check and rank == 0:
             line["e2e"]["parity_max_rel_err"] = check_step(wl, torch)[0]
+        # what the host link alone takes for a step's bytes (after the check: it overwrites the host results
+        # with the same device results, nothing else)
+        l_ms, _ = timed(hp.copies_only, max(3, min(a.steps, 10)), 3, torch, dist, None, 3)
+        line["e2e"]["host_link"] = dict(copies_only_ms=l_ms, frac=l_ms / e_ms,
+                                        note="the step's uploads and downloads alone, both directions at once, "
+                                             "measured in this run; frac = that time / the end-to-end step")
     if a.workload == "c3" and not a.no_extras and not a.only:
         del wl, step_fn
         if not a.no_e2e:
