@@ -671,6 +671,13 @@ def bind_to_gpu_numa_node(local):
     return None
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload's three kernels, from one ncu
+# capture of `python bench.py --steps 1 --warmup 3 --blocks 1 --no-graph ...` (profiles/dram_traffic_c3_step.md)
+C3_TRAFFIC = {"fused_kernel(fwd x->v->y)": 693309696 + 675111424,
+              "fused_kernel(bwd gO->dV->dX)": 198073856 + 106014720,
+              "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": 336965888 + 29999616}
+
+
 class HostPipeline:
     """The step with HOST inputs and outputs: x and gO of every projection start in pinned host memory;
     y, dX, dA and dB end in pinned host memory.  The batch is cut into row blocks - the train rows, then
@@ -1408,9 +1415,11 @@ def main():
         top = max(kb, key=lambda k: kb[k][0])
         t_ms, nbytes, nl = kb[top]
         ach = nbytes / (t_ms * 1e-3) / 1e9
-        # traffic stays null: no ncu capture of this very kernel and workload is read here
+        # DRAM bytes of one launch from the ncu capture of this very workload (seeded, so every run moves the
+        # same bytes); null for any other workload or restriction of it
+        traffic = C3_TRAFFIC.get(top) if (a.workload == "c3" and not a.only and world == 1) else None
         line["roofline"] = dict(bound="hbm", kernel=top, achieved=ach, peak=peak, unit="GB/s", frac=ach / peak,
-                                peak_source=which, traffic=None, launches_per_step=nl,
+                                peak_source=which, traffic=traffic, launches_per_step=nl,
                                 avg_launch_us=t_ms * 1e3 / nl, algorithmic_bytes_per_launch=nbytes / nl)
         line["kernels"] = {k: dict(ms_per_step=v[0], gbs=v[1] / (v[0] * 1e-3) / 1e9, frac=v[1] / (v[0] * 1e-3) / 1e9 / peak,
                                    launches=v[2], share=v[0] / sum(x[0] for x in kb.values())) for k, v in kb.items()}
