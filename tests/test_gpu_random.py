@@ -315,3 +315,42 @@ def test_cache_writers_random_shapes(seed):
     assert int(word.item()) == 0
     for got, want in zip(pd, pages):
         assert torch.equal(got.cpu().view(torch.int16), want.view(torch.int16))
+
+
+@pytest.mark.parametrize("rank", [8, 16, 32, 64, 128])
+@pytest.mark.parametrize("h_in,h_out", [(8, 8), (16, 72), (24, 8), (40, 56), (72, 24), (8, 4096), (4096, 8)])
+def test_smallest_hidden_sizes(rank, h_in, h_out):
+    """Hidden sizes below one column step, one 64-column chunk or one slab, in either direction."""
+    from gpu_util import check_forward
+    lens = [1, 70, 0, 9, 130]
+    part = [0, 1, 71, 71, 80]
+    for rm in (False, True):
+        c = O.make_case(500 + rank + h_in, lens, [0, 1, 2, 1, 0], 3, h_in, h_out, rank, torch.bfloat16,
+                        is_row_major=rm, a_std=1.0 / np.sqrt(max(h_in, 64)))
+        check_forward(c)
+        check_forward(c, indexed=True)
+        from test_gpu_parity import _grad_close as gc, _oracle_bwd, _run_bwd
+        cb = O.make_case(600 + rank + h_in, [80], [0], 4, h_in, h_out, rank, torch.bfloat16, is_row_major=rm,
+                         a_std=1.0 / np.sqrt(max(h_in, 64)))
+        dx, dA, dB = _run_bwd(cb, part)
+        gx, gA, gB = _oracle_bwd(cb, part)
+        gc(dx, gx, "dX")
+        for p in (0, 1, 3):
+            gc(dA[p], gA[p], f"dA{p}")
+            gc(dB[p], gB[p], f"dB{p}")
+
+
+@pytest.mark.parametrize("rank", [16, 64])
+def test_thousands_of_segments_and_a_long_batch(rank):
+    """6000 segments of 0-3 rows (more pieces than any launch of the other tests holds), then 150 000 rows in a
+    handful of segments."""
+    from gpu_util import check_forward
+    rng = np.random.default_rng(77 + rank)
+    lens = [int(x) for x in rng.integers(0, 4, size=6000)]
+    ids = [int(i) for i in rng.integers(0, 5, size=6000)]
+    c = O.make_case(78, lens, ids, 5, 264, 136, rank, torch.bfloat16)
+    check_forward(c)
+    check_forward(c, indexed=True)
+    lens = [70000, 1, 50000, 29999]
+    c = O.make_case(79, lens, [0, 1, 1, 0], 2, 72, 64, rank, torch.float16, is_row_major=True)
+    check_forward(c)
