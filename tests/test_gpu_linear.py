@@ -330,3 +330,73 @@ def test_segments_rebuilt_inside_a_cuda_graph_follow_new_requests():
         assert bool((y[n:] == 7.0).all()), "rows past the batch must stay untouched"
         hdr = plan_buf[:4].tolist()
         assert hdr[1] == 0, f"plan recorded fault bits {hdr[1]}"
+
+
+@pytest.mark.parametrize("path", ["fused", "reference_ops"])
+@pytest.mark.parametrize("seed", list(range(8)))
+def test_linear_training_step_random_batches(seed, path):
+    """Seeded random mixes of train partitions, prefill requests and decode tokens through the module and its
+    autograd function, against fp32 autograd of the same function on the rounded inputs."""
+    from loquetier_b200.kernel_utils import BatchLenInfo
+    from loquetier_b200.mixed_lora import MixedLoraContext, MixedLoraLinear, NamedLoraLayer
+    rng = np.random.default_rng(4000 + seed)
+    dt = torch.bfloat16 if seed % 2 == 0 else torch.float16
+    h_in, h_out = int(rng.integers(4, 120)) * 8, int(rng.integers(4, 120)) * 8
+    r = int(rng.choice([8, 16, 32, 64]))
+    n_ad = int(rng.integers(2, 7))
+    ntrain = int(rng.integers(0, min(3, n_ad) + 1))
+    train_idx = [int(i) for i in rng.permutation(n_ad)[:ntrain]]
+    trains = [(int(rng.integers(1, 4)), int(rng.integers(1, 60))) for _ in range(ntrain)]
+    prefills = [int(rng.integers(1, 90)) for _ in range(int(rng.integers(0, 4)))]
+    dec = [(int(rng.integers(0, n_ad)), int(rng.integers(1, 6))) for _ in range(int(rng.integers(0, 5)))]
+    lens = [c * n for c, n in trains] + prefills + [n for _, n in dec]
+    ids = train_idx + [int(rng.integers(0, n_ad)) for _ in prefills] + [a for a, _ in dec]
+    if sum(lens) == 0:
+        pytest.skip("empty draw")
+    T, tl = sum(lens), sum(c * n for c, n in trains)
+    g = torch.Generator().manual_seed(4000 + seed)
+    x = torch.randn((T, h_in), generator=g).to(dt)
+    wbase = (torch.randn((h_out, h_in), generator=g) * 0.02).to(dt)
+    was = [(torch.randn((r, h_in), generator=g) / np.sqrt(h_in)).to(dt) for _ in range(n_ad)]
+    wbs = [(torch.randn((h_out, r), generator=g) * 0.02).to(dt) for _ in range(n_ad)]
+    go = torch.randn((T, h_out), generator=g).to(dt)
+    scale = [float(rng.choice([1.0, 2.0, 0.5, 1.5])) for _ in range(n_ad)]
+
+    base = nn.Linear(h_in, h_out, bias=False, dtype=dt, device=DEV)
+    with torch.no_grad():
+        base.weight.copy_(wbase)
+    base.weight.requires_grad_(False)
+    ads = [NamedLoraLayer(f"a{i}", was[i].to(DEV).contiguous(), wbs[i].to(DEV).contiguous(), nn.Identity(),
+                          scale[i]) for i in range(n_ad)]
+    ctx = MixedLoraContext()
+    lin = MixedLoraLinear(ctx, base, ads, r, dt)
+    lin.set_trainable(train_idx)
+    blen = BatchLenInfo(trains, prefills, sum(n for _, n in dec), [], torch.device(DEV))
+    seg = torch.cumsum(torch.tensor([0] + lens, dtype=torch.int32, device=DEV), 0, dtype=torch.int32)
+    ctx.update(blen, ids, torch.tensor(lens, dtype=torch.int32, device=DEV), seg, train_idx)
+    xd = x.to(DEV).requires_grad_(True)
+    y = lin(xd) if path == "fused" else lin.forward_reference_ops(xd)
+    y.backward(go.to(DEV))
+    torch.cuda.synchronize()
+
+    x32 = x.float().requires_grad_(True)
+    A = [w.float().requires_grad_(True) for w in was]
+    B = [w.float().requires_grad_(True) for w in wbs]
+    seg_h = np.concatenate([[0], np.cumsum(lens)])
+    outs = []
+    for i, a in enumerate(ids):
+        xs = x32[seg_h[i]:seg_h[i + 1]]
+        outs.append(xs @ wbase.float().t() + scale[a] * ((xs @ A[a].t()) @ B[a].t()))
+    y32 = torch.cat(outs)
+    assert_close(y, y32.detach(), rtol=2e-2, atol=2e-2, what="y")
+    want_gx = go.float() @ wbase.float()
+    if tl:
+        (y32[:tl] * go.float()[:tl]).sum().backward()
+        want_gx[:tl] = x32.grad[:tl]
+    s = max(1.0, float(want_gx.abs().max()))
+    assert_close(xd.grad.float().cpu(), want_gx, rtol=1e-2, atol=1e-2 * s, what="grad_x")
+    for idx in train_idx:
+        ga = lin.get_parameter(f"lora-{idx}-A").grad
+        gb = lin.get_parameter(f"lora-{idx}-B").grad
+        assert_close(ga, A[idx].grad, rtol=1e-2, atol=1e-2 * max(1e-3, float(A[idx].grad.abs().max())), what=f"dA{idx}")
+        assert_close(gb, B[idx].grad, rtol=1e-2, atol=1e-2 * max(1e-3, float(B[idx].grad.abs().max())), what=f"dB{idx}")
