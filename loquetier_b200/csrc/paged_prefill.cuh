@@ -337,6 +337,26 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     return;
   }
 
+  // The queries of the tile: 16 threads per row (4 dims and their partners each), 16 rows per pass.  All loads
+  // of a softmax thread go out here, so that their latency passes behind the barrier set-up and the
+  // tensor-memory allocation below; the rotation that consumes them follows the allocation.
+  uint2 qo_raw[kPfRows / 16], qp_raw[kPfRows / 16];
+#pragma unroll
+  for (int it = 0; it < kPfRows / 16; ++it) qo_raw[it] = qp_raw[it] = make_uint2(0u, 0u);
+  if (warp < 8) {
+    const int d0 = (tid & 15) * 4;
+    const int rg = tid >> 4;
+#pragma unroll
+    for (int it = 0; it < kPfRows / 16; ++it) {
+      const int r = rg + 16 * it;
+      if (r / G < nq) {
+        const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi0 + r / G) * Nq + kvh * G + r % G) * kPdDim;
+        qo_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0));
+        qp_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0 + 64));
+      }
+    }
+  }
+
   if (tid == 0) PF_STAMP(0, 63, 1);
   if (tid == 0) {
     for (int i = 0; i < NS; ++i) {
@@ -468,18 +488,6 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
         const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
         fast_sincospi(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
         fast_sincospi(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
-      }
-      // all loads of the thread first (one exposure of the memory latency), then the arithmetic
-      uint2 qo_raw[kPfRows / 16], qp_raw[kPfRows / 16];
-#pragma unroll
-      for (int it = 0; it < kPfRows / 16; ++it) {
-        const int r = rg + 16 * it;
-        qo_raw[it] = qp_raw[it] = make_uint2(0u, 0u);
-        if (r / G < nq) {
-          const T* qp = static_cast<const T*>(a.q) + (static_cast<size_t>(qo0 + qi0 + r / G) * Nq + kvh * G + r % G) * kPdDim;
-          qo_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0));
-          qp_raw[it] = __ldg(reinterpret_cast<const uint2*>(qp + d0 + 64));
-        }
       }
 #pragma unroll
       for (int it = 0; it < kPfRows / 16; ++it) {
