@@ -482,39 +482,51 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       const int rg = tid >> 4;
       constexpr int STEP = 16 / G;
       const float qscale = 1.4426950408889634f * rsqrtf(static_cast<float>(kPdDim));   // log2(e) / sqrt(d)
-      float cc[4], ss[4], c1[4], s1[4];
+      // cos and sin of the four dimensions as two packed pairs, with the softmax scale folded in (a rotation
+      // is linear, so the stepped pair keeps the factor); the step's own cos and sin carry none
+      uint64_t cc2[2], ss2[2], c12[2], s12[2];
+      {
+        float cc[4], ss[4], c1[4], s1[4];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
-        fast_sincospi(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
-        fast_sincospi(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
+        for (int i = 0; i < 4; ++i) {
+          const float f = exp2f(-a.log2_theta * static_cast<float>(2 * (d0 + i)) * (1.0f / kPdDim)) * 0.31830988618379067f;
+          fast_sincospi(static_cast<float>(pos0 + qi0 + rg / G) * f, &ss[i], &cc[i]);
+          fast_sincospi(static_cast<float>(STEP) * f, &s1[i], &c1[i]);
+        }
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          cc2[k] = pack_f32x2(cc[2 * k] * qscale, cc[2 * k + 1] * qscale);
+          ss2[k] = pack_f32x2(ss[2 * k] * qscale, ss[2 * k + 1] * qscale);
+          c12[k] = pack_f32x2(c1[2 * k], c1[2 * k + 1]);
+          s12[k] = pack_f32x2(s1[2 * k], s1[2 * k + 1]);
+        }
       }
+      constexpr uint64_t kNeg2 = 0x8000000080000000ull;   // flips the sign of both halves
 #pragma unroll
       for (int it = 0; it < kPfRows / 16; ++it) {
         const int r = rg + 16 * it;
-        uint32_t wo0 = 0u, wo1 = 0u, wp0 = 0u, wp1 = 0u;
+        uint32_t wo[2] = {0u, 0u}, wp[2] = {0u, 0u};
         if (r / G < nq) {
-          const uint2 uo = qo_raw[it];
-          const uint2 up = qp_raw[it];
-          const float2 o0 = unpack2<T>(uo.x), o1 = unpack2<T>(uo.y), q0 = unpack2<T>(up.x), q1 = unpack2<T>(up.y);
-          const float own[4] = {o0.x, o0.y, o1.x, o1.y}, par[4] = {q0.x, q0.y, q1.x, q1.y};
-          float ro[4], rp[4];
+          const uint32_t uo[2] = {qo_raw[it].x, qo_raw[it].y}, up[2] = {qp_raw[it].x, qp_raw[it].y};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            ro[i] = (own[i] * cc[i] - par[i] * ss[i]) * qscale;
-            rp[i] = (par[i] * cc[i] + own[i] * ss[i]) * qscale;
+          for (int k = 0; k < 2; ++k) {
+            const float2 o = unpack2<T>(uo[k]), q = unpack2<T>(up[k]);
+            const uint64_t own = pack_f32x2(o.x, o.y), par = pack_f32x2(q.x, q.y);
+            float x0, x1;
+            unpack_f32x2(fma_f32x2(own, cc2[k], mul_f32x2(par, ss2[k] ^ kNeg2)), x0, x1);   // own cos - partner sin
+            wo[k] = pack2<T>(x0, x1);
+            unpack_f32x2(fma_f32x2(par, cc2[k], mul_f32x2(own, ss2[k])), x0, x1);           // partner cos + own sin
+            wp[k] = pack2<T>(x0, x1);
           }
-          wo0 = pack2<T>(ro[0], ro[1]); wo1 = pack2<T>(ro[2], ro[3]);
-          wp0 = pack2<T>(rp[0], rp[1]); wp1 = pack2<T>(rp[2], rp[3]);
         }
         const uint32_t addr = qs + r * 128 + (((d0 >> 3) ^ (r & 7)) << 4) + (d0 & 7) * 2;
-        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(wo0), "r"(wo1) : "memory");
-        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr + kPfRows * 128), "r"(wp0), "r"(wp1) : "memory");
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr), "r"(wo[0]), "r"(wo[1]) : "memory");
+        asm volatile("st.shared.v2.b32 [%0], {%1, %2};\n" ::"r"(addr + kPfRows * 128), "r"(wp[0]), "r"(wp[1]) : "memory");
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float cn = cc[i] * c1[i] - ss[i] * s1[i];
-          ss[i] = ss[i] * c1[i] + cc[i] * s1[i];
-          cc[i] = cn;
+        for (int k = 0; k < 2; ++k) {
+          const uint64_t cn = fma_f32x2(cc2[k], c12[k], mul_f32x2(ss2[k] ^ kNeg2, s12[k]));
+          ss2[k] = fma_f32x2(ss2[k], c12[k], mul_f32x2(cc2[k], s12[k]));
+          cc2[k] = cn;
         }
       }
       fence_proxy_async();   // the MMA reads Q through the async proxy
