@@ -145,8 +145,25 @@ __device__ __forceinline__ void pair_barrier(int wq) {
 // bounded wait that also works without an error word
 __device__ __forceinline__ void pf_wait(uint32_t bar, uint32_t parity, int* err, bool& dead) {
   if (dead) return;
-  for (int i = 0; i < kWaitLimit; ++i)
+  for (int i = 0; i < kWaitLimit; ++i) {
+#ifdef SMLM_PF_SOFT_NS
+    if (mbar_try_wait_for(bar, parity, SMLM_PF_SOFT_NS)) return;
+#else
     if (mbar_try_wait(bar, parity)) return;
+#endif
+  }
+  dead = true;
+  if (err != nullptr) atomicOr(err, kErrTimeout);
+}
+
+// the same for the single-thread roles (producer, issuers), which wait most of the time: polls up to 4 us apart
+#ifndef SMLM_PF_ROLE_NS
+#define SMLM_PF_ROLE_NS 4000
+#endif
+__device__ __forceinline__ void pf_wait_role(uint32_t bar, uint32_t parity, int* err, bool& dead) {
+  if (dead) return;
+  for (int i = 0; i < kWaitLimit; ++i)
+    if (mbar_try_wait_for(bar, parity, SMLM_PF_ROLE_NS)) return;
   dead = true;
   if (err != nullptr) atomicOr(err, kErrTimeout);
 }
@@ -394,12 +411,12 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       for (int j = 0; j < ntiles; ++j) {
         const int st = j % NS, use = j / NS;
         const int y = row0 + j * kPfKeys;
-        if (use > 0) pf_wait(k_empty + st * 8, (use - 1) & 1, a.err, dead);
+        if (use > 0) pf_wait_role(k_empty + st * 8, (use - 1) & 1, a.err, dead);
         if (dead) break;   // nothing new is put in flight once a wait has given up
         mbar_expect_tx(k_full + st * 8, kPfKvBytes);
         tma_load_2d(ks0 + st * kPfKvBytes, &kvmap, xk, y, k_full + st * 8);
         tma_load_2d(ks0 + st * kPfKvBytes + kPfKeys * 128, &kvmap, xk + 64, y, k_full + st * 8);
-        if (use > 0) pf_wait(v_empty + st * 8, (use - 1) & 1, a.err, dead);
+        if (use > 0) pf_wait_role(v_empty + st * 8, (use - 1) & 1, a.err, dead);
         if (dead) break;
         mbar_expect_tx(v_full + st * 8, kPfKvBytes);
         tma_load_2d(vs0 + st * kPfKvBytes, &kvmap, xv, y, v_full + st * 8);
@@ -410,11 +427,11 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
     // ---------------- issuer of S = Q . K^T: runs up to two tiles ahead of the softmax ----------------
     if (lane == 0) {
       const uint32_t idesc_s = tc_idesc<T>(kPfKeys, false);
-      pf_wait(q_full, 0, a.err, dead);
+      pf_wait_role(q_full, 0, a.err, dead);
       for (int j = 0; j < ntiles; ++j) {
         const int st = j % NS, sb = j % kPfSBufs, use = j / kPfSBufs;
-        pf_wait(k_full + st * 8, (j / NS) & 1, a.err, dead);
-        if (use > 0) pf_wait(s_empty + sb * 8, (use - 1) & 1, a.err, dead);
+        pf_wait_role(k_full + st * 8, (j / NS) & 1, a.err, dead);
+        if (use > 0) pf_wait_role(s_empty + sb * 8, (use - 1) & 1, a.err, dead);
         tc_fence_after();
         if (!dead) {
           const uint32_t kst = ks0 + st * kPfKvBytes;
@@ -437,9 +454,9 @@ __global__ void __launch_bounds__(kPfThreads, kPfCtasPerSm) paged_prefill_kernel
       const uint32_t idesc_o = tc_idesc<T>(kPdDim, true);
       for (int j = 0; j < ntiles; ++j) {
         const int st = j % NS;
-        pf_wait(v_full + st * 8, (j / NS) & 1, a.err, dead);
+        pf_wait_role(v_full + st * 8, (j / NS) & 1, a.err, dead);
         PF_STAMP(1, j, 1);
-        pf_wait(p_full, j & 1, a.err, dead);
+        pf_wait_role(p_full, j & 1, a.err, dead);
         PF_STAMP(1, j, 2);
         tc_fence_after();
         if (!dead) {

@@ -282,6 +282,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same poll with an explicit upper bound (in nanoseconds) on the time the thread stays suspended: it
+// still resumes as soon as the phase completes, but a warp that mostly waits polls that much less often
+// and leaves the issue slots to the warps that compute.
+__device__ __forceinline__ bool mbar_try_wait_for(uint32_t bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n.reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait: gives up after kWaitLimit polls (each poll already suspends the
 // thread for a hardware-defined interval), records kErrTimeout and lets the caller
 // run to completion instead of hanging the GPU.
