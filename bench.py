@@ -672,7 +672,7 @@ def bind_to_gpu_numa_node(local):
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload's three kernels, from one ncu
-# capture of `python bench.py --steps 1 --warmup 3 --blocks 1 --no-graph ...` (profiles/dram_traffic_c3_step.md)
+# capture of `python bench.py --steps 1 --warmup 3 --blocks 1 --no-graph ...` (the capture is summarised with the other profiles)
 C3_TRAFFIC = {"fused_kernel(fwd x->v->y)": 693309696 + 675111424,
               "fused_kernel(bwd gO->dV->dX)": 198073856 + 106014720,
               "wgrad_kernel(dB=gO^T.V, dA=dV^T.X)": 336965888 + 29999616}
